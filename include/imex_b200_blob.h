@@ -1,0 +1,95 @@
+/* Kernel-descriptor blob: what gpuModuleLoad receives on the B200 path.
+ *
+ * In the reference the `gpu.binary` attribute of a gpu.module holds a
+ * serialised SPIR-V module (lib/Transforms/SerializeSPIRV.cpp:64-69,
+ * include/imex/Utils/GPUSerialize.h:15) that Level Zero JIT-compiles in
+ * gpuModuleLoad (lib/ExecutionEngine/LEVELZERORUNTIME/LevelZeroRuntimeWrappers.cpp:396-432).
+ * Here the same slot holds a table of descriptors, one per outlined kernel:
+ * which hot-path op the kernel is, its element types, its static shape and
+ * its fused epilogue.  Kernel arguments are bare pointers with no shape
+ * (lib/Conversion/GPUXToLLVM/GPUXToLLVMPass.cpp:571-584), so the shape has to
+ * travel here.  The outlined kernel NAME is not semantic (`test_kernel`,
+ * `test_kernel_0`, ...): gpuKernelGet only uses it to pick the table row.
+ *
+ * Layout (little endian, no padding beyond what the structs show):
+ *   ImexBlobHeader, then num_kernels * ImexKernelDesc.
+ * The magic can never be mistaken for SPIR-V (0x07230203); a blob without it
+ * is rejected through the library's error convention.
+ */
+#ifndef IMEX_B200_BLOB_H
+#define IMEX_B200_BLOB_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IMEX_BLOB_MAGIC 0x0030303242584D49ULL /* "IMXB200\0" */
+#define IMEX_BLOB_VERSION 1u
+#define IMEX_KERNEL_NAME_MAX 64
+
+/* Hot-path ops.  Argument order of each (all bare device pointers, in the
+ * order the launch passes them; trailing scalar params the lowering adds for
+ * loop bounds are ignored):
+ *   GEMM            A[M,K], B[K,N], C[M,N] (, bias[N] when IMEX_FLAG_BIAS)
+ *                   dims = {M, N, K}; C = (C when IMEX_FLAG_ACCUMULATE else 0) + A.B,
+ *                   then + bias, then epilogue
+ *   SOFTMAX         X[rows,cols], Y[rows,cols]           dims = {rows, cols}
+ *   REDUCE_ROWS     X[rows,cols], Y[rows]                dims = {rows, cols}
+ *                   Y[r] = (Y[r] when ACCUMULATE else 0) + sum_c X[r,c]
+ *   REDUCE_LEADING  X[lead,inner], Y[inner]              dims = {lead, inner}
+ *   REDUCE_ALL      X[n], Y[1]                           dims = {n}
+ *   TRANSPOSE2D     X[rows,cols], Y[cols,rows]           dims = {rows, cols}
+ *   TRANSPOSE3D     X[d0,d1,d2], Y[permuted]             dims = {d0,d1,d2,p0,p1,p2}
+ *   ELTWISE         X[n], Y[n] with `epilogue` applied   dims = {n}
+ *   FILL_UNIFORM    Y[n]  dims = {n, seed, first}; fparams = {lo, hi}
+ *   FILL_NORMAL     Y[n]  dims = {n, seed, first}; fparams = {mean, stddev}
+ */
+enum ImexOp {
+  IMEX_OP_GEMM = 1,
+  IMEX_OP_SOFTMAX = 2,
+  IMEX_OP_REDUCE_ROWS = 3,
+  IMEX_OP_REDUCE_LEADING = 4,
+  IMEX_OP_REDUCE_ALL = 5,
+  IMEX_OP_TRANSPOSE2D = 6,
+  IMEX_OP_TRANSPOSE3D = 7,
+  IMEX_OP_ELTWISE = 8,
+  IMEX_OP_FILL_UNIFORM = 9,
+  IMEX_OP_FILL_NORMAL = 10
+};
+
+enum ImexDType { IMEX_F32 = 1, IMEX_BF16 = 2, IMEX_F16 = 3, IMEX_I32 = 4 };
+
+/* relu: cmpf ugt x,0 ; select x,0   (benchmarks/relu/relu_gpu.mlir.in:6-11)
+ * silu: x * 1/(exp(-x)+1)           (benchmarks/silu/silu_gpu.mlir.in:6-18) */
+enum ImexEpilogue { IMEX_EPI_NONE = 0, IMEX_EPI_RELU = 1, IMEX_EPI_SILU = 2 };
+
+enum ImexFlags {
+  IMEX_FLAG_ACCUMULATE = 1u << 0, /* output is read as the initial value */
+  IMEX_FLAG_BIAS = 1u << 1,       /* GEMM: 4th pointer is bias[N] (f32)   */
+  IMEX_FLAG_SOFTMAX_NEG_INF = 1u << 2 /* PlaidML form: max starts at -inf, cmpf ogt */
+};
+
+typedef struct ImexBlobHeader {
+  uint64_t magic;
+  uint32_t version;
+  uint32_t num_kernels;
+} ImexBlobHeader;
+
+typedef struct ImexKernelDesc {
+  char name[IMEX_KERNEL_NAME_MAX]; /* NUL-terminated outlined kernel name */
+  uint32_t op;                     /* ImexOp */
+  uint32_t in_dtype;               /* ImexDType of the inputs */
+  uint32_t out_dtype;              /* ImexDType of the output */
+  uint32_t epilogue;               /* ImexEpilogue */
+  uint32_t flags;                  /* ImexFlags */
+  uint32_t reserved;
+  int64_t dims[6];
+  float fparams[2];
+} ImexKernelDesc;
+
+#ifdef __cplusplus
+}
+#endif
+#endif

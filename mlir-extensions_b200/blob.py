@@ -1,0 +1,123 @@
+"""Kernel-descriptor blobs (include/imex_b200_blob.h) built from Python.
+
+A blob is what the front end attaches to a gpu.module in place of the
+reference's serialised SPIR-V (lib/Transforms/SerializeSPIRV.cpp:64-69) and
+what gpuModuleLoad receives."""
+import ctypes as C
+import struct
+
+MAGIC = 0x0030303242584D49
+VERSION = 1
+NAME_MAX = 64
+
+OP_GEMM, OP_SOFTMAX, OP_REDUCE_ROWS, OP_REDUCE_LEADING, OP_REDUCE_ALL = 1, 2, 3, 4, 5
+OP_TRANSPOSE2D, OP_TRANSPOSE3D, OP_ELTWISE, OP_FILL_UNIFORM, OP_FILL_NORMAL = 6, 7, 8, 9, 10
+F32, BF16, F16, I32 = 1, 2, 3, 4
+EPI_NONE, EPI_RELU, EPI_SILU = 0, 1, 2
+FLAG_ACCUMULATE, FLAG_BIAS, FLAG_SOFTMAX_NEG_INF = 1, 2, 4
+
+DTYPE_BYTES = {F32: 4, I32: 4, BF16: 2, F16: 2}
+_DESC = struct.Struct("<64s6I6q2f")  # ImexKernelDesc, 144 bytes
+_HEADER = struct.Struct("<QII")      # ImexBlobHeader, 16 bytes
+assert _DESC.size == 144 and _HEADER.size == 16
+
+
+class KernelDesc:
+    def __init__(self, name, op, in_dtype=F32, out_dtype=F32, epilogue=EPI_NONE, flags=0,
+                 dims=(), fparams=(0.0, 0.0)):
+        if len(name.encode()) >= NAME_MAX:
+            raise ValueError("kernel name too long")
+        if len(dims) > 6:
+            raise ValueError("at most 6 dims")
+        self.name, self.op = name, op
+        self.in_dtype, self.out_dtype = in_dtype, out_dtype
+        self.epilogue, self.flags = epilogue, flags
+        self.dims = tuple(int(d) for d in dims) + (0,) * (6 - len(dims))
+        self.fparams = tuple(float(f) for f in fparams)
+
+    def pack(self):
+        return _DESC.pack(self.name.encode(), self.op, self.in_dtype, self.out_dtype,
+                          self.epilogue, self.flags, 0, *self.dims, *self.fparams)
+
+
+def pack_blob(descs):
+    """bytes of a blob holding `descs` (list of KernelDesc)."""
+    return _HEADER.pack(MAGIC, VERSION, len(descs)) + b"".join(d.pack() for d in descs)
+
+
+def unpack_blob(data):
+    magic, version, n = _HEADER.unpack_from(data, 0)
+    if magic != MAGIC:
+        raise ValueError("bad blob magic")
+    out = []
+    for i in range(n):
+        f = _DESC.unpack_from(data, _HEADER.size + i * _DESC.size)
+        out.append(KernelDesc(f[0].split(b"\0")[0].decode(), f[1], f[2], f[3], f[4], f[5],
+                              f[7:13], f[13:15]))
+    return version, out
+
+
+def gemm(name, M, N, K, in_dtype=BF16, epilogue=EPI_NONE, accumulate=False, bias=False):
+    flags = (FLAG_ACCUMULATE if accumulate else 0) | (FLAG_BIAS if bias else 0)
+    return KernelDesc(name, OP_GEMM, in_dtype, F32, epilogue, flags, (M, N, K))
+
+
+def softmax(name, rows, cols, neg_inf_init=False):
+    return KernelDesc(name, OP_SOFTMAX, F32, F32, 0, FLAG_SOFTMAX_NEG_INF if neg_inf_init else 0,
+                      (rows, cols))
+
+
+def reduce_rows(name, rows, cols, accumulate=False):
+    return KernelDesc(name, OP_REDUCE_ROWS, F32, F32, 0, FLAG_ACCUMULATE if accumulate else 0,
+                      (rows, cols))
+
+
+def reduce_leading(name, lead, inner, accumulate=False):
+    return KernelDesc(name, OP_REDUCE_LEADING, F32, F32, 0, FLAG_ACCUMULATE if accumulate else 0,
+                      (lead, inner))
+
+
+def reduce_all(name, n, accumulate=False):
+    return KernelDesc(name, OP_REDUCE_ALL, F32, F32, 0, FLAG_ACCUMULATE if accumulate else 0, (n,))
+
+
+def transpose2d(name, rows, cols, dtype=F32):
+    return KernelDesc(name, OP_TRANSPOSE2D, dtype, dtype, 0, 0, (rows, cols))
+
+
+def transpose3d(name, dims, perm, dtype=F32):
+    return KernelDesc(name, OP_TRANSPOSE3D, dtype, dtype, 0, 0, tuple(dims) + tuple(perm))
+
+
+def eltwise(name, n, epilogue):
+    return KernelDesc(name, OP_ELTWISE, F32, F32, epilogue, 0, (n,))
+
+
+def fill_uniform(name, n, dtype, seed, lo, hi, first=0):
+    return KernelDesc(name, OP_FILL_UNIFORM, dtype, dtype, 0, 0, (n, seed, first), (lo, hi))
+
+
+def fill_normal(name, n, dtype, seed, mean, stddev, first=0):
+    return KernelDesc(name, OP_FILL_NORMAL, dtype, dtype, 0, 0, (n, seed, first), (mean, stddev))
+
+
+_KEEP = []
+
+
+class Blob:
+    """Owns the bytes at a fixed address for the life of the process.
+
+    gpuModuleLoad caches parsed modules by blob ADDRESS until exit (in the
+    reference the blob is a global constant of the compiled host module), so a
+    blob must never be freed and its address reused for other contents."""
+
+    def __init__(self, descs):
+        _KEEP.append(self)
+        self.descs = list(descs)
+        data = pack_blob(self.descs)
+        self.buffer = C.create_string_buffer(data, len(data))
+        self.size = len(data)
+
+    @property
+    def address(self):
+        return C.addressof(self.buffer)

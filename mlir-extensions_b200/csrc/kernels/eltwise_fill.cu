@@ -1,0 +1,129 @@
+// Standalone relu / silu (benchmarks/relu/relu_gpu.mlir.in,
+// benchmarks/silu/silu_gpu.mlir.in) and the seeded input generators that
+// stand in for the reference's unseeded std::mt19937 fill
+// (lib/ExecutionEngine/ImexRunnerUtils.cpp:38-50).
+#include "epilogue.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace imex {
+namespace {
+
+__global__ void __launch_bounds__(256)
+eltwise_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t n, int epilogue,
+               int vec_ok) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (vec_ok) {
+    const int64_t nvec = n >> 2;
+    for (int64_t i = t0; i < nvec; i += stride) {
+      float4 v = reinterpret_cast<const float4 *>(x)[i];
+      v.x = apply_epilogue(v.x, epilogue);
+      v.y = apply_epilogue(v.y, epilogue);
+      v.z = apply_epilogue(v.z, epilogue);
+      v.w = apply_epilogue(v.w, epilogue);
+      reinterpret_cast<float4 *>(y)[i] = v;
+    }
+    for (int64_t i = (nvec << 2) + t0; i < n; i += stride) y[i] = apply_epilogue(x[i], epilogue);
+  } else {
+    for (int64_t i = t0; i < n; i += stride) y[i] = apply_epilogue(x[i], epilogue);
+  }
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ULL;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  return z ^ (z >> 31);
+}
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+fill_uniform_kernel(T *__restrict__ y, int64_t n, uint64_t seed, int64_t first, float lo,
+                    float hi) {
+  const float span = __fsub_rn(hi, lo);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    uint64_t h = splitmix64(static_cast<uint64_t>(first + i) + seed * 0x9E3779B97F4A7C15ULL);
+    float u = __fmul_rn(static_cast<float>(static_cast<uint32_t>(h >> 40)), 1.0f / 16777216.0f);
+    y[i] = from_f32<T>(__fadd_rn(lo, __fmul_rn(u, span)));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+fill_normal_kernel(T *__restrict__ y, int64_t n, uint64_t seed, int64_t first, float mean,
+                   float stddev) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    uint64_t h = splitmix64(static_cast<uint64_t>(first + i) + seed * 0x9E3779B97F4A7C15ULL);
+    float u1 = (static_cast<float>(static_cast<uint32_t>(h >> 40)) + 1.0f) * (1.0f / 16777216.0f);
+    float u2 = static_cast<float>(static_cast<uint32_t>(h >> 16) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+    float r = sqrtf(-2.0f * logf(u1));
+    float z = r * cospif(2.0f * u2);
+    y[i] = from_f32<T>(mean + stddev * z);
+  }
+}
+
+unsigned grid_for(int64_t n) {
+  int64_t b = (n + 255) / 256;
+  if (b > 148 * 32) b = 148 * 32;
+  return static_cast<unsigned>(b < 1 ? 1 : b);
+}
+
+} // namespace
+
+cudaError_t launch_eltwise_f32(const float *x, float *y, int64_t n, int epilogue,
+                               cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  int vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  eltwise_kernel<<<grid_for((n + 3) / 4), 256, 0, stream>>>(x, y, n, epilogue, vec_ok);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fill_uniform(void *y, int64_t n, int dtype, uint64_t seed, int64_t first,
+                                float lo, float hi, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if (dtype == kF32)
+    fill_uniform_kernel<float><<<grid_for(n), 256, 0, stream>>>(static_cast<float *>(y), n, seed,
+                                                                first, lo, hi);
+  else if (dtype == kBF16)
+    fill_uniform_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, stream>>>(
+        static_cast<__nv_bfloat16 *>(y), n, seed, first, lo, hi);
+  else if (dtype == kF16)
+    fill_uniform_kernel<__half><<<grid_for(n), 256, 0, stream>>>(static_cast<__half *>(y), n, seed,
+                                                                 first, lo, hi);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fill_normal(void *y, int64_t n, int dtype, uint64_t seed, int64_t first,
+                               float mean, float stddev, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if (dtype == kF32)
+    fill_normal_kernel<float><<<grid_for(n), 256, 0, stream>>>(static_cast<float *>(y), n, seed,
+                                                               first, mean, stddev);
+  else if (dtype == kBF16)
+    fill_normal_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, stream>>>(
+        static_cast<__nv_bfloat16 *>(y), n, seed, first, mean, stddev);
+  else if (dtype == kF16)
+    fill_normal_kernel<__half><<<grid_for(n), 256, 0, stream>>>(static_cast<__half *>(y), n, seed,
+                                                                first, mean, stddev);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+} // namespace imex

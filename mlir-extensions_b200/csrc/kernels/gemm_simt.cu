@@ -1,0 +1,112 @@
+// Bit-exact SIMT GEMM: C[i,j] = C0[i,j] + sum_k A[i,k]*B[k,j] with k ascending
+// and the multiply and the add rounded separately — the arithmetic of the
+// scalar loop nest that convert-linalg-to-loops produces for linalg.matmul
+// (reference: test/PlaidML/OpTest.Matmul.mlir:14-20,
+//  test/PlaidML/OpTest.GEMM_FLOAT32.mlir:37-42; 16-bit inputs extended to f32
+//  first as in test/SPIRV/OpTest.GEMM_BF16_ACC_F32.mlir:126-141).
+// Changing the summation order moves some outputs by far more than 1e-4
+// relative (cancellation), so this path keeps the order; it is FP32-pipe
+// bound, not a tensor-core kernel.
+#include "epilogue.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace imex {
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const T *__restrict__ A, const T *__restrict__ B, float *__restrict__ C,
+                 const float *__restrict__ bias, int64_t M, int64_t N, int64_t K,
+                 int epilogue, int accumulate) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid % 16, ty = tid / 16;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * BM;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * BN;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      int64_t r = m0 + ty * TM + i, c = n0 + tx * TN + j;
+      acc[i][j] = (accumulate && r < M && c < N) ? C[r * N + c] : 0.0f;
+    }
+
+  for (int64_t k0 = 0; k0 < K; k0 += BK) {
+    // A tile: BM x BK, stored k-major so the inner loop reads it conflict-free
+    for (int e = tid; e < BM * BK; e += 256) {
+      int m = e / BK, k = e % BK;
+      int64_t r = m0 + m, kk = k0 + k;
+      As[k][m] = (r < M && kk < K) ? to_f32(A[r * K + kk]) : 0.0f;
+    }
+    for (int e = tid; e < BK * BN; e += 256) {
+      int k = e / BN, n = e % BN;
+      int64_t kk = k0 + k, c = n0 + n;
+      Bs[k][n] = (kk < K && c < N) ? to_f32(B[kk * N + c]) : 0.0f;
+    }
+    __syncthreads();
+    // only real k steps: a padded step would add +0 and could flip a -0 result
+    const int kmax = (K - k0 < BK) ? static_cast<int>(K - k0) : BK;
+    for (int k = 0; k < kmax; ++k) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[k][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) b[j] = Bs[k][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j)
+          acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      int64_t r = m0 + ty * TM + i, c = n0 + tx * TN + j;
+      if (r < M && c < N) {
+        float v = acc[i][j];
+        if (bias) v = __fadd_rn(v, bias[c]);
+        C[r * N + c] = apply_epilogue(v, epilogue);
+      }
+    }
+}
+
+} // namespace
+
+cudaError_t launch_gemm_simt(const GemmProblem &p, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0) return cudaSuccess;
+  dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + BM - 1) / BM));
+  if (p.in_dtype == kF32)
+    gemm_simt_kernel<float><<<grid, 256, 0, stream>>>(
+        static_cast<const float *>(p.A), static_cast<const float *>(p.B), p.C, p.bias, p.M, p.N,
+        p.K, p.epilogue, p.accumulate ? 1 : 0);
+  else if (p.in_dtype == kBF16)
+    gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(p.A), static_cast<const __nv_bfloat16 *>(p.B), p.C,
+        p.bias, p.M, p.N, p.K, p.epilogue, p.accumulate ? 1 : 0);
+  else if (p.in_dtype == kF16)
+    gemm_simt_kernel<__half><<<grid, 256, 0, stream>>>(
+        static_cast<const __half *>(p.A), static_cast<const __half *>(p.B), p.C, p.bias, p.M, p.N,
+        p.K, p.epilogue, p.accumulate ? 1 : 0);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+} // namespace imex

@@ -1,0 +1,467 @@
+// bf16/f16 -> f32 GEMM on the 5th-generation tensor cores of sm_100a, with
+// the bias / relu / silu epilogue fused.
+//
+// Reference op: linalg.matmul, C = C0 + A.B with A[M,K], B[K,N] row-major
+// 16-bit and an f32 accumulator (test/SPIRV/OpTest.GEMM_BF16_ACC_F32.mlir:126-141,
+// test/PlaidML/CppEdsl.DotF16_AccF32.mlir:19-47); epilogues are the relu and
+// silu generics (benchmarks/relu/relu_gpu.mlir.in:6-11,
+// benchmarks/silu/silu_gpu.mlir.in:6-18); bias is the row-vector add of
+// test/Integration/Dialect/XeGPU/WG/gemm_4kx4kx4k_f16_f16_f32_bias.mlir:91-113.
+// The reference's GPU lowering of this op is one work-group per C element
+// with a scalar k loop; its tuned Xe kernels tile 256x256 per work-group with
+// DPAS.  Nothing of either is reused here.
+//
+// Structure (one CTA per SM, persistent over 128x256 output tiles):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A tile
+//               (128 x 64, K-major) and the B tile (64 x 256, N-major, as four
+//               64x64 boxes) into a 4-stage 128B-swizzled smem ring, completion
+//               on mbarriers (expect-tx).  No cluster multicast.
+//   warp 1      allocates 512 TMEM columns (two 128x256 f32 accumulators) and
+//               issues tcgen05.mma.cta_group::1.kind::f16 (M128 N256 K16) from
+//               one thread; tcgen05.commit releases smem stages and publishes
+//               finished accumulators.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (32 lanes x 32 columns per
+//               warp and step), add C0 / bias, apply relu or silu, store f32 with
+//               128-bit stores.  Runs on accumulator i while the MMA warp fills
+//               accumulator i^1.
+// Every wait is bounded: when one runs out the warp records a status code in
+// the host-visible status word and leaves its loop; the kernel still drains
+// its loads, frees TMEM and returns.
+#include "epilogue.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace imex {
+namespace {
+
+constexpr int BM = 128;        // tile rows   (UMMA M)
+constexpr int BN = 256;        // tile cols   (UMMA N)
+constexpr int BK = 64;         // k per stage (one 128-byte swizzle row of 16-bit elements)
+constexpr int UMMA_K = 16;     // k per tcgen05.mma for 16-bit inputs
+constexpr int STAGES = 4;
+constexpr int NUM_ACC = 2;     // TMEM accumulators (2 x 256 columns)
+constexpr int TMEM_COLS = 512;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_STAGE_BYTES = BK * BN * 2;   // 32 KB
+constexpr int B_BOX_BYTES = BK * 64 * 2;     // one 64(k) x 64(n) box = 8 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second
+
+struct KernelParams {
+  float *C;
+  const float *bias;
+  unsigned *status;
+  int M, N, K;
+  int tiles_m, tiles_n, num_tiles, group_m;
+  int k_blocks;
+  int epilogue;
+  int accumulate;
+  uint32_t idesc;
+};
+
+// ---- PTX wrappers --------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+  }
+  return true;
+}
+// The status word lives in mapped host memory: a plain store, no atomics.
+__device__ __forceinline__ void report(unsigned *status, unsigned code) {
+  *reinterpret_cast<volatile unsigned *>(status) = code;
+  __threadfence_system();
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride
+// byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ULL << 46;  // version
+  d |= 2ULL << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Tile order: bands of `group_m` row-blocks; inside a band the column-block
+// index moves slowest, so the CTAs in flight share a band of A and a few
+// column-blocks of B through L2.
+__device__ __forceinline__ void tile_coords(int tile, const KernelParams &p, int &mb, int &nb) {
+  const int band_tiles = p.group_m * p.tiles_n;
+  const int band = tile / band_tiles;
+  const int first_m = band * p.group_m;
+  const int rows_in_band = min(p.group_m, p.tiles_m - first_m);
+  const int t = tile - band * band_tiles;
+  nb = t / rows_in_band;
+  mb = first_m + t % rows_in_band;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles need 1024-byte aligned bases
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + NUM_ACC + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 2 * NUM_ACC);
+  uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t *tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t *>(smem_aligned + STAGES * STAGE_BYTES +
+                                            8 * (2 * STAGES + 2 * NUM_ACC));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed = 0;         // stages whose full barrier was armed at least once
+      uint32_t armed_parity = 0;  // phase parity of the latest arming, per stage
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, p, mb, nb);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            report(p.status, kStatusTmaWaitTimeout);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          armed |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          tma_load_2d(a_dst, &tmap_a, kb * BK, mb * BM, full_bar(stage));
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_2d(b_dst + j * B_BOX_BYTES, &tmap_b, nb * BN + j * 64, kb * BK,
+                        full_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // let the loads already in flight land before the CTA can exit
+        for (int s = 0; s < STAGES; ++s)
+          if (armed & (1u << s)) mbar_wait(full_bar(s), (armed_parity >> s) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
+          report(p.status, kStatusMmaWaitTimeout);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            report(p.status, kStatusMmaWaitTimeout);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // A (K-major): 8-row groups 1024 B apart; +32 B per 16 k inside the swizzle row.
+            // B (N-major): 8-k groups 1024 B apart (SBO), 64-column groups one box apart (LBO);
+            //              +2048 B per 16 k.
+            const uint64_t a_desc = make_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = make_smem_desc(b_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+            tcgen05_mma_f16(d_tmem, a_desc, b_desc, p.idesc, (kb | k) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar(stage));  // smem stage reusable once these MMAs finish
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tcgen05_commit(acc_full_bar(acc));  // accumulator ready for the epilogue
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int lane_group = warp & 3;  // TMEM lanes this warp may read: 32*lane_group ..
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, p, mb, nb);
+      bool ok = mbar_wait(acc_full_bar(acc), acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
+        break;
+      }
+      tcgen05_fence_after();
+      const int row = mb * BM + lane_group * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BN;
+      float *c_row = p.C + static_cast<size_t>(row) * p.N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        const int col0 = nb * BN + c0;
+        if (row < p.M && col0 < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int col = col0 + j;
+            if (col < p.N) {  // N % 8 == 0, so a group of 4 is inside or outside as a whole
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.accumulate) {
+                const float4 c = *reinterpret_cast<const float4 *>(c_row + col);
+                v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+              }
+              if (p.bias) {
+                const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+              }
+              v.x = apply_epilogue(v.x, p.epilogue);
+              v.y = apply_epilogue(v.y, p.epilogue);
+              v.z = apply_epilogue(v.z, p.epilogue);
+              v.w = apply_epilogue(v.w, p.epilogue);
+              *reinterpret_cast<float4 *>(c_row + col) = v;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  __syncwarp();  // lanes of the producer / MMA warps rejoin their elected lane
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                              const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return static_cast<EncodeFn>(nullptr);
+    return reinterpret_cast<EncodeFn>(sym);
+  }();
+  return fn;
+}
+
+// 2-D row-major [outer, inner] 16-bit tensor, box [box_outer, 64], 128B swizzle.
+bool make_map(CUtensorMap *m, const void *base, int in_dtype, int64_t inner, int64_t outer,
+              int box_outer) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt =
+      in_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
+} // namespace
+
+bool gemm_tcgen05_supported(const GemmProblem &p) {
+  if (p.in_dtype != kBF16 && p.in_dtype != kF16) return false;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return false;
+  if (p.K % 8 || p.N % 8) return false;  // TMA row pitch must be a multiple of 16 bytes
+  if (p.M > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX) return false;
+  auto al = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  return al(p.A) && al(p.B) && al(p.C) && (!p.bias || al(p.bias));
+}
+
+cudaError_t launch_gemm_tcgen05(const GemmProblem &g, unsigned *status, cudaStream_t stream) {
+  if (!gemm_tcgen05_supported(g)) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+
+  CUtensorMap ta, tb;
+  // cudaErrorNotSupported: the driver refused this shape for a tensor map; the
+  // caller falls back to the SIMT kernel
+  if (!make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM)) return cudaErrorNotSupported;
+  if (!make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK)) return cudaErrorNotSupported;
+
+  KernelParams p;
+  p.C = g.C;
+  p.bias = g.bias;
+  p.status = status;
+  p.M = static_cast<int>(g.M);
+  p.N = static_cast<int>(g.N);
+  p.K = static_cast<int>(g.K);
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.group_m = 16;
+  if (const char *e = getenv("IMEX_GEMM_GROUP_M")) {
+    int v = atoi(e);
+    if (v > 0) p.group_m = v;
+  }
+  p.k_blocks = (p.K + BK - 1) / BK;
+  p.epilogue = g.epilogue;
+  p.accumulate = g.accumulate ? 1 : 0;
+  const uint32_t fmt = g.in_dtype == kBF16 ? 1u : 0u;
+  // instruction descriptor: D f32, A/B format, A K-major, B N-major, N>>3, M>>4
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
+            (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+
+  int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+} // namespace imex

@@ -1,0 +1,79 @@
+// Launchers of the sm_100a kernels behind the GPU runtime-wrapper C ABI.
+// Every launcher enqueues on `stream` and returns the launch status; none
+// allocates.  `status` is a host-mapped error word kernels with bounded
+// waits write to when a wait runs out (0 = fine).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace imex {
+
+enum DType : int { kF32 = 1, kBF16 = 2, kF16 = 3, kI32 = 4 };
+enum Epilogue : int { kEpiNone = 0, kEpiRelu = 1, kEpiSilu = 2 };
+
+// Device status codes written to the status word.
+enum Status : unsigned {
+  kStatusOk = 0,
+  kStatusTmaWaitTimeout = 1,   // producer gave up waiting for a free smem stage
+  kStatusMmaWaitTimeout = 2,   // MMA warp gave up waiting for operands / a free accumulator
+  kStatusEpiWaitTimeout = 3    // epilogue gave up waiting for an accumulator
+};
+
+struct GemmProblem {
+  const void *A;      // [M,K] row-major, in_dtype
+  const void *B;      // [K,N] row-major, in_dtype
+  float *C;           // [M,N] row-major f32
+  const float *bias;  // [N] or nullptr
+  int64_t M, N, K;
+  int in_dtype;       // DType
+  int epilogue;       // Epilogue
+  bool accumulate;    // C is read as the initial value
+};
+
+// f32 or 16-bit inputs, one thread per 4x4 outputs, k ascending with
+// separately rounded multiply and add: bit-identical to the scalar loop nest
+// of linalg-to-loops.  Any shape.
+cudaError_t launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
+
+// bf16/f16 -> f32 on the 5th-gen tensor cores (tcgen05.mma, TMEM
+// accumulators, TMA-fed 128B-swizzled smem ring, persistent tiles).
+// Needs K % 8 == 0, N % 8 == 0 and 16-byte aligned A, B, C.
+bool gemm_tcgen05_supported(const GemmProblem &p);
+cudaError_t launch_gemm_tcgen05(const GemmProblem &p, unsigned *status,
+                                cudaStream_t stream);
+
+// Row softmax over the last dim (one pass over HBM: read X once, write Y once).
+cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols,
+                               bool neg_inf_init, cudaStream_t stream);
+
+// Y[r] = (acc ? Y[r] : 0) + sum_c X[r,c]
+cudaError_t launch_reduce_rows_f32(const float *x, float *y, int64_t rows, int64_t cols,
+                                   bool accumulate, cudaStream_t stream);
+// Y[i] = (acc ? Y[i] : 0) + sum_l X[l,i], l ascending (bit-identical to the loop nest)
+cudaError_t launch_reduce_leading_f32(const float *x, float *y, int64_t lead, int64_t inner,
+                                      bool accumulate, cudaStream_t stream);
+// *Y = (acc ? *Y : 0) + sum X.  `partials` is scratch for reduce_all_partials() floats.
+int64_t reduce_all_partials(int64_t n);
+cudaError_t launch_reduce_all_f32(const float *x, float *y, int64_t n, bool accumulate,
+                                  float *partials, cudaStream_t stream);
+
+// Y[j,i] = X[i,j]; elem_bytes 4 or 2.
+cudaError_t launch_transpose2d(const void *x, void *y, int64_t rows, int64_t cols,
+                               int elem_bytes, cudaStream_t stream);
+// rank-3 permutation of 4-byte elements: Y dims = X dims permuted by perm.
+cudaError_t launch_transpose3d_b32(const void *x, void *y, const int64_t dims[3],
+                                   const int perm[3], cudaStream_t stream);
+
+// Y[i] = epilogue(X[i]) (standalone relu / silu)
+cudaError_t launch_eltwise_f32(const float *x, float *y, int64_t n, int epilogue,
+                               cudaStream_t stream);
+
+// Seeded synthetic inputs.  uniform: lo + (hi-lo)*u24(seed, first+i), the same
+// integer hash as the CPU oracle (bit-identical in f32).  normal: Box-Muller.
+cudaError_t launch_fill_uniform(void *y, int64_t n, int dtype, uint64_t seed, int64_t first,
+                                float lo, float hi, cudaStream_t stream);
+cudaError_t launch_fill_normal(void *y, int64_t n, int dtype, uint64_t seed, int64_t first,
+                               float mean, float stddev, cudaStream_t stream);
+
+} // namespace imex

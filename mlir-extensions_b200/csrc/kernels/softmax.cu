@@ -1,0 +1,153 @@
+// One-pass row softmax over the last dim (f32).
+//
+// The reference lowers softmax to six launches with four full-size
+// temporaries (fill, row max, x-max, exp, fill, row sum, divide:
+// benchmarks/softmax/softmax_gpu.mlir.in:8-42; one work-item per row or per
+// element, test/SPIRV/OpTest.Softmax_FLOAT32.mlir:64-86).  Here a row is read
+// from HBM once with 128-bit loads, kept in registers, and written once:
+// algorithmic traffic = 2 * rows * cols * 4 bytes.
+//
+// Arithmetic per element is the reference's: t = x - max (exact max),
+// e = expf(t), y = e / sum with IEEE division.  Only the order of the adds in
+// `sum` differs from the sequential loop (per-lane partial sums + shuffle
+// tree), which is where the <= 1e-5 relative tolerance goes.
+#include "kernels.h"
+#include <cfloat>
+
+namespace imex {
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// fmaxf drops NaNs where arith.maximumf keeps them; a NaN element still turns
+// the whole row into NaN through exp -> sum -> divide, as in the reference.
+
+// One warp per row, the whole row in registers: cols == 4 * 32 * V exactly or
+// ragged (guarded), cols <= 128 * V.
+template <int V>
+__global__ void __launch_bounds__(256)
+softmax_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int cols,
+                    float max_init) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols);
+  float4 *yr = reinterpret_cast<float4 *>(y + row * cols);
+  const int nvec = cols >> 2;
+
+  float4 v[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    int idx = lane + 32 * i;
+    v[i] = (idx < nvec) ? __ldg(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+  }
+  float m = max_init;
+#pragma unroll
+  for (int i = 0; i < V; ++i) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+  m = warp_max(m);
+
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < nvec) {
+      v[i].x = expf(v[i].x - m);
+      v[i].y = expf(v[i].y - m);
+      v[i].z = expf(v[i].z - m);
+      v[i].w = expf(v[i].w - m);
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  s = warp_sum(s);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < nvec) {
+      float4 o;
+      o.x = __fdiv_rn(v[i].x, s);
+      o.y = __fdiv_rn(v[i].y, s);
+      o.z = __fdiv_rn(v[i].z, s);
+      o.w = __fdiv_rn(v[i].w, s);
+      yr[idx] = o;
+    }
+  }
+}
+
+// Any cols: one block per row, three sweeps over the row (the 2nd and 3rd hit
+// L1/L2).  Used for ragged or very long rows.
+__global__ void __launch_bounds__(256)
+softmax_block_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows,
+                     int64_t cols, float max_init) {
+  __shared__ float red[8];
+  __shared__ float bcast;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float *xr = x + row * cols;
+    float *yr = y + row * cols;
+    float m = max_init;
+    for (int64_t c = tid; c < cols; c += 256) m = fmaxf(m, xr[c]);
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+      float t = red[0];
+      for (int w = 1; w < 8; ++w) t = fmaxf(t, red[w]);
+      bcast = t;
+    }
+    __syncthreads();
+    m = bcast;
+    float s = 0.0f;
+    for (int64_t c = tid; c < cols; c += 256) s += expf(xr[c] - m);
+    s = warp_sum(s);
+    __syncthreads();
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (tid == 0) {
+      float t = red[0];
+      for (int w = 1; w < 8; ++w) t += red[w];
+      bcast = t;
+    }
+    __syncthreads();
+    s = bcast;
+    for (int64_t c = tid; c < cols; c += 256) yr[c] = __fdiv_rn(expf(xr[c] - m), s);
+    __syncthreads();
+  }
+}
+
+template <int V>
+cudaError_t launch_warp(const float *x, float *y, int64_t rows, int cols, float max_init,
+                        cudaStream_t stream) {
+  const int warps = 8;
+  unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  softmax_warp_kernel<V><<<grid, warps * 32, 0, stream>>>(x, y, rows, cols, max_init);
+  return cudaGetLastError();
+}
+
+} // namespace
+
+cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols,
+                               bool neg_inf_init, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  const float max_init = neg_inf_init ? -INFINITY : -FLT_MAX;
+  const bool vec_ok = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+  if (vec_ok && cols <= 128) return launch_warp<1>(x, y, rows, (int)cols, max_init, stream);
+  if (vec_ok && cols <= 256) return launch_warp<2>(x, y, rows, (int)cols, max_init, stream);
+  if (vec_ok && cols <= 512) return launch_warp<4>(x, y, rows, (int)cols, max_init, stream);
+  if (vec_ok && cols <= 1024) return launch_warp<8>(x, y, rows, (int)cols, max_init, stream);
+  if (vec_ok && cols <= 2048) return launch_warp<16>(x, y, rows, (int)cols, max_init, stream);
+  unsigned grid = static_cast<unsigned>(rows < 148 * 16 ? rows : 148 * 16);
+  softmax_block_kernel<<<grid, 256, 0, stream>>>(x, y, rows, cols, max_init);
+  return cudaGetLastError();
+}
+
+} // namespace imex

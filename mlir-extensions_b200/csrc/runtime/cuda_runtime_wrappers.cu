@@ -1,0 +1,641 @@
+// CUDA implementation of the reference's GPU runtime-wrapper C ABI
+// (libimex_cuda_runtime.so).  It takes the place of the Level Zero and SYCL
+// wrapper libraries (lib/ExecutionEngine/LEVELZERORUNTIME/LevelZeroRuntimeWrappers.cpp,
+// lib/ExecutionEngine/SYCLRUNTIME/SyclRuntimeWrappers.cpp): same symbols, same
+// argument meaning, same error convention.  Where those libraries hand a
+// SPIR-V module to the driver's JIT, this one reads a kernel-descriptor blob
+// (include/imex_b200_blob.h) and dispatches each recognised op to a
+// hand-written sm_100a kernel.  There is no CPU fallback: an op or blob it
+// does not know is an error.
+#include "../../../include/imex_b200_blob.h"
+#include "../../../include/imex_cuda_runtime.h"
+#include "../kernels/kernels.h"
+#include "stats.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+// Error convention of the reference (LevelZeroRuntimeWrappers.cpp:41-53).
+template <typename F> auto catchAll(F &&func) {
+  try {
+    return func();
+  } catch (const std::exception &e) {
+    fprintf(stdout, "An exception was thrown: %s\n", e.what());
+    fflush(stdout);
+    abort();
+  } catch (...) {
+    fprintf(stdout, "An unknown exception was thrown\n");
+    fflush(stdout);
+    abort();
+  }
+}
+
+void check(cudaError_t e, const char *what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string(what) + " failed: " + cudaGetErrorString(e));
+}
+#define CHECK_CUDA(expr) check((expr), #expr)
+
+struct Allocation {
+  size_t size;
+  bool managed;
+  int device;
+};
+
+struct Stream {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool owned = true;
+  unsigned *status_host = nullptr;  // mapped, written by kernels whose bounded waits run out
+  unsigned *status_dev = nullptr;
+  float *scratch = nullptr;  // reduce-all partials
+  size_t scratch_bytes = 0;
+  const char *last_kernel = "";
+};
+
+struct Module {
+  std::vector<ImexKernelDesc> kernels;
+};
+
+struct Kernel {
+  ImexKernelDesc desc;
+};
+
+struct Event {
+  cudaEvent_t ev = nullptr;
+};
+
+std::mutex g_mutex;
+std::map<const void *, std::unique_ptr<Module>> g_modules;  // keyed by blob address, lives to exit
+std::unordered_map<void *, Allocation> g_allocs;
+std::atomic<uint64_t> g_launches{0};
+
+const char *op_name(uint32_t op) {
+  switch (op) {
+  case IMEX_OP_GEMM: return "gemm";
+  case IMEX_OP_SOFTMAX: return "softmax";
+  case IMEX_OP_REDUCE_ROWS: return "reduce_rows";
+  case IMEX_OP_REDUCE_LEADING: return "reduce_leading";
+  case IMEX_OP_REDUCE_ALL: return "reduce_all";
+  case IMEX_OP_TRANSPOSE2D: return "transpose2d";
+  case IMEX_OP_TRANSPOSE3D: return "transpose3d";
+  case IMEX_OP_ELTWISE: return "eltwise";
+  case IMEX_OP_FILL_UNIFORM: return "fill_uniform";
+  case IMEX_OP_FILL_NORMAL: return "fill_normal";
+  }
+  return nullptr;
+}
+
+size_t dtype_bytes(uint32_t dt) {
+  switch (dt) {
+  case IMEX_F32: case IMEX_I32: return 4;
+  case IMEX_BF16: case IMEX_F16: return 2;
+  }
+  throw std::runtime_error("unknown element type " + std::to_string(dt));
+}
+
+Stream *make_stream(const int32_t *device, cudaStream_t adopt) {
+  auto s = std::make_unique<Stream>();
+  if (device) {
+    s->device = *device;
+    CHECK_CUDA(cudaSetDevice(s->device));
+  } else {
+    CHECK_CUDA(cudaGetDevice(&s->device));
+  }
+  if (adopt) {
+    s->stream = adopt;
+    s->owned = false;
+  } else {
+    CHECK_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+  }
+  CHECK_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&s->status_host), sizeof(unsigned),
+                           cudaHostAllocMapped));
+  *s->status_host = 0;
+  CHECK_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&s->status_dev), s->status_host, 0));
+  return s.release();
+}
+
+void destroy_stream(Stream *s) {
+  if (!s) return;
+  if (s->scratch) cudaFree(s->scratch);
+  if (s->status_host) cudaFreeHost(s->status_host);
+  if (s->owned && s->stream) CHECK_CUDA(cudaStreamDestroy(s->stream));
+  delete s;
+}
+
+void *alloc_memory(Stream *s, size_t size, size_t /*alignment*/, bool shared) {
+  void *p = nullptr;
+  const size_t bytes = size ? size : 1;
+  if (s) CHECK_CUDA(cudaSetDevice(s->device));
+  if (getenv("IMEX_B200_FAIL_ALLOC"))  // host-side fault injection for tests
+    throw std::runtime_error("gpuMemAlloc failed: injected allocation failure");
+  if (shared)
+    CHECK_CUDA(cudaMallocManaged(&p, bytes));
+  else
+    CHECK_CUDA(cudaMalloc(&p, bytes));
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_allocs[p] = Allocation{size, shared, dev};
+  return p;
+}
+
+void free_memory(void *p) {
+  if (!p) return;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_allocs.erase(p);
+  }
+  CHECK_CUDA(cudaFree(p));
+}
+
+Module *load_module(const void *data, size_t size) {
+  if (!data) throw std::runtime_error("gpuModuleLoad: null blob");
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_modules.find(data);
+    if (it != g_modules.end()) return it->second.get();
+  }
+  if (size < sizeof(ImexBlobHeader)) throw std::runtime_error("gpuModuleLoad: blob too small");
+  ImexBlobHeader h;
+  memcpy(&h, data, sizeof h);
+  if (h.magic != IMEX_BLOB_MAGIC) {
+    uint32_t w;
+    memcpy(&w, data, 4);
+    if (w == 0x07230203u)
+      throw std::runtime_error("gpuModuleLoad: blob is a SPIR-V module; this runtime loads "
+                               "IMEX B200 kernel-descriptor blobs only");
+    throw std::runtime_error("gpuModuleLoad: bad blob magic");
+  }
+  if (h.version != IMEX_BLOB_VERSION)
+    throw std::runtime_error("gpuModuleLoad: unsupported blob version " + std::to_string(h.version));
+  if (size < sizeof h + static_cast<size_t>(h.num_kernels) * sizeof(ImexKernelDesc))
+    throw std::runtime_error("gpuModuleLoad: blob truncated");
+  auto m = std::make_unique<Module>();
+  m->kernels.resize(h.num_kernels);
+  memcpy(m->kernels.data(), static_cast<const char *>(data) + sizeof h,
+         h.num_kernels * sizeof(ImexKernelDesc));
+  for (auto &k : m->kernels) {
+    k.name[IMEX_KERNEL_NAME_MAX - 1] = 0;
+    if (!op_name(k.op))
+      throw std::runtime_error(std::string("gpuModuleLoad: kernel '") + k.name +
+                               "' names an unknown op " + std::to_string(k.op));
+  }
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto &slot = g_modules[data];
+  if (!slot) slot = std::move(m);
+  return slot.get();
+}
+
+Kernel *get_kernel(Module *m, const char *name) {
+  if (!m || !name) throw std::runtime_error("gpuKernelGet: null module or name");
+  for (auto &k : m->kernels)
+    if (strncmp(k.name, name, IMEX_KERNEL_NAME_MAX) == 0) {
+      auto *out = new Kernel;  // never released, like the reference's kernel handles
+      out->desc = k;
+      return out;
+    }
+  throw std::runtime_error(std::string("gpuKernelGet: no kernel named '") + name + "' in module");
+}
+
+template <typename T> size_t countUntilNull(T *p, bool (*isEnd)(const T &)) {
+  size_t n = 0;
+  while (!isEnd(p[n])) ++n;
+  return n;
+}
+
+void prefetch_managed(Stream *s, void *ptr) {
+  Allocation a;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_allocs.find(ptr);
+    if (it == g_allocs.end() || !it->second.managed) return;
+    a = it->second;
+  }
+  // host code filled this buffer; move it before the kernel touches it so the
+  // launch does not run at page-fault speed
+#if CUDART_VERSION >= 13000
+  cudaMemLocation loc;
+  loc.type = cudaMemLocationTypeDevice;
+  loc.id = s->device;
+  cudaMemPrefetchAsync(ptr, a.size, loc, 0, s->stream);
+#else
+  cudaMemPrefetchAsync(ptr, a.size, s->device, s->stream);
+#endif
+}
+
+void ensure_scratch(Stream *s, size_t bytes) {
+  if (s->scratch_bytes >= bytes) return;
+  if (s->scratch) {
+    CHECK_CUDA(cudaStreamSynchronize(s->stream));
+    CHECK_CUDA(cudaFree(s->scratch));
+  }
+  size_t cap = bytes < (1u << 20) ? (1u << 20) : bytes;
+  CHECK_CUDA(cudaMalloc(reinterpret_cast<void **>(&s->scratch), cap));
+  s->scratch_bytes = cap;
+}
+
+// One enqueue of the op a kernel handle stands for.
+void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
+  auto need = [&](size_t n) {
+    if (nptrs < n)
+      throw std::runtime_error(std::string("gpuLaunchKernel: '") + d.name + "' (" + op_name(d.op) +
+                               ") needs " + std::to_string(n) + " pointer arguments, got " +
+                               std::to_string(nptrs));
+  };
+  const bool acc = d.flags & IMEX_FLAG_ACCUMULATE;
+  cudaError_t err = cudaSuccess;
+  int launches = 1;
+  switch (d.op) {
+  case IMEX_OP_GEMM: {
+    const bool has_bias = d.flags & IMEX_FLAG_BIAS;
+    need(has_bias ? 4 : 3);
+    if (d.out_dtype != IMEX_F32)
+      throw std::runtime_error("gpuLaunchKernel: gemm output must be f32");
+    imex::GemmProblem g;
+    g.A = ptrs[0];
+    g.B = ptrs[1];
+    g.C = static_cast<float *>(ptrs[2]);
+    g.bias = has_bias ? static_cast<const float *>(ptrs[3]) : nullptr;
+    g.M = d.dims[0];
+    g.N = d.dims[1];
+    g.K = d.dims[2];
+    g.in_dtype = static_cast<int>(d.in_dtype);
+    g.epilogue = static_cast<int>(d.epilogue);
+    g.accumulate = acc;
+    if (g.M < 0 || g.N < 0 || g.K < 0) throw std::runtime_error("gpuLaunchKernel: negative gemm dims");
+    const bool force_simt = getenv("IMEX_B200_FORCE_SIMT_GEMM") != nullptr;
+    bool done = false;
+    if (!force_simt && imex::gemm_tcgen05_supported(g)) {
+      s->last_kernel = "gemm_tcgen05";
+      err = imex::launch_gemm_tcgen05(g, s->status_dev, s->stream);
+      done = err != cudaErrorNotSupported;
+    }
+    if (done) {
+    } else if (d.in_dtype == IMEX_F32 || d.in_dtype == IMEX_BF16 || d.in_dtype == IMEX_F16) {
+      s->last_kernel = "gemm_simt";
+      err = imex::launch_gemm_simt(g, s->stream);
+    } else {
+      throw std::runtime_error("gpuLaunchKernel: gemm input type not supported");
+    }
+    break;
+  }
+  case IMEX_OP_SOFTMAX:
+    need(2);
+    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: softmax is f32 only");
+    s->last_kernel = "softmax";
+    err = imex::launch_softmax_f32(static_cast<const float *>(ptrs[0]), static_cast<float *>(ptrs[1]),
+                                   d.dims[0], d.dims[1], d.flags & IMEX_FLAG_SOFTMAX_NEG_INF,
+                                   s->stream);
+    break;
+  case IMEX_OP_REDUCE_ROWS:
+    need(2);
+    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: reduce is f32 only");
+    s->last_kernel = "reduce_rows";
+    err = imex::launch_reduce_rows_f32(static_cast<const float *>(ptrs[0]),
+                                       static_cast<float *>(ptrs[1]), d.dims[0], d.dims[1], acc,
+                                       s->stream);
+    break;
+  case IMEX_OP_REDUCE_LEADING:
+    need(2);
+    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: reduce is f32 only");
+    s->last_kernel = "reduce_leading";
+    err = imex::launch_reduce_leading_f32(static_cast<const float *>(ptrs[0]),
+                                          static_cast<float *>(ptrs[1]), d.dims[0], d.dims[1], acc,
+                                          s->stream);
+    break;
+  case IMEX_OP_REDUCE_ALL: {
+    need(2);
+    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: reduce is f32 only");
+    ensure_scratch(s, static_cast<size_t>(imex::reduce_all_partials(d.dims[0])) * sizeof(float));
+    s->last_kernel = "reduce_all";
+    launches = 2;
+    err = imex::launch_reduce_all_f32(static_cast<const float *>(ptrs[0]),
+                                      static_cast<float *>(ptrs[1]), d.dims[0], acc, s->scratch,
+                                      s->stream);
+    break;
+  }
+  case IMEX_OP_TRANSPOSE2D:
+    need(2);
+    s->last_kernel = "transpose2d";
+    err = imex::launch_transpose2d(ptrs[0], ptrs[1], d.dims[0], d.dims[1],
+                                   static_cast<int>(dtype_bytes(d.in_dtype)), s->stream);
+    break;
+  case IMEX_OP_TRANSPOSE3D: {
+    need(2);
+    if (dtype_bytes(d.in_dtype) != 4)
+      throw std::runtime_error("gpuLaunchKernel: transpose3d takes 4-byte elements");
+    const int64_t dims[3] = {d.dims[0], d.dims[1], d.dims[2]};
+    const int perm[3] = {static_cast<int>(d.dims[3]), static_cast<int>(d.dims[4]),
+                         static_cast<int>(d.dims[5])};
+    int seen = 0;
+    for (int q : perm) {
+      if (q < 0 || q > 2) throw std::runtime_error("gpuLaunchKernel: bad transpose3d permutation");
+      seen |= 1 << q;
+    }
+    if (seen != 7) throw std::runtime_error("gpuLaunchKernel: bad transpose3d permutation");
+    s->last_kernel = "transpose3d";
+    err = imex::launch_transpose3d_b32(ptrs[0], ptrs[1], dims, perm, s->stream);
+    break;
+  }
+  case IMEX_OP_ELTWISE:
+    need(2);
+    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: eltwise is f32 only");
+    s->last_kernel = "eltwise";
+    err = imex::launch_eltwise_f32(static_cast<const float *>(ptrs[0]), static_cast<float *>(ptrs[1]),
+                                   d.dims[0], static_cast<int>(d.epilogue), s->stream);
+    break;
+  case IMEX_OP_FILL_UNIFORM:
+    need(1);
+    s->last_kernel = "fill_uniform";
+    err = imex::launch_fill_uniform(ptrs[0], d.dims[0], static_cast<int>(d.out_dtype),
+                                    static_cast<uint64_t>(d.dims[1]), d.dims[2], d.fparams[0],
+                                    d.fparams[1], s->stream);
+    break;
+  case IMEX_OP_FILL_NORMAL:
+    need(1);
+    s->last_kernel = "fill_normal";
+    err = imex::launch_fill_normal(ptrs[0], d.dims[0], static_cast<int>(d.out_dtype),
+                                   static_cast<uint64_t>(d.dims[1]), d.dims[2], d.fparams[0],
+                                   d.fparams[1], s->stream);
+    break;
+  default:
+    throw std::runtime_error("gpuLaunchKernel: unknown op");
+  }
+  check(err, (std::string("launch of ") + op_name(d.op)).c_str());
+  g_launches.fetch_add(launches, std::memory_order_relaxed);
+}
+
+void check_status(Stream *s) {
+  unsigned st = *reinterpret_cast<volatile unsigned *>(s->status_host);
+  if (st != 0) {
+    *s->status_host = 0;
+    throw std::runtime_error("device kernel reported status " + std::to_string(st) +
+                             " (a bounded wait ran out)");
+  }
+}
+
+// The reference's profiling loop (LevelZeroRuntimeWrappers.cpp:521-597): warm-ups,
+// then `rounds` timed launches, optionally flushing the last-level cache before
+// each by writing a buffer twice its size; one statistics line on stdout.
+void profile(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
+  long rounds = 1000, warmups = 3;
+  if (const char *e = getenv("IMEX_PROFILING_RUNS")) {
+    long v = strtol(e, nullptr, 10);
+    if (v) rounds = v;
+  }
+  if (const char *e = getenv("IMEX_PROFILING_WARMUPS")) {
+    long v = strtol(e, nullptr, 10);
+    if (v >= 0) warmups = v;
+  }
+  const bool flush = getenv("IMEX_ENABLE_CACHE_FLUSHING") != nullptr;
+  void *cache = nullptr;
+  size_t cache_bytes = 0;
+  if (flush) {
+    int l2 = 0;
+    CHECK_CUDA(cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, s->device));
+    cache_bytes = 2 * static_cast<size_t>(l2);
+    CHECK_CUDA(cudaMalloc(&cache, cache_bytes));
+  }
+  for (long r = 0; r < warmups; ++r) enqueue(s, d, ptrs, nptrs);
+  cudaEvent_t e0, e1;
+  CHECK_CUDA(cudaEventCreate(&e0));
+  CHECK_CUDA(cudaEventCreate(&e1));
+  std::vector<float> ms(static_cast<size_t>(rounds), 0.0f);
+  for (long r = 0; r < rounds; ++r) {
+    if (flush) CHECK_CUDA(cudaMemsetAsync(cache, 0, cache_bytes, s->stream));
+    CHECK_CUDA(cudaEventRecord(e0, s->stream));
+    enqueue(s, d, ptrs, nptrs);
+    CHECK_CUDA(cudaEventRecord(e1, s->stream));
+    CHECK_CUDA(cudaEventSynchronize(e1));
+    CHECK_CUDA(cudaEventElapsedTime(&ms[static_cast<size_t>(r)], e0, e1));
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (cache) CHECK_CUDA(cudaFree(cache));
+  fprintf(stdout,
+          "the kernel execution time is (ms, on CUDA runtime):"
+          "avg: %.4f, min: %.4f, max: %.4f, median: %4f, std_deviation: %4f, "
+          "variance: %4f, P95: %4f, P5: %4f, median_one_third_avg: %4f (over "
+          "%ld runs)\n",
+          imex::calculateAverage(ms), imex::calculateMin(ms), imex::calculateMax(ms),
+          imex::calculateMedian(ms), imex::calculateStdDev(ms), imex::calculateVariance(ms),
+          imex::calculateP95(ms), imex::calculateP5(ms), imex::calculateMiddleThirdAverage(ms),
+          rounds);
+  fflush(stdout);
+}
+
+Event *launch(Stream *s, Kernel *k, size_t sharedMemBytes, ImexParamDesc *params,
+              ImexEventDesc *deps) {
+  if (!s || !k) throw std::runtime_error("gpuLaunchKernel: null stream or kernel");
+  CHECK_CUDA(cudaSetDevice(s->device));
+  size_t nparams = 0;
+  if (params)
+    while (!(params[nparams].data == nullptr && params[nparams].size == 0)) ++nparams;
+  // the caller passes an i32; the last param is the local-memory placeholder then
+  if ((sharedMemBytes & 0xFFFFFFFFu) != 0 && nparams > 0) --nparams;
+  std::vector<void *> ptrs;
+  for (size_t i = 0; i < nparams; ++i) {
+    if (params[i].size == sizeof(void *) && params[i].data) {
+      void *v;
+      memcpy(&v, params[i].data, sizeof v);
+      ptrs.push_back(v);
+    }
+  }
+  // Pointer arguments come first in every op; the scalars the lowering appends
+  // for loop bounds have pointer size too, so only the leading ones are used.
+  if (deps)
+    for (size_t i = 0; deps[i].event; ++i)
+      CHECK_CUDA(cudaStreamWaitEvent(s->stream, static_cast<Event *>(deps[i].event)->ev, 0));
+  for (void *p : ptrs) prefetch_managed(s, p);
+  if (getenv("IMEX_ENABLE_PROFILING")) profile(s, k->desc, ptrs.data(), ptrs.size());
+  enqueue(s, k->desc, ptrs.data(), ptrs.size());
+  auto *ev = new Event;  // never released by the caller, as in the reference
+  CHECK_CUDA(cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming));
+  CHECK_CUDA(cudaEventRecord(ev->ev, s->stream));
+  return ev;
+}
+
+thread_local Stream *t_default_stream = nullptr;
+Stream *default_stream() {
+  if (!t_default_stream) t_default_stream = make_stream(nullptr, nullptr);
+  return t_default_stream;
+}
+
+} // namespace
+
+extern "C" {
+
+void *gpuCreateStream(void *device, void *context) {
+  return catchAll([&]() -> void * {
+    return make_stream(static_cast<const int32_t *>(device), static_cast<cudaStream_t>(context));
+  });
+}
+
+void gpuStreamDestroy(void *stream) {
+  catchAll([&]() { destroy_stream(static_cast<Stream *>(stream)); });
+}
+
+void *gpuMemAlloc(void *stream, size_t size, size_t alignment, bool isShared) {
+  return catchAll(
+      [&]() { return alloc_memory(static_cast<Stream *>(stream), size, alignment, isShared); });
+}
+
+void gpuMemFree(void *stream, void *ptr) {
+  (void)stream;
+  catchAll([&]() { free_memory(ptr); });
+}
+
+void gpuMemCopy(void *stream, void *dst, void *src, size_t size) {
+  catchAll([&]() {
+    auto *s = static_cast<Stream *>(stream);
+    if (!size) return;
+    if (s) {
+      CHECK_CUDA(cudaSetDevice(s->device));
+      CHECK_CUDA(cudaMemcpyAsync(dst, src, size, cudaMemcpyDefault, s->stream));
+      CHECK_CUDA(cudaStreamSynchronize(s->stream));
+    } else {
+      CHECK_CUDA(cudaMemcpy(dst, src, size, cudaMemcpyDefault));
+    }
+  });
+}
+
+void gpuMemcpy(void *stream, void *dst, void *src, size_t size) {
+  gpuMemCopy(stream, dst, src, size);
+}
+
+void *gpuModuleLoad(void *stream, const void *data, size_t dataSize) {
+  (void)stream;
+  return catchAll([&]() -> void * { return load_module(data, dataSize); });
+}
+
+void *gpuKernelGet(void *stream, void *module, const char *name) {
+  (void)stream;
+  return catchAll([&]() -> void * { return get_kernel(static_cast<Module *>(module), name); });
+}
+
+void *gpuLaunchKernel(void *stream, void *kernel, size_t gridX, size_t gridY, size_t gridZ,
+                      size_t blockX, size_t blockY, size_t blockZ, size_t sharedMemBytes,
+                      void *params, void *depEvents) {
+  (void)gridX; (void)gridY; (void)gridZ; (void)blockX; (void)blockY; (void)blockZ;
+  return catchAll([&]() -> void * {
+    return launch(static_cast<Stream *>(stream), static_cast<Kernel *>(kernel), sharedMemBytes,
+                  static_cast<ImexParamDesc *>(params), static_cast<ImexEventDesc *>(depEvents));
+  });
+}
+
+void gpuWait(void *stream) {
+  catchAll([&]() {
+    auto *s = static_cast<Stream *>(stream);
+    if (!s) throw std::runtime_error("gpuWait: null stream");
+    CHECK_CUDA(cudaStreamSynchronize(s->stream));
+    check_status(s);
+  });
+}
+
+void gpuModuleUnload(void *module) { (void)module; /* modules are cached until exit */ }
+
+// ---- upstream-style wrappers (LevelZeroRuntimeWrappers.cpp:673-741) --------
+void *mgpuStreamCreate(void) {
+  return catchAll([&]() -> void * { return make_stream(nullptr, nullptr); });
+}
+void mgpuStreamSynchronize(void *stream) { gpuWait(stream); }
+void mgpuStreamDestroy(void *stream) { gpuStreamDestroy(stream); }
+void *mgpuMemAlloc(size_t size, void *stream, bool isShared) {
+  return catchAll([&]() {
+    Stream *s = stream ? static_cast<Stream *>(stream) : default_stream();
+    return alloc_memory(s, size, 64, isShared);
+  });
+}
+void mgpuMemFree(void *stream, void *ptr) { gpuMemFree(stream, ptr); }
+void *mgpuModuleLoad(const void *data, size_t dataSize) {
+  return gpuModuleLoad(nullptr, data, dataSize);
+}
+void *mgpuModuleGetFunction(void *module, const char *name) {
+  return gpuKernelGet(nullptr, module, name);
+}
+void mgpuModuleUnload(void *module) { (void)module; }
+void mgpuLaunchKernel(void *kernel, size_t gridX, size_t gridY, size_t gridZ, size_t blockX,
+                      size_t blockY, size_t blockZ, size_t sharedMemBytes, void *stream,
+                      void **params, void **extra, size_t paramsCount) {
+  (void)gridX; (void)gridY; (void)gridZ; (void)blockX; (void)blockY; (void)blockZ; (void)extra;
+  catchAll([&]() {
+    // every param is a pointer to a pointer-sized slot (LevelZeroRuntimeWrappers.cpp:697-699)
+    std::vector<ImexParamDesc> descs(paramsCount + 1);
+    for (size_t i = 0; i < paramsCount; ++i) descs[i] = ImexParamDesc{params[i], sizeof(void *)};
+    descs[paramsCount] = ImexParamDesc{nullptr, 0};
+    Stream *s = stream ? static_cast<Stream *>(stream) : default_stream();
+    launch(s, static_cast<Kernel *>(kernel), sharedMemBytes, descs.data(), nullptr);
+  });
+}
+
+// ---- additions ---------------------------------------------------------------
+void *imexStreamNative(void *stream) {
+  return stream ? static_cast<void *>(static_cast<Stream *>(stream)->stream) : nullptr;
+}
+
+void *imexEventRecord(void *stream) {
+  return catchAll([&]() -> void * {
+    auto *s = static_cast<Stream *>(stream);
+    if (!s) throw std::runtime_error("imexEventRecord: null stream");
+    auto *ev = new Event;
+    CHECK_CUDA(cudaEventCreate(&ev->ev));
+    CHECK_CUDA(cudaEventRecord(ev->ev, s->stream));
+    return ev;
+  });
+}
+
+float imexEventElapsedMs(void *startEvent, void *stopEvent) {
+  return catchAll([&]() {
+    auto *a = static_cast<Event *>(startEvent);
+    auto *b = static_cast<Event *>(stopEvent);
+    CHECK_CUDA(cudaEventSynchronize(b->ev));
+    float ms = 0.f;
+    CHECK_CUDA(cudaEventElapsedTime(&ms, a->ev, b->ev));
+    return ms;
+  });
+}
+
+uint64_t imexLaunchCount(void) { return g_launches.load(); }
+
+const char *imexLastKernelName(void *stream) {
+  return stream ? static_cast<Stream *>(stream)->last_kernel : "";
+}
+
+int64_t imexShardSize(int64_t shard, int64_t numShards, int64_t extent) {
+  return extent / numShards + (shard >= numShards - (extent % numShards) ? 1 : 0);
+}
+
+int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent) {
+  int64_t extra = shard - (numShards - (extent % numShards));
+  return shard * (extent / numShards) + (extra > 0 ? extra : 0);
+}
+
+float imexStat(int which, const float *values, size_t n) {
+  std::vector<float> v(values, values + n);
+  switch (which) {
+  case 0: return imex::calculateAverage(v);
+  case 1: return imex::calculateMin(v);
+  case 2: return imex::calculateMax(v);
+  case 3: return imex::calculateMedian(v);
+  case 4: return imex::calculateStdDev(v);
+  case 5: return imex::calculateVariance(v);
+  case 6: return imex::calculateP95(v);
+  case 7: return imex::calculateP5(v);
+  case 8: return imex::calculateMiddleThirdAverage(v);
+  }
+  return -1.0f;
+}
+
+} // extern "C"

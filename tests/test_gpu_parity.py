@@ -1,0 +1,438 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Every test drives libimex_cuda_runtime.so with the call sequence the
+reference's lowered host code uses (gpuCreateStream ... gpuLaunchKernel ...
+gpuWait) and compares with oracle/ on the same seeded inputs.  Tolerances are
+the ones the task states: bit-exact for transpose, f32 matmul and the seeded
+fill; max relative error <= 1e-5 for softmax / reduce; relative Frobenius
+error <= 1e-3 for the 16-bit GEMM.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from __graft_entry__ import load_package
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SOFTMAX_REDUCE_TOL = 1e-5
+GEMM_FROB_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    return load_package()
+
+
+@pytest.fixture()
+def sess(pkg):
+    s = pkg.Session(device=0)
+    yield s
+    s.close()
+
+
+def _gemm(pkg, sess, A, Bm, in_dtype, epilogue=0, C_init=None, bias=None, name="k"):
+    B = pkg.blob
+    M, K = A.shape
+    _, N = Bm.shape
+    dA, dB = sess.upload(A), sess.upload(Bm)
+    if C_init is not None:
+        dC = sess.upload(C_init)
+    else:
+        dC = sess.upload(np.full((M, N), np.nan, np.float32))  # poison: must be overwritten
+    args = [dA, dB, dC]
+    if bias is not None:
+        args.append(sess.upload(bias))
+    sess.run(B.gemm(name, M, N, K, in_dtype, epilogue, accumulate=C_init is not None,
+                    bias=bias is not None), args)
+    return sess.download(dC, (M, N), np.float32)
+
+
+def _oracle_gemm(A, Bm, kind, epilogue=0, C_init=None, bias=None):
+    if kind == "f32":
+        c = oracle.matmul_f32(A, Bm, C_init)
+    else:
+        c = oracle.matmul_x16_f32(A, Bm, kind == "bf16", C_init)
+    if bias is not None:
+        c = oracle.bias_add(c, bias)
+    return oracle.epilogue(c, epilogue)
+
+
+# ---------------------------------------------------------------- f32 matmul
+def test_config1_matmul_f32_256x512x256_bit_exact(pkg, sess):
+    A = oracle.fill_uniform((256, 512), 1, -1.0, 1.0)
+    Bm = oracle.fill_uniform((512, 256), 101, -1.0, 1.0)
+    got = _gemm(pkg, sess, A, Bm, pkg.blob.F32)
+    ref = oracle.matmul_f32(A, Bm)
+    assert sess.last_kernel() == "gemm_simt"
+    assert oracle.max_rel_err(got, ref) <= 1e-4
+    assert got.tobytes() == ref.tobytes()  # same order, same roundings: identical bits
+
+
+@pytest.mark.parametrize("shape", [(5, 2, 3), (1, 1, 1), (65, 67, 17), (64, 64, 16), (130, 70, 33),
+                                   (3, 200, 1), (8, 32, 16)])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_matmul_f32_shapes_epilogues(pkg, sess, shape, epi):
+    M, N, K = shape
+    rng = np.random.default_rng(M * 1000 + N * 10 + K)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    Bm = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    got = _gemm(pkg, sess, A, Bm, pkg.blob.F32, epi, C0, bias)
+    ref = _oracle_gemm(A, Bm, "f32", epi, C0, bias)
+    if epi == 2:  # silu goes through expf: CUDA's and glibc's differ in the last ulps
+        assert oracle.max_rel_err(got, ref, 1e-30) <= 1e-5
+    else:
+        assert got.tobytes() == ref.tobytes()
+
+
+def test_matmul_empty_k_gives_init(pkg, sess):
+    A = np.zeros((4, 0), np.float32)
+    Bm = np.zeros((0, 8), np.float32)
+    got = _gemm(pkg, sess, A, Bm, pkg.blob.F32)
+    assert np.array_equal(got, np.zeros((4, 8), np.float32))
+
+
+# ---------------------------------------------------------------- golden vectors
+with open(os.path.join(HERE, "golden", "reference_vectors.json")) as f:
+    GOLDEN = {c["name"]: c for c in json.load(f)["cases"]}
+
+
+def _arr(inp):
+    dt = np.int32 if inp["dtype"].startswith("i") else np.float32
+    return np.array(inp["data"], dt).reshape(inp["dims"])
+
+
+def _p6(v):
+    return float("%.6g" % float(v))
+
+
+def test_golden_matmul_and_gemm(pkg, sess):
+    c = GOLDEN["matmul_5x3x2_f32"]
+    got = _gemm(pkg, sess, _arr(c["inputs"][0]), _arr(c["inputs"][1]), pkg.blob.F32)
+    assert got.reshape(-1).tolist() == c["expected"]
+    c = GOLDEN["gemm_3x3_f32_cinit"]
+    ins = [_arr(i) for i in c["inputs"]]
+    got = _gemm(pkg, sess, ins[0], ins[1], pkg.blob.F32, C_init=ins[2])
+    assert [_p6(v) for v in got.reshape(-1)] == c["expected"]
+    c = GOLDEN["dot_8x16x32_f32"]
+    got = _gemm(pkg, sess, _arr(c["inputs"][0]), _arr(c["inputs"][1]), pkg.blob.F32)
+    assert got[0].tolist() == c["expected"]
+    c = GOLDEN["gemm_3x3_bf16_accf32"]
+    ins = [_arr(i) for i in c["inputs"]]
+    got = _gemm(pkg, sess, oracle.to_bf16_bits(ins[0]), oracle.to_bf16_bits(ins[1]), pkg.blob.BF16,
+                C_init=ins[2])
+    assert oracle.allclose(got, np.array(c["expected"], np.float32))
+    c = GOLDEN["dot_f16_accf32_8x16x32"]
+    got = _gemm(pkg, sess, oracle.to_f16_bits(_arr(c["inputs"][0])),
+                oracle.to_f16_bits(_arr(c["inputs"][1])), pkg.blob.F16)
+    assert np.all(got == c["expected"][0])
+
+
+def test_golden_softmax_sum_transpose_relu(pkg, sess):
+    B = pkg.blob
+    c = GOLDEN["softmax_10x20_f32"]
+    X = _arr(c["inputs"][0])
+    dX, dY = sess.upload(X), sess.alloc(X.nbytes)
+    sess.run(B.softmax("sm", 10, 20, neg_inf_init=True), [dX, dY])
+    got = sess.download(dY, X.shape, np.float32)
+    assert np.allclose([_p6(v) for v in got.reshape(-1)], c["expected"], rtol=2e-6, atol=0)
+
+    c = GOLDEN["sum_10x20_f32"]
+    X = _arr(c["inputs"][0])
+    dX, dY = sess.upload(X), sess.alloc(4)
+    sess.run(B.reduce_all("sum", X.size), [dX, dY])
+    assert sess.download(dY, (1,), np.float32).tolist() == c["expected"]
+
+    for name in ("transpose_10x20_f32", "swapaxes_2x1_i32"):
+        c = GOLDEN[name]
+        X = _arr(c["inputs"][0])
+        dX, dY = sess.upload(X), sess.alloc(X.nbytes)
+        sess.run(B.transpose2d("tr", X.shape[0], X.shape[1]), [dX, dY])
+        got = sess.download(dY, X.shape[::-1], X.dtype)
+        assert got.reshape(-1).astype(np.float64).tolist() == c["expected"]
+
+    c = GOLDEN["relu_4x5_f32"]
+    X = _arr(c["inputs"][0])
+    dX, dY = sess.upload(X), sess.alloc(X.nbytes)
+    sess.run(B.eltwise("relu", X.size, B.EPI_RELU), [dX, dY])
+    assert [_p6(v) for v in sess.download(dY, (X.size,), np.float32)] == c["expected"]
+
+
+# ---------------------------------------------------------------- 16-bit GEMM (tcgen05)
+@pytest.mark.parametrize("kind", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 256), (256, 512, 256),
+                                   (384, 768, 128), (200, 264, 72), (1000, 1000, 1000),
+                                   (8, 8, 8), (4096, 256, 64), (129, 2056, 2048)])
+def test_gemm_tcgen05_shapes(pkg, sess, kind, shape):
+    M, N, K = shape
+    A = oracle.fill_uniform((M, K), 3, -1.0, 1.0)
+    Bm = oracle.fill_uniform((K, N), 4, -1.0, 1.0)
+    conv = oracle.to_bf16_bits if kind == "bf16" else oracle.to_f16_bits
+    Ab, Bb = conv(A), conv(Bm)
+    dt = pkg.blob.BF16 if kind == "bf16" else pkg.blob.F16
+    got = _gemm(pkg, sess, Ab, Bb, dt)
+    assert sess.last_kernel() == "gemm_tcgen05"
+    ref = oracle.matmul_x16_f32(Ab, Bb, kind == "bf16")
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= GEMM_FROB_TOL
+    assert oracle.allclose(got, ref)
+
+
+@pytest.mark.parametrize("epi", [1, 2])
+def test_gemm_tcgen05_epilogues_bias_accumulate(pkg, sess, epi):
+    M, N, K = 300, 520, 200
+    rng = np.random.default_rng(11)
+    Ab = oracle.to_bf16_bits(rng.normal(0, 0.5, (M, K)).astype(np.float32))
+    Bb = oracle.to_bf16_bits(rng.normal(0, 0.5, (K, N)).astype(np.float32))
+    C0 = rng.normal(0, 1, (M, N)).astype(np.float32)
+    bias = rng.normal(0, 1, N).astype(np.float32)
+    got = _gemm(pkg, sess, Ab, Bb, pkg.blob.BF16, epi, C0, bias)
+    assert sess.last_kernel() == "gemm_tcgen05"
+    ref = _oracle_gemm(Ab, Bb, "bf16", epi, C0, bias)
+    assert oracle.rel_frobenius(got, ref) <= GEMM_FROB_TOL
+    if epi == 1:
+        assert np.all(got >= 0)
+
+
+def test_gemm_odd_shape_takes_exact_simt_path(pkg, sess):
+    M, N, K = 37, 45, 51  # N and K not multiples of 8: no TMA row pitch
+    Ab = oracle.to_bf16_bits(oracle.fill_uniform((M, K), 3, -1.0, 1.0))
+    Bb = oracle.to_bf16_bits(oracle.fill_uniform((K, N), 4, -1.0, 1.0))
+    got = _gemm(pkg, sess, Ab, Bb, pkg.blob.BF16)
+    assert sess.last_kernel() == "gemm_simt"
+    assert got.tobytes() == oracle.matmul_x16_f32(Ab, Bb, True).tobytes()
+
+
+def test_config3_gemm_bf16_4096_relu_sampled_rows(pkg, sess):
+    """4096^3 + relu.  The oracle runs on 256 sampled rows (the full product is
+    69 GMAC on the CPU); every other row is covered by linearity: rows of C
+    depend on the matching rows of A only, so C(A with rows permuted) must be
+    C with rows permuted, bit for bit."""
+    B = pkg.blob
+    n = 4096
+    A = oracle.to_bf16_bits(oracle.fill_uniform((n, n), 3, -1.0, 1.0))
+    Bm = oracle.to_bf16_bits(oracle.fill_uniform((n, n), 4, -1.0, 1.0))
+    dA, dB, dC = sess.upload(A), sess.upload(Bm), sess.alloc(n * n * 4)
+    k = sess.kernel(B.gemm("cfg3", n, n, n, B.BF16, B.EPI_RELU))
+    sess.launch(k, [dA, dB, dC])
+    assert sess.last_kernel() == "gemm_tcgen05"
+    got = sess.download(dC, (n, n), np.float32)
+    rows = np.sort(np.random.default_rng(0).choice(n, 256, replace=False))
+    ref = oracle.relu(oracle.matmul_x16_f32(A[rows], Bm, True))
+    assert oracle.rel_frobenius(got[rows], ref) <= GEMM_FROB_TOL
+    perm = np.random.default_rng(1).permutation(n)
+    dA2 = sess.upload(A[perm])
+    sess.launch(k, [dA2, dB, dC])
+    got2 = sess.download(dC, (n, n), np.float32)
+    assert np.array_equal(got2, got[perm])
+
+
+# ---------------------------------------------------------------- softmax
+def _softmax(pkg, sess, X, neg_inf=False):
+    dX = sess.upload(X)
+    dY = sess.upload(np.full(X.shape, np.nan, np.float32))
+    sess.run(pkg.blob.softmax("sm", X.shape[0], X.shape[1], neg_inf), [dX, dY])
+    return sess.download(dY, X.shape, np.float32)
+
+
+def test_config2_softmax_4096x1024(pkg, sess):
+    X = np.random.default_rng(2).normal(0.0, 3.0, (4096, 1024)).astype(np.float32)
+    got = _softmax(pkg, sess, X)
+    ref = oracle.softmax(X)
+    assert oracle.max_rel_err(got, ref) <= SOFTMAX_REDUCE_TOL
+    x64 = X.astype(np.float64)
+    e = np.exp(x64 - x64.max(-1, keepdims=True))
+    truth = e / e.sum(-1, keepdims=True)
+    assert np.max(np.abs(got - truth) / truth) <= SOFTMAX_REDUCE_TOL
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 7), (10, 20), (33, 128), (17, 132), (64, 512),
+                                   (5, 2000), (9, 2048), (4, 5000), (2, 40000), (300, 1001)])
+def test_softmax_shapes(pkg, sess, shape):
+    X = np.random.default_rng(shape[0] * 7 + shape[1]).normal(0.0, 3.0, shape).astype(np.float32)
+    x64 = X.astype(np.float64)
+    e = np.exp(x64 - x64.max(-1, keepdims=True))
+    truth = e / e.sum(-1, keepdims=True)
+    for neg_inf in (False, True):
+        got = _softmax(pkg, sess, X, neg_inf)
+        ref = oracle.softmax(X, oracle.SOFTMAX_PLAIDML if neg_inf else oracle.SOFTMAX_BENCH)
+        assert np.max(np.abs(got - truth) / truth) <= SOFTMAX_REDUCE_TOL
+        # The oracle adds the row sequentially in f32; on rows of tens of
+        # thousands of elements its own rounding error exceeds 1e-5, so the
+        # budget against it is 1e-5 plus the oracle's distance from the f64 result.
+        oracle_err = float(np.max(np.abs(ref - truth) / truth))
+        assert oracle.max_rel_err(got, ref) <= SOFTMAX_REDUCE_TOL + oracle_err
+        if shape[1] <= 4096:
+            assert oracle.max_rel_err(got, ref) <= SOFTMAX_REDUCE_TOL
+
+
+def test_softmax_special_values(pkg, sess):
+    X = np.random.default_rng(5).normal(0.0, 3.0, (6, 256)).astype(np.float32)
+    X[1, 17] = np.nan
+    X[2, 3] = np.inf
+    X[3, :] = -np.inf
+    X[4, :] = 1e30
+    X[5, 0] = -np.inf
+    got = _softmax(pkg, sess, X)
+    ref = oracle.softmax(X)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    ok = ~np.isnan(ref)
+    assert oracle.max_rel_err(got[ok], ref[ok]) <= SOFTMAX_REDUCE_TOL
+
+
+# ---------------------------------------------------------------- reductions
+def test_config4_reduce_rows_32768x8192(pkg, sess):
+    rows, cols = 32768, 8192
+    B = pkg.blob
+    dX, dY = sess.alloc(rows * cols * 4), sess.alloc(rows * 4)
+    sess.run(B.fill_uniform("fill", rows * cols, B.F32, 5, 0.0, 1.0), [dX])
+    sess.run(B.reduce_rows("red", rows, cols), [dX, dY])
+    got = sess.download(dY, (rows,), np.float32)
+    X = oracle.fill_uniform((rows, cols), 5, 0.0, 1.0)
+    # the device generator is the same integer hash: identical inputs
+    chunk = sess.download(dX, (rows * cols,), np.float32)
+    assert np.array_equal(chunk, X.reshape(-1))
+    ref = oracle.reduce_rows(X)
+    assert oracle.max_rel_err(got, ref) <= SOFTMAX_REDUCE_TOL
+    truth = X.astype(np.float64).sum(-1)
+    assert np.max(np.abs(got - truth) / truth) <= SOFTMAX_REDUCE_TOL
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (7, 3), (10, 20), (64, 128), (33, 1001), (5, 4100),
+                                   (2, 70000), (1000, 36), (3, 0)])
+@pytest.mark.parametrize("acc", [False, True])
+def test_reduce_rows_shapes(pkg, sess, shape, acc):
+    rng = np.random.default_rng(shape[0] + 31 * shape[1])
+    X = rng.uniform(0, 1, shape).astype(np.float32)
+    init = rng.uniform(0, 1, shape[0]).astype(np.float32)
+    dX, dY = sess.upload(X), sess.upload(init if acc else np.full(shape[0], np.nan, np.float32))
+    sess.run(pkg.blob.reduce_rows("red", shape[0], shape[1], acc), [dX, dY])
+    got = sess.download(dY, (shape[0],), np.float32)
+    ref = oracle.reduce_rows(X, init if acc else None)
+    truth = X.astype(np.float64).sum(-1) + (init if acc else 0.0)
+    den = np.maximum(np.abs(truth), 1e-30)
+    assert np.max(np.abs(got - truth) / den, initial=0.0) <= SOFTMAX_REDUCE_TOL
+    # sequential f32 adds drift beyond 1e-5 on very long rows: budget against the
+    # oracle = 1e-5 + the oracle's own distance from the f64 sum
+    oracle_err = float(np.max(np.abs(ref - truth) / den, initial=0.0))
+    assert oracle.max_rel_err(got, ref) <= SOFTMAX_REDUCE_TOL + oracle_err
+    if shape[1] <= 8192:
+        assert oracle.max_rel_err(got, ref) <= SOFTMAX_REDUCE_TOL
+
+
+@pytest.mark.parametrize("shape", [(32, 1000), (1, 5), (100, 3), (7, 4096)])
+@pytest.mark.parametrize("acc", [False, True])
+def test_reduce_leading_is_bit_exact(pkg, sess, shape, acc):
+    rng = np.random.default_rng(shape[0] + shape[1])
+    X = rng.uniform(-1, 1, shape).astype(np.float32)
+    init = rng.uniform(-1, 1, shape[1]).astype(np.float32)
+    dX, dY = sess.upload(X), sess.upload(init if acc else np.full(shape[1], np.nan, np.float32))
+    sess.run(pkg.blob.reduce_leading("red", shape[0], shape[1], acc), [dX, dY])
+    got = sess.download(dY, (shape[1],), np.float32)
+    assert got.tobytes() == oracle.reduce_leading(X, init if acc else None).tobytes()
+
+
+@pytest.mark.parametrize("n", [1, 200, 16384, 16385, 1000003])
+def test_reduce_all(pkg, sess, n):
+    X = np.random.default_rng(n).uniform(0, 1, n).astype(np.float32)
+    dX, dY = sess.upload(X), sess.upload(np.array([2.5], np.float32))
+    sess.run(pkg.blob.reduce_all("sum", n, accumulate=True), [dX, dY])
+    got = sess.download(dY, (1,), np.float32)[0]
+    truth = X.astype(np.float64).sum() + 2.5
+    assert abs(got - truth) / truth <= SOFTMAX_REDUCE_TOL
+
+
+# ---------------------------------------------------------------- transpose
+def test_config4_transpose_8192_bit_exact(pkg, sess):
+    n = 8192
+    T = oracle.fill_uniform((n, n), 6, -1.0, 1.0)
+    dT, dU = sess.upload(T), sess.alloc(T.nbytes)
+    sess.run(pkg.blob.transpose2d("tr", n, n), [dT, dU])
+    got = sess.download(dU, (n, n), np.float32)
+    assert got.tobytes() == oracle.transpose2d(T).tobytes()
+    # involution: transposing twice gives the input back
+    sess.run(pkg.blob.transpose2d("tr", n, n), [dU, dT])
+    assert sess.download(dT, (n, n), np.float32).tobytes() == T.tobytes()
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (10, 20), (64, 64), (65, 63), (4, 1000), (1000, 4),
+                                   (128, 260), (1, 77), (1024, 1024)])
+@pytest.mark.parametrize("dtype", [np.float32, np.uint16])
+def test_transpose2d_shapes(pkg, sess, shape, dtype):
+    rng = np.random.default_rng(shape[0] * 3 + shape[1])
+    X = rng.integers(0, 60000, shape).astype(dtype)
+    dX, dY = sess.upload(X), sess.upload(np.zeros(shape[::-1], dtype))
+    dt = pkg.blob.F32 if dtype == np.float32 else pkg.blob.BF16
+    sess.run(pkg.blob.transpose2d("tr", shape[0], shape[1], dt), [dX, dY])
+    assert np.array_equal(sess.download(dY, shape[::-1], dtype), oracle.transpose2d(X))
+
+
+@pytest.mark.parametrize("dims", [(16, 96, 96), (96, 7, 96), (3, 5, 7)])
+@pytest.mark.parametrize("perm", [(0, 2, 1), (2, 1, 0), (1, 0, 2), (2, 0, 1), (1, 2, 0)])
+def test_transpose3d(pkg, sess, dims, perm):
+    X = np.random.default_rng(sum(dims)).uniform(-1, 1, dims).astype(np.float32)
+    dX, dY = sess.upload(X), sess.alloc(X.nbytes)
+    sess.run(pkg.blob.transpose3d("tr3", dims, perm), [dX, dY])
+    got = sess.download(dY, tuple(dims[p] for p in perm), np.float32)
+    assert np.array_equal(got, oracle.transpose3d(X, perm))
+
+
+# ---------------------------------------------------------------- eltwise / fill
+def test_eltwise_relu_silu(pkg, sess):
+    X = np.random.default_rng(8).normal(0, 4, 100003).astype(np.float32)
+    X[:4] = [np.nan, -0.0, 0.0, -np.inf]
+    dX, dY = sess.upload(X), sess.alloc(X.nbytes)
+    sess.run(pkg.blob.eltwise("relu", X.size, pkg.blob.EPI_RELU), [dX, dY])
+    got = sess.download(dY, X.shape, np.float32)
+    ref = oracle.relu(X)
+    assert np.array_equal(got[1:].view(np.uint32), ref[1:].view(np.uint32)) and np.isnan(got[0])
+    sess.run(pkg.blob.eltwise("silu", X.size, pkg.blob.EPI_SILU), [dX, dY])
+    got = sess.download(dY, X.shape, np.float32)
+    ref = oracle.silu(X)
+    ok = ~np.isnan(ref)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert oracle.max_rel_err(got[ok], ref[ok], 1e-37) <= 1e-5
+
+
+def test_fill_uniform_matches_oracle_bits(pkg, sess):
+    B = pkg.blob
+    n = 100001
+    d = sess.alloc(n * 4)
+    sess.run(B.fill_uniform("f", n, B.F32, 42, -1.0, 1.0, first=7), [d])
+    got = sess.download(d, (n,), np.float32)
+    assert got.tobytes() == oracle.fill_uniform((n,), 42, -1.0, 1.0, first=7).tobytes()
+    sess.run(B.fill_uniform("fb", n, B.BF16, 42, -1.0, 1.0), [d])
+    gb = sess.download(d, (n,), np.uint16)
+    assert np.array_equal(gb, oracle.to_bf16_bits(oracle.fill_uniform((n,), 42, -1.0, 1.0)))
+    sess.run(B.fill_normal("fn", n, B.F32, 9, 0.0, 0.02), [d])
+    z = sess.download(d, (n,), np.float32)
+    assert abs(z.mean()) < 5e-4 and abs(z.std() - 0.02) < 5e-4
+
+
+# ---------------------------------------------------------------- ABI behaviour
+def test_launch_counter_events_and_shared_memory(pkg, sess):
+    rt, B = pkg.runtime, pkg.blob
+    before = rt.imexLaunchCount()
+    X = oracle.fill_uniform((64, 256), 1, 0.0, 1.0)
+    # host_shared allocation: host writes it directly, the launch prefetches it
+    import ctypes as C
+    p = sess.alloc(X.nbytes, shared=True)
+    C.memmove(p, X.ctypes.data, X.nbytes)
+    y = sess.alloc(64 * 4, shared=True)
+    k = sess.kernel(B.reduce_rows("r", 64, 256))
+    e0 = rt.imexEventRecord(sess.stream)
+    ev = sess.launch(k, [p, y], wait=False)
+    k2 = sess.kernel(B.eltwise("relu", 64, B.EPI_RELU))
+    sess.launch(k2, [y, y], wait=False, deps=[ev])
+    e1 = rt.imexEventRecord(sess.stream)
+    sess.wait()
+    assert rt.imexEventElapsedMs(e0, e1) > 0
+    host = np.ctypeslib.as_array((C.c_float * 64).from_address(y))
+    assert oracle.max_rel_err(host.copy(), oracle.reduce_rows(X)) <= SOFTMAX_REDUCE_TOL
+    assert rt.imexLaunchCount() - before == 2

@@ -119,7 +119,9 @@ def test_16bit_conversions_match_numpy():
     allh = np.arange(65536, dtype=np.uint16)
     ours = np.array([oracle.lib().oracle_f16_to_f32(int(v)) for v in allh[::7]], np.float32)
     ref = allh[::7].view(np.float16).astype(np.float32)
-    assert np.array_equal(ours.view(np.uint32), ref.view(np.uint32))
+    finite = ~np.isnan(ref)  # NaN payloads may be quieted on the way back through ctypes
+    assert np.array_equal(ours.view(np.uint32)[finite], ref.view(np.uint32)[finite])
+    assert np.all(np.isnan(ours[~finite]))
     b = oracle.to_bf16_bits(x)
     import torch
     tb = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
