@@ -33,8 +33,10 @@ extern "C" {
  * order the launch passes them; trailing scalar params the lowering adds for
  * loop bounds are ignored):
  *   GEMM            A[M,K], B[K,N], C[M,N] (, bias[N] when IMEX_FLAG_BIAS)
- *                   dims = {M, N, K}; C = (C when IMEX_FLAG_ACCUMULATE else 0) + A.B,
- *                   then + bias, then epilogue
+ *                   dims = {M, N, K, lda, ldb, ldc}; row pitches in elements, 0 = dense
+ *                   (memref strides are static in the IR, so they travel here too);
+ *                   C = (C when IMEX_FLAG_ACCUMULATE else 0) + A.B, then + bias,
+ *                   then epilogue
  *   SOFTMAX         X[rows,cols], Y[rows,cols]           dims = {rows, cols}
  *   REDUCE_ROWS     X[rows,cols], Y[rows]                dims = {rows, cols}
  *                   Y[r] = (Y[r] when ACCUMULATE else 0) + sum_c X[r,c]

@@ -57,9 +57,11 @@ def unpack_blob(data):
     return version, out
 
 
-def gemm(name, M, N, K, in_dtype=BF16, epilogue=EPI_NONE, accumulate=False, bias=False):
+def gemm(name, M, N, K, in_dtype=BF16, epilogue=EPI_NONE, accumulate=False, bias=False,
+         lda=0, ldb=0, ldc=0):
+    """lda/ldb/ldc: row pitches in elements (0 = dense)."""
     flags = (FLAG_ACCUMULATE if accumulate else 0) | (FLAG_BIAS if bias else 0)
-    return KernelDesc(name, OP_GEMM, in_dtype, F32, epilogue, flags, (M, N, K))
+    return KernelDesc(name, OP_GEMM, in_dtype, F32, epilogue, flags, (M, N, K, lda, ldb, ldc))
 
 
 def softmax(name, rows, cols, neg_inf_init=False):

@@ -25,6 +25,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-I" + os.path.join(ROOT, "i
 RUNTIME_SOURCES = [
     "kernels/gemm_simt.cu",
     "kernels/gemm_tcgen05.cu",
+    "kernels/gemm_tcgen05_2cta.cu",
     "kernels/softmax.cu",
     "kernels/reduce.cu",
     "kernels/transpose.cu",

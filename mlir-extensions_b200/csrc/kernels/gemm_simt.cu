@@ -26,8 +26,8 @@ template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return _
 template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T *__restrict__ A, const T *__restrict__ B, float *__restrict__ C,
-                 const float *__restrict__ bias, int64_t M, int64_t N, int64_t K,
-                 int epilogue, int accumulate) {
+                 const float *__restrict__ bias, int64_t M, int64_t N, int64_t K, int64_t lda,
+                 int64_t ldb, int64_t ldc, int epilogue, int accumulate) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -41,7 +41,7 @@ gemm_simt_kernel(const T *__restrict__ A, const T *__restrict__ B, float *__rest
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       int64_t r = m0 + ty * TM + i, c = n0 + tx * TN + j;
-      acc[i][j] = (accumulate && r < M && c < N) ? C[r * N + c] : 0.0f;
+      acc[i][j] = (accumulate && r < M && c < N) ? C[r * ldc + c] : 0.0f;
     }
 
   for (int64_t k0 = 0; k0 < K; k0 += BK) {
@@ -49,12 +49,12 @@ gemm_simt_kernel(const T *__restrict__ A, const T *__restrict__ B, float *__rest
     for (int e = tid; e < BM * BK; e += 256) {
       int m = e / BK, k = e % BK;
       int64_t r = m0 + m, kk = k0 + k;
-      As[k][m] = (r < M && kk < K) ? to_f32(A[r * K + kk]) : 0.0f;
+      As[k][m] = (r < M && kk < K) ? to_f32(A[r * lda + kk]) : 0.0f;
     }
     for (int e = tid; e < BK * BN; e += 256) {
       int k = e / BN, n = e % BN;
       int64_t kk = k0 + k, c = n0 + n;
-      Bs[k][n] = (kk < K && c < N) ? to_f32(B[kk * N + c]) : 0.0f;
+      Bs[k][n] = (kk < K && c < N) ? to_f32(B[kk * ldb + c]) : 0.0f;
     }
     __syncthreads();
     // only real k steps: a padded step would add +0 and could flip a -0 result
@@ -82,7 +82,7 @@ gemm_simt_kernel(const T *__restrict__ A, const T *__restrict__ B, float *__rest
       if (r < M && c < N) {
         float v = acc[i][j];
         if (bias) v = __fadd_rn(v, bias[c]);
-        C[r * N + c] = apply_epilogue(v, epilogue);
+        C[r * ldc + c] = apply_epilogue(v, epilogue);
       }
     }
 }
@@ -91,19 +91,21 @@ gemm_simt_kernel(const T *__restrict__ A, const T *__restrict__ B, float *__rest
 
 cudaError_t launch_gemm_simt(const GemmProblem &p, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0) return cudaSuccess;
+  const int64_t lda = p.lda > 0 ? p.lda : p.K, ldb = p.ldb > 0 ? p.ldb : p.N,
+                ldc = p.ldc > 0 ? p.ldc : p.N;
   dim3 grid(static_cast<unsigned>((p.N + BN - 1) / BN), static_cast<unsigned>((p.M + BM - 1) / BM));
   if (p.in_dtype == kF32)
     gemm_simt_kernel<float><<<grid, 256, 0, stream>>>(
         static_cast<const float *>(p.A), static_cast<const float *>(p.B), p.C, p.bias, p.M, p.N,
-        p.K, p.epilogue, p.accumulate ? 1 : 0);
+        p.K, lda, ldb, ldc, p.epilogue, p.accumulate ? 1 : 0);
   else if (p.in_dtype == kBF16)
     gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(p.A), static_cast<const __nv_bfloat16 *>(p.B), p.C,
-        p.bias, p.M, p.N, p.K, p.epilogue, p.accumulate ? 1 : 0);
+        p.bias, p.M, p.N, p.K, lda, ldb, ldc, p.epilogue, p.accumulate ? 1 : 0);
   else if (p.in_dtype == kF16)
     gemm_simt_kernel<__half><<<grid, 256, 0, stream>>>(
         static_cast<const __half *>(p.A), static_cast<const __half *>(p.B), p.C, p.bias, p.M, p.N,
-        p.K, p.epilogue, p.accumulate ? 1 : 0);
+        p.K, lda, ldb, ldc, p.epilogue, p.accumulate ? 1 : 0);
   else
     return cudaErrorInvalidValue;
   return cudaGetLastError();

@@ -28,6 +28,8 @@
 // the host-visible status word and leaves its loop; the kernel still drains
 // its loads, frees TMEM and returns.
 #include "epilogue.cuh"
+#include "tcgen05_ptx.cuh"
+#include "tcgen05_host.h"
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -53,13 +55,13 @@ constexpr int B_BOX_BYTES = BK * 64 * 2;     // one 64(k) x 64(n) box = 8 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second
 
 struct KernelParams {
   float *C;
   const float *bias;
   unsigned *status;
   int M, N, K;
+  long long ldc;
   int tiles_m, tiles_n, num_tiles, group_m;
   int k_blocks;
   int epilogue;
@@ -67,101 +69,8 @@ struct KernelParams {
   uint32_t idesc;
 };
 
-// ---- PTX wrappers --------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
-  }
-  return true;
-}
-// The status word lives in mapped host memory: a plain store, no atomics.
-__device__ __forceinline__ void report(unsigned *status, unsigned code) {
-  *reinterpret_cast<volatile unsigned *>(status) = code;
-  __threadfence_system();
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
-      "{%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                                uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor (tcgen05): start address, leading / stride
-// byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ULL << 46;  // version
-  d |= 2ULL << 61;  // SWIZZLE_128B
-  return d;
-}
+using namespace tc;
+using namespace tc_host;
 
 // Tile order: bands of `group_m` row-blocks; inside a band the column-block
 // index moves slowest, so the CTAs in flight share a band of A and a few
@@ -315,7 +224,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tcgen05_fence_after();
       const int row = mb * BM + lane_group * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BN;
-      float *c_row = p.C + static_cast<size_t>(row) * p.N;
+      float *c_row = p.C + static_cast<size_t>(row) * p.ldc;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -364,57 +273,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-// ---- host side -------------------------------------------------------------
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                              const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = [] {
-    void *sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) !=
-            cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return static_cast<EncodeFn>(nullptr);
-    return reinterpret_cast<EncodeFn>(sym);
-  }();
-  return fn;
-}
-
-// 2-D row-major [outer, inner] 16-bit tensor, box [box_outer, 64], 128B swizzle.
-bool make_map(CUtensorMap *m, const void *base, int in_dtype, int64_t inner, int64_t outer,
-              int box_outer) {
-  EncodeFn enc = encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
-  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMapDataType dt =
-      in_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return enc(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 148;
-  }();
-  return n;
-}
-
 } // namespace
 
 bool gemm_tcgen05_supported(const GemmProblem &p) {
   if (p.in_dtype != kBF16 && p.in_dtype != kF16) return false;
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return false;
   if (p.K % 8 || p.N % 8) return false;  // TMA row pitch must be a multiple of 16 bytes
+  if (p.lda % 8 || p.ldb % 8 || p.ldc % 4) return false;
+  if ((p.lda && p.lda < p.K) || (p.ldb && p.ldb < p.N) || (p.ldc && p.ldc < p.N)) return false;
   if (p.M > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX) return false;
   auto al = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   return al(p.A) && al(p.B) && al(p.C) && (!p.bias || al(p.bias));
@@ -433,8 +299,8 @@ cudaError_t launch_gemm_tcgen05(const GemmProblem &g, unsigned *status, cudaStre
   CUtensorMap ta, tb;
   // cudaErrorNotSupported: the driver refused this shape for a tensor map; the
   // caller falls back to the SIMT kernel
-  if (!make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM)) return cudaErrorNotSupported;
-  if (!make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK)) return cudaErrorNotSupported;
+  if (!make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM, g.lda)) return cudaErrorNotSupported;
+  if (!make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK, g.ldb)) return cudaErrorNotSupported;
 
   KernelParams p;
   p.C = g.C;
@@ -443,6 +309,7 @@ cudaError_t launch_gemm_tcgen05(const GemmProblem &g, unsigned *status, cudaStre
   p.M = static_cast<int>(g.M);
   p.N = static_cast<int>(g.N);
   p.K = static_cast<int>(g.K);
+  p.ldc = g.ldc > 0 ? g.ldc : g.N;
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_tiles = p.tiles_m * p.tiles_n;

@@ -1,0 +1,362 @@
+// bf16/f16 -> f32 GEMM on CTA pairs: tcgen05.mma.cta_group::2 (M256 N256 K16).
+//
+// Same op, epilogues and reference citations as gemm_tcgen05.cu.  Two CTAs of a
+// 2-CTA cluster share one 256x256 output tile: CTA r owns rows [128r, 128r+128)
+// of it (its own 128-lane TMEM accumulator) and loads, per 64-wide k block,
+// its own 128x64 slice of A and HALF of the B block (64 x 128 columns).  The
+// pair's tensor cores read both halves of B from both CTAs' shared memory, so
+// every byte of B is fetched from L2 once per pair instead of once per CTA:
+// 32 KB per CTA and stage instead of 48 KB, which is what bounds the 1-CTA
+// kernel (the tensor pipe waits for smem fills).  There is no TMA multicast:
+// each CTA issues plain tile loads into its own shared memory; only the
+// completion barrier lives in the leader CTA.
+//
+//   warp 0 (both CTAs)   TMA producer: waits its own `empty[s]`, loads A and its
+//                        B half, completion bytes go to the LEADER's `full[s]`.
+//   warp 1 (leader only) waits `full[s]` (64 KB from both CTAs), issues 4 MMAs per
+//                        k block, tcgen05.commit multicast to `empty[s]` of both
+//                        CTAs; after the last k block commits to `acc_full[a]` of both.
+//   warps 2-5 (both)     epilogue on the CTA's own 128 rows: tcgen05.ld, + C0 / bias,
+//                        relu / silu, 128-bit stores; then arrive on the leader's
+//                        `acc_empty[a]` (8 arrivals: 4 warps x 2 CTAs).
+// Waits are bounded; a wait that runs out records a status code and the role
+// leaves its loop, after which the pair drains, syncs and frees TMEM.
+#include "epilogue.cuh"
+#include "tcgen05_host.h"
+#include "tcgen05_ptx.cuh"
+
+#include <cstdlib>
+#include <mutex>
+
+namespace imex {
+namespace {
+
+using namespace tc;
+using namespace tc_host;
+
+constexpr int BM = 128;       // rows per CTA
+constexpr int PAIR_M = 256;   // rows per CTA pair (UMMA M)
+constexpr int BN = 256;       // tile columns (UMMA N)
+constexpr int BN_HALF = 128;  // columns of B each CTA loads
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 6;
+constexpr int NUM_ACC = 2;
+constexpr int TMEM_COLS = 512;
+constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KB
+constexpr int B_BOX_BYTES = BK * 64 * 2;         // 8 KB: 64 k x 64 columns
+constexpr int B_STAGE_BYTES = BK * BN_HALF * 2;  // 16 KB = two boxes
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct PairParams {
+  float *C;
+  const float *bias;
+  unsigned *status;
+  int M, N, K;
+  long long ldc;
+  int tiles_m, tiles_n, num_tiles, group_m;  // in 256x256 pair tiles
+  int k_blocks;
+  int epilogue;
+  int accumulate;
+  uint32_t idesc;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// Tile load of a CTA pair: data lands in this CTA's shared memory, completion
+// bytes are counted on a barrier that may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc,
+                                                     uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void pair_tile_coords(int tile, const PairParams &p, int &mb, int &nb) {
+  const int band_tiles = p.group_m * p.tiles_n;
+  const int band = tile / band_tiles;
+  const int first_m = band * p.group_m;
+  const int rows_in_band = min(p.group_m, p.tiles_m - first_m);
+  const int t = tile - band * band_tiles;
+  nb = t / rows_in_band;
+  mb = first_m + t % rows_in_band;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + NUM_ACC + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 2 * NUM_ACC);
+  uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(
+      smem_aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * NUM_ACC));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // used in the leader: its own expect-tx arrival
+      mbar_init(empty_bar(s), 1);  // one multicast commit per round
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);  // used in the leader: 4 epilogue warps x 2 CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
+        int mb, nb;
+        pair_tile_coords(tile, p, mb, nb);
+        const int row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
+        const int col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            report(p.status, kStatusTmaWaitTimeout);
+            ok = false;
+            break;
+          }
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          tma_load_2d_pair(a_dst, &tmap_a, kb * BK, row0, leader_full);
+          tma_load_2d_pair(b_dst, &tmap_b, col0, kb * BK, leader_full);
+          tma_load_2d_pair(b_dst + B_BOX_BYTES, &tmap_b, col0 + 64, kb * BK, leader_full);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // Tail: every stage this CTA filled has been consumed (its commit arrived
+      // here) before the CTA may exit — nothing is still reading this shared memory
+      // or about to signal these barriers.
+      for (int s = 0; s < STAGES; ++s) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u)) break;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader) -----------------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
+          report(p.status, kStatusMmaWaitTimeout);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            report(p.status, kStatusMmaWaitTimeout);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = make_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = make_smem_desc(b_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+            tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | k) ? 1u : 0u);
+          }
+          tcgen05_commit_pair(empty_bar(stage), 3);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tcgen05_commit_pair(acc_full_bar(acc), 3);
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // -------------------------------- epilogue (both CTAs) ---------------------
+    const int lane_group = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
+      int mb, nb;
+      pair_tile_coords(tile, p, mb, nb);
+      bool ok = mbar_wait(acc_full_bar(acc), acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
+        break;
+      }
+      tcgen05_fence_after();
+      const int row = mb * PAIR_M + static_cast<int>(cta_rank) * BM + lane_group * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BN;
+      float *c_row = p.C + static_cast<size_t>(row) * p.ldc;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        const int col0 = nb * BN + c0;
+        if (row < p.M && col0 < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int col = col0 + j;
+            if (col < p.N) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.accumulate) {
+                const float4 c = *reinterpret_cast<const float4 *>(c_row + col);
+                v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+              }
+              if (p.bias) {
+                const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+              }
+              v.x = apply_epilogue(v.x, p.epilogue);
+              v.y = apply_epilogue(v.y, p.epilogue);
+              v.z = apply_epilogue(v.z, p.epilogue);
+              v.w = apply_epilogue(v.w, p.epilogue);
+              *reinterpret_cast<float4 *>(c_row + col) = v;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its smem or barriers
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+} // namespace
+
+bool gemm_tcgen05_2cta_preferred(const GemmProblem &p) {
+  // a single row block gains nothing from pairing
+  return gemm_tcgen05_supported(p) && p.M > 128 && !getenv("IMEX_B200_GEMM_1CTA");
+}
+
+cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cudaStream_t stream) {
+  if (!gemm_tcgen05_supported(g)) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+
+  const int64_t lda = g.lda > 0 ? g.lda : g.K;
+  const int64_t ldb = g.ldb > 0 ? g.ldb : g.N;
+  const int64_t ldc = g.ldc > 0 ? g.ldc : g.N;
+  CUtensorMap ta, tb;
+  if (!make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM, lda)) return cudaErrorNotSupported;
+  if (!make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK, ldb)) return cudaErrorNotSupported;
+
+  PairParams p;
+  p.C = g.C;
+  p.bias = g.bias;
+  p.status = status;
+  p.M = static_cast<int>(g.M);
+  p.N = static_cast<int>(g.N);
+  p.K = static_cast<int>(g.K);
+  p.ldc = ldc;
+  p.tiles_m = (p.M + PAIR_M - 1) / PAIR_M;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.group_m = 8;
+  if (const char *e = getenv("IMEX_GEMM_GROUP_M")) {
+    int v = atoi(e);
+    if (v > 0) p.group_m = v;
+  }
+  p.k_blocks = (p.K + BK - 1) / BK;
+  p.epilogue = g.epilogue;
+  p.accumulate = g.accumulate ? 1 : 0;
+  const uint32_t fmt = g.in_dtype == kBF16 ? 1u : 0u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
+            (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(PAIR_M >> 4) << 24);
+
+  const int max_clusters = sm_count() / 2;
+  const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
+  gemm_tcgen05_2cta_kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+} // namespace imex

@@ -26,6 +26,7 @@ struct GemmProblem {
   float *C;           // [M,N] row-major f32
   const float *bias;  // [N] or nullptr
   int64_t M, N, K;
+  int64_t lda = 0, ldb = 0, ldc = 0;  // row pitches in elements; 0 = dense (K, N, N)
   int in_dtype;       // DType
   int epilogue;       // Epilogue
   bool accumulate;    // C is read as the initial value
@@ -38,10 +39,15 @@ cudaError_t launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
 
 // bf16/f16 -> f32 on the 5th-gen tensor cores (tcgen05.mma, TMEM
 // accumulators, TMA-fed 128B-swizzled smem ring, persistent tiles).
-// Needs K % 8 == 0, N % 8 == 0 and 16-byte aligned A, B, C.
+// Needs K % 8 == 0, N % 8 == 0, pitches that keep rows 16-byte aligned and
+// 16-byte aligned A, B, C.
 bool gemm_tcgen05_supported(const GemmProblem &p);
 cudaError_t launch_gemm_tcgen05(const GemmProblem &p, unsigned *status,
                                 cudaStream_t stream);
+// Same contract on CTA pairs (tcgen05.mma.cta_group::2, 256x256 tile per pair).
+bool gemm_tcgen05_2cta_preferred(const GemmProblem &p);
+cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &p, unsigned *status,
+                                     cudaStream_t stream);
 
 // Row softmax over the last dim (one pass over HBM: read X once, write Y once).
 cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols,

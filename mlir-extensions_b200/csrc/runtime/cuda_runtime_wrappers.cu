@@ -271,13 +271,22 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     g.M = d.dims[0];
     g.N = d.dims[1];
     g.K = d.dims[2];
+    g.lda = d.dims[3];
+    g.ldb = d.dims[4];
+    g.ldc = d.dims[5];
     g.in_dtype = static_cast<int>(d.in_dtype);
     g.epilogue = static_cast<int>(d.epilogue);
     g.accumulate = acc;
     if (g.M < 0 || g.N < 0 || g.K < 0) throw std::runtime_error("gpuLaunchKernel: negative gemm dims");
+    if ((g.lda && g.lda < g.K) || (g.ldb && g.ldb < g.N) || (g.ldc && g.ldc < g.N))
+      throw std::runtime_error("gpuLaunchKernel: gemm row pitch smaller than the row");
     const bool force_simt = getenv("IMEX_B200_FORCE_SIMT_GEMM") != nullptr;
     bool done = false;
-    if (!force_simt && imex::gemm_tcgen05_supported(g)) {
+    if (!force_simt && imex::gemm_tcgen05_2cta_preferred(g)) {
+      s->last_kernel = "gemm_tcgen05_2cta";
+      err = imex::launch_gemm_tcgen05_2cta(g, s->status_dev, s->stream);
+      done = err != cudaErrorNotSupported;
+    } else if (!force_simt && imex::gemm_tcgen05_supported(g)) {
       s->last_kernel = "gemm_tcgen05";
       err = imex::launch_gemm_tcgen05(g, s->status_dev, s->stream);
       done = err != cudaErrorNotSupported;

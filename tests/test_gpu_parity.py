@@ -21,6 +21,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOFTMAX_REDUCE_TOL = 1e-5
 GEMM_FROB_TOL = 1e-3
+TENSOR_CORE_KERNELS = ("gemm_tcgen05", "gemm_tcgen05_2cta")
 
 
 @pytest.fixture(scope="module")
@@ -177,7 +178,7 @@ def test_gemm_tcgen05_shapes(pkg, sess, kind, shape):
     Ab, Bb = conv(A), conv(Bm)
     dt = pkg.blob.BF16 if kind == "bf16" else pkg.blob.F16
     got = _gemm(pkg, sess, Ab, Bb, dt)
-    assert sess.last_kernel() == "gemm_tcgen05"
+    assert sess.last_kernel() in TENSOR_CORE_KERNELS
     ref = oracle.matmul_x16_f32(Ab, Bb, kind == "bf16")
     assert not np.isnan(got).any()
     assert oracle.rel_frobenius(got, ref) <= GEMM_FROB_TOL
@@ -193,11 +194,52 @@ def test_gemm_tcgen05_epilogues_bias_accumulate(pkg, sess, epi):
     C0 = rng.normal(0, 1, (M, N)).astype(np.float32)
     bias = rng.normal(0, 1, N).astype(np.float32)
     got = _gemm(pkg, sess, Ab, Bb, pkg.blob.BF16, epi, C0, bias)
-    assert sess.last_kernel() == "gemm_tcgen05"
+    assert sess.last_kernel() in TENSOR_CORE_KERNELS
     ref = _oracle_gemm(Ab, Bb, "bf16", epi, C0, bias)
     assert oracle.rel_frobenius(got, ref) <= GEMM_FROB_TOL
     if epi == 1:
         assert np.all(got >= 0)
+
+
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+def test_gemm_with_row_pitches(pkg, sess, kind):
+    """Sub-matrices of larger buffers: lda / ldb / ldc pitches (column slabs of B and C)."""
+    B = pkg.blob
+    M, N, K, lda, ldb, ldc = 300, 256, 192, 256, 512, 768
+    rng = np.random.default_rng(21)
+    Af = rng.uniform(-1, 1, (M, lda)).astype(np.float32)
+    Bf = rng.uniform(-1, 1, (K, ldb)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (M, ldc)).astype(np.float32)
+    if kind == "bf16":
+        Ah, Bh = oracle.to_bf16_bits(Af), oracle.to_bf16_bits(Bf)
+        dt, col_b, col_c = B.BF16, 128, 256
+        ref = oracle.matmul_x16_f32(Ah[:, :K].copy(), Bh[:, col_b:col_b + N].copy(), True)
+        esz = 2
+    else:
+        Ah, Bh = Af, Bf
+        dt, col_b, col_c = B.F32, 128, 256
+        ref = oracle.matmul_f32(Af[:, :K].copy(), Bf[:, col_b:col_b + N].copy())
+        esz = 4
+    dA, dB, dC = sess.upload(Ah), sess.upload(Bh), sess.upload(C0)
+    sess.run(B.gemm("pitched", M, N, K, dt, lda=lda, ldb=ldb, ldc=ldc),
+             [dA, dB + col_b * esz, dC + col_c * 4])
+    got = sess.download(dC, (M, ldc), np.float32)
+    assert np.array_equal(got[:, :col_c], C0[:, :col_c])          # untouched outside the slab
+    assert np.array_equal(got[:, col_c + N:], C0[:, col_c + N:])
+    if kind == "f32":
+        assert got[:, col_c:col_c + N].tobytes() == ref.tobytes()
+    else:
+        assert sess.last_kernel() in TENSOR_CORE_KERNELS
+        assert oracle.rel_frobenius(got[:, col_c:col_c + N], ref) <= GEMM_FROB_TOL
+
+
+def test_gemm_single_cta_kernel_still_matches(pkg, sess, monkeypatch):
+    monkeypatch.setenv("IMEX_B200_GEMM_1CTA", "1")
+    Ab = oracle.to_bf16_bits(oracle.fill_uniform((512, 320), 3, -1.0, 1.0))
+    Bb = oracle.to_bf16_bits(oracle.fill_uniform((320, 768), 4, -1.0, 1.0))
+    got = _gemm(pkg, sess, Ab, Bb, pkg.blob.BF16)
+    assert sess.last_kernel() == "gemm_tcgen05"
+    assert oracle.rel_frobenius(got, oracle.matmul_x16_f32(Ab, Bb, True)) <= GEMM_FROB_TOL
 
 
 def test_gemm_odd_shape_takes_exact_simt_path(pkg, sess):
@@ -221,7 +263,7 @@ def test_config3_gemm_bf16_4096_relu_sampled_rows(pkg, sess):
     dA, dB, dC = sess.upload(A), sess.upload(Bm), sess.alloc(n * n * 4)
     k = sess.kernel(B.gemm("cfg3", n, n, n, B.BF16, B.EPI_RELU))
     sess.launch(k, [dA, dB, dC])
-    assert sess.last_kernel() == "gemm_tcgen05"
+    assert sess.last_kernel() in TENSOR_CORE_KERNELS
     got = sess.download(dC, (n, n), np.float32)
     rows = np.sort(np.random.default_rng(0).choice(n, 256, replace=False))
     ref = oracle.relu(oracle.matmul_x16_f32(A[rows], Bm, True))
