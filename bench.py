@@ -191,6 +191,7 @@ def run_reference_arm(args):
 CASES = {
     "gemm8192_silu": "bf16 GEMM 8192x8192x8192 + silu (the config-5 kernel on 1/8 of the rows)",
     "gemm4096_relu": "bf16 GEMM 4096^3 + relu (config 3)",
+    "gemm8192_none": "bf16 GEMM 8192x8192x8192, no epilogue",
     "softmax": "softmax 4096x1024 (config 2)",
     "softmax_big": "softmax 65536x1024 (config-2 kernel on a 512 MiB problem, larger than L2)",
     "reduce": "row reduce 32768x8192 (config 4a)",
@@ -210,7 +211,7 @@ def run_case(name, iters):
     sess = pkg.Session(device=0, adopt_stream=stream.cuda_stream)
     if name.startswith("gemm"):
         n = 8192 if name.startswith("gemm8192") else 4096
-        epi = B.EPI_SILU if name.endswith("silu") else B.EPI_RELU
+        epi = {"silu": B.EPI_SILU, "relu": B.EPI_RELU, "none": B.EPI_NONE}[name.split("_")[1]]
         A = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
         Bm = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
         Cm = torch.empty((n, n), dtype=torch.float32, device=dev)
@@ -262,6 +263,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--rows", type=int, default=M_TOTAL, help="total rows of A (small runs)")
+    ap.add_argument("--sm-margin", type=int, default=4,
+                    help="SMs the GEMM leaves to the NCCL broadcast when N > 1")
     ap.add_argument("--case", default=None, choices=sorted(CASES),
                     help="run ONE small kernel case --iters times and exit (ncu captures)")
     ap.add_argument("--iters", type=int, default=3)
@@ -319,13 +322,17 @@ def main():
              [A.data_ptr()])
     if rank == 0:
         sess.run(B.fill_normal("fill_b", K_DIM * N_DIM, B.BF16, SEED_B, 0.0, 0.02), [Bm.data_ptr()])
-    gemm = sess.kernel(B.gemm("gemm_silu", rows, N_DIM, K_DIM, B.BF16, B.EPI_SILU))
-    ptrs = [A.data_ptr(), Bm.data_ptr(), Cm.data_ptr()]
+    epi = {"silu": B.EPI_SILU, "relu": B.EPI_RELU, "none": B.EPI_NONE}[
+        os.environ.get("IMEX_BENCH_EPILOGUE", "silu")]  # experiments only; the metric is silu
+    from mlir_extensions_b200.dist import RowShardedGemm
+    gemm = RowShardedGemm(sess, rank, world, M_total, N_DIM, K_DIM, B.BF16, epi, src=0,
+                          sm_margin=args.sm_margin, device=dev)
+    assert (gemm.row0, gemm.rows) == (row0, rows)
 
     def step():
-        if world > 1:
-            dist.broadcast(Bm, src=0)  # B lives on rank 0; lands in local HBM, read by TMA there
-        sess.launch(gemm, ptrs, wait=False)
+        # world > 1: B lives on rank 0; its column slabs are NCCL-broadcast on a side
+        # stream and land in local HBM, each slab's GEMM starts when its slab is in
+        return gemm(A, Bm, Cm)
 
     for _ in range(args.warmup):
         step()
@@ -339,21 +346,33 @@ def main():
     barrier()
     e0.record()
     for _ in range(args.steps):
-        if world > 1:
-            dist.broadcast(Bm, src=0)
-        ka, kb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ka.record()
-        sess.launch(gemm, ptrs, wait=False)
-        kb.record()
-        k_events.append((ka, kb))
+        if world == 1:
+            ka, kb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ka.record()
+            step()
+            kb.record()
+            k_events.append((ka, kb))
+        else:
+            step()
     e1.record()
     barrier()
     sess.wait()
     launches = rt.imexLaunchCount() - launches0
     clocks = sampler.stop() if rank == 0 else None
     total_ms = max_over_ranks(e0.elapsed_time(e1))
-    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_events]))
     ms_per_step = total_ms / args.steps
+    if world == 1:
+        kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_events]))
+    else:
+        # the GEMM launches of one step, timed alone (B already replicated), max over ranks
+        barrier()
+        ka, kb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ka.record()
+        for (c0, w), buf, kern in zip(gemm.slabs, gemm.slab_bufs, gemm.kernels):
+            sess.launch(kern, [A.data_ptr(), buf.data_ptr(), Cm.data_ptr() + 4 * c0], wait=False)
+        kb.record()
+        kb.synchronize()
+        kernel_ms = max_over_ranks(ka.elapsed_time(kb))
     flops_job = 2.0 * M_total * N_DIM * K_DIM
     value = flops_job / (ms_per_step * 1e-3) / 1e12
 
@@ -361,6 +380,8 @@ def main():
     from oracle import oracle
     sample_rows = np.sort(np.random.default_rng(rank).choice(rows, size=min(8, rows), replace=False))
     a_bits = A[torch.as_tensor(sample_rows, device=dev)].view(torch.int16).cpu().numpy().view(np.uint16)
+    if world > 1:
+        dist.broadcast(Bm, src=0)  # only for this check: non-root ranks hold B as slabs
     b_bits = Bm.view(torch.int16).cpu().numpy().view(np.uint16)
     got = Cm[torch.as_tensor(sample_rows, device=dev)].cpu().numpy()
     ref = oracle.silu(oracle.matmul_x16_f32(a_bits, b_bits, True))
@@ -386,6 +407,8 @@ def main():
             rt.gpuMemCopy(own.stream, dB, hB.data_ptr(), hB.numel() * 2)
             own.launch(k2, [dA, dB, dC], wait=True)
             rt.gpuMemCopy(own.stream, hC.data_ptr(), dC, hC.numel() * 4)
+        # (at N > 1 every rank uploads B from its own host copy: over PCIe that is
+        #  cheaper than waiting for rank 0's upload plus a broadcast)
 
         e2e_step()
         barrier()
@@ -416,6 +439,11 @@ def main():
                          "CPU GEMM (runner-utils _mlir_ciface_gemmBF16BF16F32) is single-threaded" % dt,
                "host_cores": os.cpu_count()}
 
+    sharded = None
+    if world > 1 and not args.no_kernels:
+        sharded = bench_sharded_rows(torch, pkg, sess, dev, peaks, rank, world, barrier,
+                                     max_over_ranks)
+
     if rank == 0:
         flops_launch = 2.0 * rows * N_DIM * K_DIM
         achieved = flops_launch / (kernel_ms * 1e-3) / 1e12
@@ -426,23 +454,64 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_total": M_total, "rows_per_rank": rows,
                        "partition": "block rows, last extent%N shards one longer",
-                       "collective": "NCCL broadcast of B from rank 0 inside every step" if world > 1 else "none",
+                       "collective": ("NCCL broadcast of B from rank 0 inside every step, in column "
+                                      "slabs %s overlapped with the slab GEMMs; GEMM leaves %d SMs free"
+                                      % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 else "none",
                        "l2": "inputs (1 GiB A shard + 128 MiB B) exceed the 126 MB L2"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC["gemm_cfg5"],
-                         "kernel": "gemm_tcgen05", "kernel_ms": kernel_ms,
+                         "kernel": sess.last_kernel(), "kernel_ms": kernel_ms,
+                         "launches_per_step": len(gemm.slabs),
                          "peak_source": peaks["source"] + " (cuBLAS bf16 burst)",
                          "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"])
                          if peaks.get("bf16_tflops_sustained") else None,
                          "frac_of_nominal_2250": achieved / 2250.0},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "parity": {"rel_frobenius_sampled_rows": frob, "tolerance": 1e-3},
-            "cpu_baseline": cpu, "kernels": kernels,
+            "cpu_baseline": cpu, "kernels": kernels, "sharded_rows": sharded,
         }
         print(json.dumps(line), flush=True)
     sess.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_sharded_rows(torch, pkg, sess, dev, peaks, rank, world, barrier, max_over_ranks,
+                       iters=20):
+    """Configs 4a and 2 row-sharded over the ranks: no exchange step, every rank
+    reduces / normalises its own block of rows; aggregate GB/s = all bytes / max time."""
+    B, rt = pkg.blob, pkg.runtime
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, total_rows, cols, make in (
+            ("reduce_rows_32768x8192", 32768, 8192, lambda r, c: B.reduce_rows("reduce", r, c)),
+            ("softmax_4096x1024", 4096, 1024, lambda r, c: B.softmax("softmax", r, c))):
+        rows = rt.imexShardSize(rank, world, total_rows)
+        X = torch.empty((rows, cols), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
+        is_reduce = name.startswith("reduce")
+        Y = torch.empty(rows if is_reduce else (rows, cols), dtype=torch.float32, device=dev)
+        k = sess.kernel(make(rows, cols))
+        ms = []
+        for i in range(iters + 3):
+            flush.zero_()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            sess.launch(k, [X.data_ptr(), Y.data_ptr()], wait=False)
+            b.record()
+            b.synchronize()
+            t = max_over_ranks(a.elapsed_time(b))
+            if i >= 3:
+                ms.append(t)
+        nbytes = total_rows * cols * 4 + (total_rows * 4 if is_reduce else total_rows * cols * 4)
+        med = float(np.median(ms))
+        ach = nbytes / (med * 1e-3) / 1e9
+        out[name] = {"value": ach, "unit": "GB/s", "ms_cold_median": med, "n_gpus": world,
+                     "rows_per_rank": rows, "algorithmic_bytes": nbytes,
+                     "frac_of_measured_hbm_per_gpu": ach / world / peaks["hbm_gbs"],
+                     "collective": "none (rows are independent)"}
+        del X, Y
+    return out
 
 
 def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):

@@ -86,7 +86,7 @@ typedef struct ImexKernelDesc {
   uint32_t out_dtype;              /* ImexDType of the output */
   uint32_t epilogue;               /* ImexEpilogue */
   uint32_t flags;                  /* ImexFlags */
-  uint32_t reserved;
+  uint32_t sm_margin;              /* GEMM: SMs left free for a collective running beside it */
   int64_t dims[6];
   float fparams[2];
 } ImexKernelDesc;

@@ -24,7 +24,7 @@ assert _DESC.size == 144 and _HEADER.size == 16
 
 class KernelDesc:
     def __init__(self, name, op, in_dtype=F32, out_dtype=F32, epilogue=EPI_NONE, flags=0,
-                 dims=(), fparams=(0.0, 0.0)):
+                 dims=(), fparams=(0.0, 0.0), sm_margin=0):
         if len(name.encode()) >= NAME_MAX:
             raise ValueError("kernel name too long")
         if len(dims) > 6:
@@ -32,12 +32,13 @@ class KernelDesc:
         self.name, self.op = name, op
         self.in_dtype, self.out_dtype = in_dtype, out_dtype
         self.epilogue, self.flags = epilogue, flags
+        self.sm_margin = int(sm_margin)
         self.dims = tuple(int(d) for d in dims) + (0,) * (6 - len(dims))
         self.fparams = tuple(float(f) for f in fparams)
 
     def pack(self):
         return _DESC.pack(self.name.encode(), self.op, self.in_dtype, self.out_dtype,
-                          self.epilogue, self.flags, 0, *self.dims, *self.fparams)
+                          self.epilogue, self.flags, self.sm_margin, *self.dims, *self.fparams)
 
 
 def pack_blob(descs):
@@ -53,15 +54,17 @@ def unpack_blob(data):
     for i in range(n):
         f = _DESC.unpack_from(data, _HEADER.size + i * _DESC.size)
         out.append(KernelDesc(f[0].split(b"\0")[0].decode(), f[1], f[2], f[3], f[4], f[5],
-                              f[7:13], f[13:15]))
+                              f[7:13], f[13:15], sm_margin=f[6]))
     return version, out
 
 
 def gemm(name, M, N, K, in_dtype=BF16, epilogue=EPI_NONE, accumulate=False, bias=False,
-         lda=0, ldb=0, ldc=0):
-    """lda/ldb/ldc: row pitches in elements (0 = dense)."""
+         lda=0, ldb=0, ldc=0, sm_margin=0):
+    """lda/ldb/ldc: row pitches in elements (0 = dense); sm_margin: SMs the
+    persistent kernel leaves free (for a collective running beside it)."""
     flags = (FLAG_ACCUMULATE if accumulate else 0) | (FLAG_BIAS if bias else 0)
-    return KernelDesc(name, OP_GEMM, in_dtype, F32, epilogue, flags, (M, N, K, lda, ldb, ldc))
+    return KernelDesc(name, OP_GEMM, in_dtype, F32, epilogue, flags, (M, N, K, lda, ldb, ldc),
+                      sm_margin=sm_margin)
 
 
 def softmax(name, rows, cols, neg_inf_init=False):

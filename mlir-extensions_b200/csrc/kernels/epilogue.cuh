@@ -17,6 +17,19 @@ __device__ __forceinline__ float silu_chain(float x) {
   return __fmul_rn(s, x);
 }
 
+// Tensor-core path only: the same function with the hardware exp2 / reciprocal
+// approximations (relative error ~1e-6, far inside the 1e-3 Frobenius budget of
+// the 16-bit GEMM); a quarter of the instructions of silu_chain.
+__device__ __forceinline__ float silu_fast(float x) {
+  return __fdividef(x, 1.0f + __expf(-x));
+}
+
+__device__ __forceinline__ float apply_epilogue_fast(float v, int epilogue) {
+  if (epilogue == kEpiRelu) return relu_ugt(v);
+  if (epilogue == kEpiSilu) return silu_fast(v);
+  return v;
+}
+
 __device__ __forceinline__ float apply_epilogue(float v, int epilogue) {
   if (epilogue == kEpiRelu) return relu_ugt(v);
   if (epilogue == kEpiSilu) return silu_chain(v);

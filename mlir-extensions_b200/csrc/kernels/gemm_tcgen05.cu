@@ -326,7 +326,9 @@ cudaError_t launch_gemm_tcgen05(const GemmProblem &g, unsigned *status, cudaStre
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
 
-  int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  int usable = sm_count() - (g.sm_margin > 0 ? g.sm_margin : 0);
+  if (usable < 1) usable = 1;
+  int grid = p.num_tiles < usable ? p.num_tiles : usable;
   gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   return cudaGetLastError();
 }

@@ -25,6 +25,7 @@
 #include "tcgen05_host.h"
 #include "tcgen05_ptx.cuh"
 
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -40,7 +41,6 @@ constexpr int BN = 256;       // tile columns (UMMA N)
 constexpr int BN_HALF = 128;  // columns of B each CTA loads
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KB
@@ -48,7 +48,9 @@ constexpr int B_BOX_BYTES = BK * 64 * 2;         // 8 KB: 64 k x 64 columns
 constexpr int B_STAGE_BYTES = BK * BN_HALF * 2;  // 16 KB = two boxes
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_CHUNK_BYTES = 32 * 32 * 4;              // 32 rows x 32 f32 columns
+constexpr int EPI_BYTES = 4 * 2 * EPI_CHUNK_BYTES;        // 4 epilogue warps, double buffered
+constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + EPI_BYTES + 1024 + 256; }
 
 struct PairParams {
   float *C;
@@ -61,6 +63,10 @@ struct PairParams {
   int epilogue;
   int accumulate;
   uint32_t idesc;
+  long long *stats;   // optional per-CTA cycle counters (nullptr = off), 8 per CTA
+  unsigned sleep_ns;  // back-off of the non-critical waits
+  int fast_math;      // silu through ex2.approx / rcp.approx
+  int prefetch_dist;  // k blocks the L2 prefetch runs ahead of the loads (0 = off)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -119,12 +125,15 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams &p, 
   mb = first_m + t % rows_in_band;
 }
 
+template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, const PairParams p) {
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_c, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t epi_base = smem_base + STAGES * STAGE_BYTES;  // 1024-byte aligned
+  const uint32_t bars = epi_base + EPI_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
@@ -132,7 +141,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 2 * NUM_ACC);
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(
-      smem_aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * NUM_ACC));
+      smem_aligned + STAGES * STAGE_BYTES + EPI_BYTES + 8 * (2 * STAGES + 2 * NUM_ACC));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -173,17 +182,50 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long t_begin = clock64(), w_empty = 0, w_issue = 0;
+      // L2 prefetch cursor: runs `prefetch_dist` k blocks ahead of the load cursor
+      // over the same (tile, k block) sequence.  Clusters that share a row or
+      // column block walk k in step, so without it every stage waits for the one
+      // DRAM miss they all share.
+      int pf_tile = cluster_id, pf_kb = 0, pf_row0 = 0, pf_col0 = 0, pf_credit = 0;
+      if (p.prefetch_dist > 0 && pf_tile < p.num_tiles) {
+        int mb, nb;
+        pair_tile_coords(pf_tile, p, mb, nb);
+        pf_row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
+        pf_col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
+        pf_credit = p.prefetch_dist;  // k blocks the cursor may still advance
+      }
+      auto prefetch_step = [&]() {
+        if (pf_tile >= p.num_tiles) return;
+        tma_prefetch_2d(&tmap_a, pf_kb * BK, pf_row0);
+        tma_prefetch_2d(&tmap_b, pf_col0, pf_kb * BK);
+        tma_prefetch_2d(&tmap_b, pf_col0 + 64, pf_kb * BK);
+        if (++pf_kb == p.k_blocks) {
+          pf_kb = 0;
+          pf_tile += num_clusters;
+          if (pf_tile < p.num_tiles) {
+            int mb, nb;
+            pair_tile_coords(pf_tile, p, mb, nb);
+            pf_row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
+            pf_col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
+          }
+        }
+      };
+      for (; pf_credit > 0; --pf_credit) prefetch_step();
       for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
         int mb, nb;
         pair_tile_coords(tile, p, mb, nb);
         const int row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
         const int col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+          const long long t0 = clock64();
+          if (!mbar_wait_relaxed(empty_bar(stage), phase ^ 1u, p.sleep_ns >> 2)) {
             report(p.status, kStatusTmaWaitTimeout);
             ok = false;
             break;
           }
+          w_empty += clock64() - t0;
+          const long long t1 = clock64();
           const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
           if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
@@ -191,8 +233,16 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tma_load_2d_pair(a_dst, &tmap_a, kb * BK, row0, leader_full);
           tma_load_2d_pair(b_dst, &tmap_b, col0, kb * BK, leader_full);
           tma_load_2d_pair(b_dst + B_BOX_BYTES, &tmap_b, col0 + 64, kb * BK, leader_full);
+          w_issue += clock64() - t1;
+          if (p.prefetch_dist > 0) prefetch_step();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+      }
+      if (p.stats) {
+        long long *st = p.stats + 8 * blockIdx.x;
+        st[3] = clock64() - t_begin;  // producer: total
+        st[4] = w_empty;              // ... of which waiting for a free stage
+        st[7] = w_issue;              // ... of which issuing the three tile loads
       }
       // Tail: every stage this CTA filled has been consumed (its commit arrived
       // here) before the CTA may exit — nothing is still reading this shared memory
@@ -210,20 +260,26 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      long long t_begin = clock64(), w_full = 0, w_acc = 0, w_mma = 0;
       for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
+        long long t0 = clock64();
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
           report(p.status, kStatusMmaWaitTimeout);
           break;
         }
+        w_acc += clock64() - t0;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          t0 = clock64();
           if (!mbar_wait(full_bar(stage), phase)) {
             report(p.status, kStatusMmaWaitTimeout);
             ok = false;
             break;
           }
+          w_full += clock64() - t0;
           tcgen05_fence_after();
+          t0 = clock64();
           const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
@@ -233,10 +289,18 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | k) ? 1u : 0u);
           }
           tcgen05_commit_pair(empty_bar(stage), 3);
+          w_mma += clock64() - t0;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) tcgen05_commit_pair(acc_full_bar(acc), 3);
         if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (p.stats) {
+        long long *st = p.stats + 8 * blockIdx.x;
+        st[0] = clock64() - t_begin;  // MMA thread: issue loop, total
+        st[1] = w_full;               // ... of which waiting for operands
+        st[2] = w_acc;                // ... of which waiting for a free accumulator
+        p.stats[8 * (blockIdx.x + 1) + 2] = w_mma;  // (peer's unused slot) issuing MMAs + commit
       }
     }
   } else {
@@ -244,46 +308,89 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int lane_group = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    long long t_begin = clock64(), w_accfull = 0;
     for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
       int mb, nb;
       pair_tile_coords(tile, p, mb, nb);
-      bool ok = mbar_wait(acc_full_bar(acc), acc_phase);
+      const long long t0 = clock64();
+      bool ok = mbar_wait_relaxed(acc_full_bar(acc), acc_phase, p.sleep_ns);
+      w_accfull += clock64() - t0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
         break;
       }
       tcgen05_fence_after();
-      const int row = mb * PAIR_M + static_cast<int>(cta_rank) * BM + lane_group * 32 + lane;
+      const int row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM + lane_group * 32;
+      const int row = row0 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BN;
       float *c_row = p.C + static_cast<size_t>(row) * p.ldc;
+      const uint32_t my_bufs = epi_base + (warp - 2) * 2 * EPI_CHUNK_BYTES;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
         const int col0 = nb * BN + c0;
-        if (row < p.M && col0 < p.N) {
+        if (p.accumulate) {
+          // C is also an input: per-thread row segments, read-modify-write in place
+          if (row < p.M && col0 < p.N) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int col = col0 + j;
-            if (col < p.N) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (p.accumulate) {
+            for (int j = 0; j < 32; j += 4) {
+              const int col = col0 + j;
+              if (col < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
                 const float4 c = *reinterpret_cast<const float4 *>(c_row + col);
                 v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+                if (p.bias) {
+                  const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
+                  v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                }
+                v.x = apply_epilogue(v.x, p.epilogue);
+                v.y = apply_epilogue(v.y, p.epilogue);
+                v.z = apply_epilogue(v.z, p.epilogue);
+                v.w = apply_epilogue(v.w, p.epilogue);
+                *reinterpret_cast<float4 *>(c_row + col) = v;
               }
-              if (p.bias) {
+            }
+          }
+        } else {
+          // Stage the 32x32 block in shared memory (128B-swizzled rows, so the 32
+          // lanes' 16-byte stores spread over all banks) and let TMA write whole
+          // 128-byte lines; rows / columns beyond M / N are clipped by the tensor map.
+          const uint32_t buf = my_bufs + ((c0 >> 5) & 1) * EPI_CHUNK_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            if (p.bias) {
+              const int col = col0 + j;
+              if (col < p.N) {
                 const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
               }
+            }
+            if (p.fast_math) {
+              v.x = apply_epilogue_fast(v.x, p.epilogue);
+              v.y = apply_epilogue_fast(v.y, p.epilogue);
+              v.z = apply_epilogue_fast(v.z, p.epilogue);
+              v.w = apply_epilogue_fast(v.w, p.epilogue);
+            } else {
               v.x = apply_epilogue(v.x, p.epilogue);
               v.y = apply_epilogue(v.y, p.epilogue);
               v.z = apply_epilogue(v.z, p.epilogue);
               v.w = apply_epilogue(v.w, p.epilogue);
-              *reinterpret_cast<float4 *>(c_row + col) = v;
             }
+            st_shared_v4(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4), v);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M && col0 < p.N) {
+            tma_store_2d(&tmap_c, buf, col0, row0);
+            tma_store_commit();
           }
         }
       }
@@ -291,6 +398,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (lane == 0) tma_store_wait_all<0>();  // all of this warp's tile stores have landed
+    if (p.stats && warp == 2 && lane == 0) {
+      long long *st = p.stats + 8 * blockIdx.x;
+      st[5] = clock64() - t_begin;  // epilogue warp: total
+      st[6] = w_accfull;            // ... of which waiting for an accumulator
     }
   }
 
@@ -317,9 +430,18 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   if (!gemm_tcgen05_supported(g)) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
+  static int stages = 6;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (const char *e = getenv("IMEX_GEMM_STAGES")) {
+      int v = atoi(e);
+      if (v == 4 || v == 5) stages = v;
+    }
+    auto set = [](const void *fn, int st) {
+      return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(st));
+    };
+    attr_err = stages == 4   ? set((const void *)gemm_tcgen05_2cta_kernel<4>, 4)
+               : stages == 5 ? set((const void *)gemm_tcgen05_2cta_kernel<5>, 5)
+                             : set((const void *)gemm_tcgen05_2cta_kernel<6>, 6);
   });
   if (attr_err != cudaSuccess) return attr_err;
 
@@ -329,6 +451,8 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   CUtensorMap ta, tb;
   if (!make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM, lda)) return cudaErrorNotSupported;
   if (!make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK, ldb)) return cudaErrorNotSupported;
+  CUtensorMap tc_;
+  if (!make_map_f32_out(&tc_, g.C, g.N, g.M, ldc)) return cudaErrorNotSupported;
 
   PairParams p;
   p.C = g.C;
@@ -349,13 +473,44 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   p.k_blocks = (p.K + BK - 1) / BK;
   p.epilogue = g.epilogue;
   p.accumulate = g.accumulate ? 1 : 0;
+  p.stats = nullptr;
+  static long long *stats_buf = nullptr;
+  const bool want_stats = getenv("IMEX_GEMM_STATS") != nullptr;  // development aid
+  if (want_stats) {
+    if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 148 * sizeof(long long));
+    p.stats = stats_buf;
+  }
+  p.sleep_ns = 0;
+  if (const char *e = getenv("IMEX_GEMM_SLEEP_NS")) p.sleep_ns = static_cast<unsigned>(atoi(e));
+  p.prefetch_dist = 0;
+  if (const char *e = getenv("IMEX_GEMM_PREFETCH")) p.prefetch_dist = atoi(e);
+  p.fast_math = 0;
+  if (const char *e = getenv("IMEX_GEMM_FAST_EPILOGUE")) p.fast_math = atoi(e);
   const uint32_t fmt = g.in_dtype == kBF16 ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(PAIR_M >> 4) << 24);
 
-  const int max_clusters = sm_count() / 2;
+  int usable = sm_count() - (g.sm_margin > 0 ? g.sm_margin : 0);
+  if (usable < 2) usable = 2;
+  const int max_clusters = usable / 2;
   const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
-  gemm_tcgen05_2cta_kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  const dim3 grid(2 * clusters), block(NUM_THREADS);
+  switch (stages) {
+  case 4: gemm_tcgen05_2cta_kernel<4><<<grid, block, smem_bytes(4), stream>>>(ta, tb, tc_, p); break;
+  case 5: gemm_tcgen05_2cta_kernel<5><<<grid, block, smem_bytes(5), stream>>>(ta, tb, tc_, p); break;
+  default: gemm_tcgen05_2cta_kernel<6><<<grid, block, smem_bytes(6), stream>>>(ta, tb, tc_, p); break;
+  }
+  if (want_stats && stats_buf) {
+    cudaStreamSynchronize(stream);
+    double a[8] = {0};
+    for (int c = 0; c < 2 * clusters; ++c)
+      for (int i = 0; i < 8; ++i) a[i] += static_cast<double>(stats_buf[8 * c + i]);
+    const double nl = clusters, nc = 2.0 * clusters;
+    fprintf(stderr,
+            "[gemm_2cta stats, mean cycles] mma total %.0f wait_full %.0f wait_acc %.0f | "
+            "producer total %.0f wait_empty %.0f issue %.0f | epilogue total %.0f wait_acc_full %.0f\n",
+            a[0] / nl, a[1] / nl, a[2] / nl, a[3] / nc, a[4] / nc, a[7] / nc, a[5] / nc, a[6] / nc);
+  }
   return cudaGetLastError();
 }
 

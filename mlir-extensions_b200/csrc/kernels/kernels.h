@@ -30,6 +30,7 @@ struct GemmProblem {
   int in_dtype;       // DType
   int epilogue;       // Epilogue
   bool accumulate;    // C is read as the initial value
+  int sm_margin = 0;  // SMs the persistent kernels leave unused
 };
 
 // f32 or 16-bit inputs, one thread per 4x4 outputs, k ascending with

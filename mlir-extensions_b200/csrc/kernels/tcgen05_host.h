@@ -44,6 +44,21 @@ inline bool make_map(CUtensorMap *m, const void *base, int in_dtype, int64_t inn
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D row-major [rows, cols] f32 tensor with row pitch `pitch` elements, box
+// [32 rows, 32 cols] (128 bytes wide), 128B swizzle: the store side of the GEMM.
+inline bool make_map_f32_out(CUtensorMap *m, const void *base, int64_t cols, int64_t rows,
+                             int64_t pitch) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch > 0 ? pitch : cols) * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 inline int sm_count() {
   static int n = [] {
     int dev = 0, v = 0;

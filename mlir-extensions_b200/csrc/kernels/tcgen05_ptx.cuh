@@ -45,6 +45,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return true;
 }
+// Bounded wait for warps that are not on the critical path (epilogue waiting
+// for an accumulator, producer waiting for a free stage): sleeps between polls
+// so that idle warps do not burn issue slots and power.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, unsigned sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+  }
+  return true;
+}
 // The status word lives in mapped host memory: a plain store, no atomics.
 __device__ __forceinline__ void report(unsigned *status, unsigned code) {
   *reinterpret_cast<volatile unsigned *>(status) = code;
@@ -57,6 +69,37 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       "{%2, %3}], [%4];" ::"r"(dst),
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+// Ask L2 to fetch a tile ahead of the load that will need it (no smem, no barrier).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x),
+               "r"(y)
+               : "memory");
+}
+// Tile store smem -> global (bulk async group); out-of-range parts are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// at most N store groups of this thread still reading shared memory
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// generic-proxy writes to shared memory become visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -277,6 +277,7 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     g.in_dtype = static_cast<int>(d.in_dtype);
     g.epilogue = static_cast<int>(d.epilogue);
     g.accumulate = acc;
+    g.sm_margin = static_cast<int>(d.sm_margin);
     if (g.M < 0 || g.N < 0 || g.K < 0) throw std::runtime_error("gpuLaunchKernel: negative gemm dims");
     if ((g.lda && g.lda < g.K) || (g.ldb && g.ldb < g.N) || (g.ldc && g.ldc < g.N))
       throw std::runtime_error("gpuLaunchKernel: gemm row pitch smaller than the row");
