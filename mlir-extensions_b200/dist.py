@@ -101,9 +101,15 @@ class RowShardedGemm:
         self.device = device
         self.comm_stream = torch.cuda.Stream(device=device) if world > 1 else None
         elt = torch.bfloat16 if in_dtype == B.BF16 else torch.float16
-        self.slab_bufs = None
+        # two sets of slab buffers: the broadcast of call i+1 may run while the GEMMs of
+        # call i still read theirs, so back-to-back calls hide the replication entirely
+        self.slab_sets = None
+        self.calls = 0
+        self.done_events = [None, None]
         if world > 1:
-            self.slab_bufs = [torch.empty((k, w), dtype=elt, device=device) for _, w in self.slabs]
+            self.slab_sets = [[torch.empty((k, w), dtype=elt, device=device) for _, w in self.slabs]
+                              for _ in range(2)]
+            self.slab_bufs = self.slab_sets[0]
         self.kernels = []
         for j, (c0, w) in enumerate(self.slabs):
             ldb = w if world > 1 else 0
@@ -111,20 +117,38 @@ class RowShardedGemm:
                 f"row_sharded_gemm_slab{j}", self.rows, w, k, in_dtype, epilogue,
                 ldb=ldb, ldc=n if w != n else 0, sm_margin=self.margin)))
 
-    def __call__(self, a_shard, b_full, c_shard):
+    def __call__(self, a_shard, b_full, c_shard, b_ready=None):
         """a_shard [rows,k], c_shard [rows,n] on this rank; b_full [k,n] valid on `src`
-        (a scratch tensor of that shape elsewhere).  Enqueues on the current stream."""
+        (a scratch tensor of that shape elsewhere).  Enqueues on the current stream.
+
+        b_ready: None  -> the broadcast waits for everything queued so far on the
+                          current stream (b_full may be produced there); safe default;
+                 True  -> b_full is already complete in memory (resident weights): the
+                          broadcast starts at once and overlaps earlier GEMMs;
+                 event -> the broadcast waits for that CUDA event only."""
         torch = self.torch
         if self.world == 1:
             self.sess.launch(self.kernels[0], [a_shard.data_ptr(), b_full.data_ptr(),
                                                c_shard.data_ptr()], wait=False)
             return 1
         cur = torch.cuda.current_stream()
-        self.comm_stream.wait_stream(cur)  # earlier GEMMs are done with the slab buffers
-        works = replicate_slabs(b_full, self.slab_bufs, self.slabs, self.src,
-                                self.rank == self.src, self.comm_stream)
-        for (c0, w), buf, work, kern in zip(self.slabs, self.slab_bufs, works, self.kernels):
+        which = self.calls & 1
+        self.calls += 1
+        bufs = self.slab_bufs = self.slab_sets[which]
+        if b_ready is None:
+            self.comm_stream.wait_stream(cur)
+        elif b_ready is not True:
+            self.comm_stream.wait_event(b_ready)
+        # this set of slab buffers was last read by the GEMMs of two calls ago
+        if self.done_events[which] is not None:
+            self.comm_stream.wait_event(self.done_events[which])
+        works = replicate_slabs(b_full, bufs, self.slabs, self.src, self.rank == self.src,
+                                self.comm_stream)
+        for (c0, w), buf, work, kern in zip(self.slabs, bufs, works, self.kernels):
             work.wait()  # the current stream waits for this slab only
             self.sess.launch(kern, [a_shard.data_ptr(), buf.data_ptr(),
                                     c_shard.data_ptr() + 4 * c0], wait=False)
+        done = torch.cuda.Event()
+        done.record(cur)
+        self.done_events[which] = done
         return len(self.slabs)
