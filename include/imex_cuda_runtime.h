@@ -122,6 +122,24 @@ int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent);
  * 8 middle-third average. */
 float imexStat(int which, const float *values, size_t n);
 
+/* Full sum of n f32 values without any allocation — no counterpart in the
+ * reference (its runtime always allocates through the driver).
+ *   *y = (accumulate ? *y : 0) + sum x[0..n)       x, y: device pointers
+ * Same kernels and result as an IMEX_OP_REDUCE_ALL launch, but the block
+ * partials live in a 256 KiB array built into the library instead of a
+ * cudaMalloc'ed buffer, for callers that must not let a library allocate:
+ * hosts that hand out all device memory themselves, loops that cannot afford
+ * cudaMalloc's device-wide synchronisation.  Limit: 65536 partials, i.e.
+ * n <= 65536 * 16384 = 1,073,741,824 elements; larger n is refused.
+ * cudaStream: a cudaStream_t (NULL = default stream); the launch is
+ * asynchronous on it.  The first call made with a given device current looks
+ * up the array's device address and should come before any stream capture.
+ * The array is shared by all calls and keeps the last call's contents: calls
+ * that may overlap on the GPU must be ordered by the caller.
+ * Returns 0, or: 1 invalid argument, 2 n beyond the limit, 3 address look-up
+ * failed, 4 launch failed (a message goes to stderr; nothing is aborted). */
+int imexReduceAllF32Static(const float *x, float *y, int64_t n, int accumulate, void *cudaStream);
+
 #ifdef __cplusplus
 }
 #endif

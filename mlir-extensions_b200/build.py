@@ -28,6 +28,7 @@ RUNTIME_SOURCES = [
     "kernels/gemm_tcgen05_2cta.cu",
     "kernels/softmax.cu",
     "kernels/reduce.cu",
+    "kernels/reduce_all_static.cu",
     "kernels/transpose.cu",
     "kernels/eltwise_fill.cu",
     "runtime/cuda_runtime_wrappers.cu",

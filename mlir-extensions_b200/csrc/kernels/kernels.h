@@ -62,6 +62,7 @@ cudaError_t launch_reduce_leading_f32(const float *x, float *y, int64_t lead, in
                                       bool accumulate, cudaStream_t stream);
 // *Y = (acc ? *Y : 0) + sum X.  `partials` is scratch for reduce_all_partials() floats.
 int64_t reduce_all_partials(int64_t n);
+int64_t reduce_all_block_elems();  // elements summed into one partial
 cudaError_t launch_reduce_all_f32(const float *x, float *y, int64_t n, bool accumulate,
                                   float *partials, cudaStream_t stream);
 

@@ -175,6 +175,8 @@ cudaError_t launch_reduce_leading_f32(const float *x, float *y, int64_t lead, in
   return cudaGetLastError();
 }
 
+int64_t reduce_all_block_elems() { return ALL_PER_BLOCK; }
+
 int64_t reduce_all_partials(int64_t n) {
   int64_t b = (n + ALL_PER_BLOCK - 1) / ALL_PER_BLOCK;
   return b < 1 ? 1 : b;
