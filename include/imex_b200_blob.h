@@ -45,6 +45,7 @@ extern "C" {
  *   TRANSPOSE2D     X[rows,cols], Y[cols,rows]           dims = {rows, cols}
  *   TRANSPOSE3D     X[d0,d1,d2], Y[permuted]             dims = {d0,d1,d2,p0,p1,p2}
  *   ELTWISE         X[n], Y[n] with `epilogue` applied   dims = {n}
+ *                   (in_dtype != out_dtype: arith.extf / arith.truncf, no epilogue)
  *   FILL_UNIFORM    Y[n]  dims = {n, seed, first}; fparams = {lo, hi}
  *   FILL_NORMAL     Y[n]  dims = {n, seed, first}; fparams = {mean, stddev}
  */

@@ -98,6 +98,11 @@ def eltwise(name, n, epilogue):
     return KernelDesc(name, OP_ELTWISE, F32, F32, epilogue, 0, (n,))
 
 
+def convert(name, n, in_dtype, out_dtype):
+    """arith.extf / arith.truncf between f32 and bf16 / f16."""
+    return KernelDesc(name, OP_ELTWISE, in_dtype, out_dtype, EPI_NONE, 0, (n,))
+
+
 def fill_uniform(name, n, dtype, seed, lo, hi, first=0):
     return KernelDesc(name, OP_FILL_UNIFORM, dtype, dtype, 0, 0, (n, seed, first), (lo, hi))
 

@@ -5,6 +5,7 @@
 Outputs (git-ignored, shipped with the working tree):
     lib/libimex_cuda_runtime.so   GPU runtime-wrapper C ABI + all CUDA kernels
     lib/libimex_runner_utils.so   host runner utilities (fill / print / allclose / ...)
+    bin/imex-b200-runner          MLIR-text front end: recognises the hot-path ops and runs them
 Objects are rebuilt only when a source or header is newer.
 """
 import os
@@ -35,6 +36,8 @@ RUNTIME_SOURCES = [
     "runtime/stats.cpp",
 ]
 UTILS_SOURCES = ["utils/runner_utils.cpp"]
+FRONTEND_SOURCES = ["frontend/mlir_text.cpp", "frontend/recognise.cpp", "frontend/runner_main.cpp"]
+BIN = os.path.join(PKG, "bin")
 
 
 def _nvcc():
@@ -92,6 +95,14 @@ def build(force=False, verbose=False):
         ut = os.path.join(LIB, "libimex_runner_utils.so")
         if force or _stale(ut, objs):
             _run(["/usr/bin/g++", "-shared", "-o", ut] + objs, verbose)
+    if all(os.path.exists(os.path.join(CSRC, s)) for s in FRONTEND_SOURCES):
+        os.makedirs(BIN, exist_ok=True)
+        objs = _compile(FRONTEND_SOURCES, force, verbose)
+        exe = os.path.join(BIN, "imex-b200-runner")
+        if force or _stale(exe, objs + [rt]):
+            _run(["/usr/bin/g++", "-o", exe] + objs +
+                 ["-L" + LIB, "-limex_cuda_runtime", "-limex_runner_utils",
+                  "-Wl,-rpath,$ORIGIN/../lib", "-ldl", "-lpthread"], verbose)
     return rt
 
 

@@ -1,0 +1,263 @@
+// Classification of linalg ops; see recognise.h.
+#include "recognise.h"
+
+#include <algorithm>
+#include <sstream>
+
+namespace imex {
+namespace fe {
+
+const char *kindName(Kind k) {
+  switch (k) {
+  case Kind::Unknown: return "unknown";
+  case Kind::Matmul: return "matmul";
+  case Kind::Relu: return "relu";
+  case Kind::Sigmoid: return "sigmoid";
+  case Kind::Mul: return "mul";
+  case Kind::RowMax: return "row_max";
+  case Kind::SubRowBcast: return "sub_row_broadcast";
+  case Kind::Exp: return "exp";
+  case Kind::RowSum: return "row_sum";
+  case Kind::DivRowBcast: return "div_row_broadcast";
+  case Kind::Transpose: return "transpose";
+  case Kind::ReduceLeading: return "reduce_leading";
+  case Kind::ReduceAll: return "reduce_all";
+  case Kind::ExtF: return "extf";
+  case Kind::TruncF: return "truncf";
+  case Kind::Fill: return "fill";
+  }
+  return "?";
+}
+
+namespace {
+
+std::string fmtConst(double v) {
+  std::ostringstream os;
+  os << "c(" << v << ")";
+  return os.str();
+}
+
+// Canonical expression of every yielded value of a linalg.generic body.
+// Block arguments become in0.. / out0..; captured scalars become c(value);
+// commutative ops sort their operands; tensor.from_elements / extract pairs on
+// scalars are looked through (benchmarks/reduce/reduce_gpu.mlir.in:11-18).
+std::vector<std::string> bodyExpressions(const Op &op, const ConstantTable &constants,
+                                         std::string &why) {
+  std::map<std::string, std::string> env;
+  const Block &b = *op.body;
+  const size_t nIn = op.ins.size();
+  for (size_t i = 0; i < b.args.size(); ++i)
+    env[b.args[i]] = (i < nIn ? "in" : "out") + std::to_string(i < nIn ? i : i - nIn);
+  auto val = [&](const std::string &name) -> std::string {
+    auto it = env.find(name);
+    if (it != env.end()) return it->second;
+    auto c = constants.find(name);
+    if (c != constants.end()) return fmtConst(c->second);
+    why = "body uses value " + name + " that is neither a block argument nor a known constant";
+    return "?";
+  };
+  std::vector<std::string> yields;
+  for (auto &o : b.ops) {
+    const std::string &n = o->name;
+    if (n == "linalg.yield") {
+      for (auto &v : o->operands) yields.push_back(val(v));
+      continue;
+    }
+    std::string e;
+    auto fn = n.substr(n.find('.') + 1);
+    if (n == "arith.constant") {
+      e = fmtConst(o->isRaw[0] ? 0.0 : o->numbers[0]);
+    } else if (n == "linalg.index") {
+      e = "index" + std::to_string(o->intAttr);
+    } else if (n == "arith.cmpf" || n == "arith.cmpi") {
+      e = fn + "(" + o->predicate + "," + val(o->operands[0]) + "," + val(o->operands[1]) + ")";
+    } else if (n == "arith.select") {
+      e = "select(" + val(o->operands[0]) + "," + val(o->operands[1]) + "," + val(o->operands[2]) + ")";
+    } else if (n == "tensor.from_elements" || n == "tensor.extract") {
+      e = val(o->operands[0]);  // scalar <-> tensor<f32> round trip
+    } else if (o->operands.size() == 1) {
+      e = fn + "(" + val(o->operands[0]) + ")";
+    } else if (o->operands.size() == 2) {
+      std::string a = val(o->operands[0]), c = val(o->operands[1]);
+      if (fn == "maxf") fn = "maximumf";  // older spelling of the same op
+      const bool commutative = fn == "addf" || fn == "mulf" || fn == "maximumf" || fn == "addi" ||
+                               fn == "muli" || fn == "maxnumf";
+      if (commutative && c < a) std::swap(a, c);
+      e = fn + "(" + a + "," + c + ")";
+    } else {
+      why = "unsupported operation " + n + " in a linalg body";
+      e = "?";
+    }
+    for (auto &r : o->results) env[r] = e;
+  }
+  return yields;
+}
+
+bool mapIs(const AffineMap &m, std::initializer_list<int> dims) {
+  if (m.results.size() != dims.size()) return false;
+  size_t i = 0;
+  for (int d : dims) {
+    const MapResult &r = m.results[i++];
+    if (d < 0) {  // -1: constant 0
+      if (!r.isConst || r.value != 0) return false;
+    } else if (r.isConst || r.value != d) {
+      return false;
+    }
+  }
+  return true;
+}
+
+bool allParallel(const Op &op) {
+  return std::all_of(op.iterators.begin(), op.iterators.end(),
+                     [](const std::string &s) { return s == "parallel"; });
+}
+
+// (d0,d1)->(d0,0) or (d0,d1)->(d0): one value per row
+bool isRowVectorMap(const AffineMap &m) {
+  return m.numDims == 2 && (mapIs(m, {0, -1}) || mapIs(m, {0}));
+}
+
+} // namespace
+
+Classified classify(const Op &op, const ConstantTable &constants) {
+  Classified c;
+  if (op.name == "linalg.matmul") {
+    c.kind = Kind::Matmul;
+    c.expr = "linalg.matmul";
+    return c;
+  }
+  if (op.name == "linalg.fill") {
+    c.kind = Kind::Fill;
+    return c;
+  }
+  if (op.name == "linalg.transpose") {
+    c.kind = Kind::Transpose;
+    for (auto &g : op.reassociation) c.perm.push_back(static_cast<int>(g[0]));
+    return c;
+  }
+  if (op.name != "linalg.generic" || !op.body) {
+    c.why = "not a linalg structured op";
+    return c;
+  }
+  if (op.maps.size() != op.ins.size() + op.outs.size()) {
+    c.why = "indexing_maps do not match the operand count";
+    return c;
+  }
+  std::string why;
+  std::vector<std::string> ys = bodyExpressions(op, constants, why);
+  if (!why.empty() || ys.empty()) {
+    c.why = why.empty() ? "empty body" : why;
+    return c;
+  }
+  const std::string &y = ys[0];
+  c.expr = y;
+  const size_t nIn = op.ins.size(), nOut = op.outs.size();
+  const int nd = op.maps[0].numDims;
+  const AffineMap &outMap = op.maps[nIn];
+
+  // ---- contractions ------------------------------------------------------
+  if (nd == 3 && nIn == 2 && nOut == 1 && op.iterators.size() == 3 &&
+      op.iterators[0] == "parallel" && op.iterators[1] == "parallel" &&
+      op.iterators[2] == "reduction" && mapIs(op.maps[0], {0, 2}) && mapIs(op.maps[1], {2, 1}) &&
+      mapIs(outMap, {0, 1})) {
+    if (y == "addf(mulf(in0,in1),out0)" || y == "addf(mulf(extf(in0),extf(in1)),out0)") {
+      c.kind = Kind::Matmul;
+      return c;
+    }
+    c.why = "matmul-shaped generic with body " + y + " (only f32 mulf/addf is mapped to a GEMM)";
+    return c;
+  }
+
+  // ---- reductions ----------------------------------------------------------
+  const bool hasReduction = !allParallel(op);
+  if (hasReduction) {
+    if (nd == 2 && nIn == 1 && op.iterators[0] == "parallel" && op.iterators[1] == "reduction" &&
+        op.maps[0].isIdentity() && isRowVectorMap(outMap)) {
+      if (y == "addf(in0,out0)") {
+        c.kind = Kind::RowSum;
+        return c;
+      }
+      if (y == "maximumf(in0,out0)") {
+        c.kind = Kind::RowMax;
+        return c;
+      }
+      if (y == "select(cmpf(ogt,in0,out0),in0,out0)" || y == "select(cmpf(ogt,out0,in0),out0,in0)") {
+        c.kind = Kind::RowMax;
+        c.rowMaxOgt = true;
+        return c;
+      }
+    }
+    if (y == "addf(in0,out0)" && nIn == 1 && nOut == 1) {
+      bool allRed = std::all_of(op.iterators.begin(), op.iterators.end(),
+                                [](const std::string &s) { return s == "reduction"; });
+      if (allRed && outMap.results.empty() && op.maps[0].isIdentity()) {
+        c.kind = Kind::ReduceAll;
+        return c;
+      }
+      // leading dim: in (d0..dn-1) -> (dn-1, d0, .., dn-2), out identity on the parallel dims,
+      // last iterator is the reduction (benchmarks/reduce/reduce_gpu.mlir.in:1-2)
+      bool lastRed = op.iterators.back() == "reduction";
+      bool outIdent = static_cast<int>(outMap.results.size()) == nd - 1;
+      for (int i = 0; outIdent && i < nd - 1; ++i)
+        outIdent = !outMap.results[i].isConst && outMap.results[i].value == i;
+      bool inRot = static_cast<int>(op.maps[0].results.size()) == nd;
+      if (inRot) {
+        inRot = !op.maps[0].results[0].isConst && op.maps[0].results[0].value == nd - 1;
+        for (int i = 1; inRot && i < nd; ++i)
+          inRot = !op.maps[0].results[i].isConst && op.maps[0].results[i].value == i - 1;
+      }
+      if (lastRed && outIdent && inRot) {
+        c.kind = Kind::ReduceLeading;
+        return c;
+      }
+    }
+    c.why = "reduction with maps/body that match no hot-path reduction (body " + y + ")";
+    return c;
+  }
+
+  // ---- elementwise / permutations -------------------------------------------
+  if (y == "in0" && nIn == 1 && nOut == 1) {
+    // pure data movement: out[outMap(d)] = in[inMap(d)]
+    const AffineMap &inMap = op.maps[0];
+    if (inMap.results.size() == outMap.results.size() &&
+        static_cast<int>(inMap.results.size()) == nd) {
+      // position of loop dim d in the input / output
+      std::vector<int> inPos(nd, -1), outPos(nd, -1);
+      for (int i = 0; i < nd; ++i) {
+        if (inMap.results[i].isConst || outMap.results[i].isConst) {
+          c.why = "broadcasting copy";
+          return c;
+        }
+        inPos[inMap.results[i].value] = i;
+        outPos[outMap.results[i].value] = i;
+      }
+      c.perm.assign(nd, 0);
+      for (int d = 0; d < nd; ++d) c.perm[outPos[d]] = inPos[d];
+      c.kind = Kind::Transpose;
+      return c;
+    }
+  }
+  bool identityAll = true;
+  for (auto &m : op.maps) identityAll = identityAll && m.isIdentity();
+  if (identityAll && nIn == 1) {
+    if (y == "select(cmpf(ugt,in0,c(0)),in0,c(0))") { c.kind = Kind::Relu; return c; }
+    if (y == "divf(c(1),addf(c(1),exp(negf(in0))))") { c.kind = Kind::Sigmoid; return c; }
+    if (y == "exp(in0)") { c.kind = Kind::Exp; return c; }
+    if (y == "extf(in0)") { c.kind = Kind::ExtF; return c; }
+    if (y == "truncf(in0)") { c.kind = Kind::TruncF; return c; }
+  }
+  if (identityAll && nIn == 2 && y == "mulf(in0,in1)") {
+    c.kind = Kind::Mul;
+    return c;
+  }
+  if (nd == 2 && nIn == 2 && op.maps[0].isIdentity() && isRowVectorMap(op.maps[1]) &&
+      outMap.isIdentity()) {
+    if (y == "subf(in0,in1)") { c.kind = Kind::SubRowBcast; return c; }
+    if (y == "divf(in0,in1)") { c.kind = Kind::DivRowBcast; return c; }
+  }
+  c.why = "elementwise body " + y + " matches no hot-path op";
+  return c;
+}
+
+} // namespace fe
+} // namespace imex

@@ -76,6 +76,20 @@ fill_normal_kernel(T *__restrict__ y, int64_t n, uint64_t seed, int64_t first, f
   }
 }
 
+// arith.extf / arith.truncf as a standalone generic (test/PlaidML/CppEdsl.DotF16_AccF32.mlir:22-47):
+// 16-bit -> f32 is exact, f32 -> 16-bit rounds to nearest even.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+convert_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, int64_t n) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v;
+    if constexpr (sizeof(TIn) == 4) v = x[i];
+    else v = static_cast<float>(x[i]);
+    y[i] = from_f32<TOut>(v);
+  }
+}
+
 unsigned grid_for(int64_t n) {
   int64_t b = (n + 255) / 256;
   if (b > 148 * 32) b = 148 * 32;
@@ -89,6 +103,21 @@ cudaError_t launch_eltwise_f32(const float *x, float *y, int64_t n, int epilogue
   if (n <= 0) return cudaSuccess;
   int vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   eltwise_kernel<<<grid_for((n + 3) / 4), 256, 0, stream>>>(x, y, n, epilogue, vec_ok);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_convert(const void *x, void *y, int64_t n, int in_dtype, int out_dtype,
+                           cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  const unsigned g = grid_for(n);
+#define IMEX_CONVERT(TI, TO) \
+  convert_kernel<TI, TO><<<g, 256, 0, stream>>>(static_cast<const TI *>(x), static_cast<TO *>(y), n)
+  if (in_dtype == kF32 && out_dtype == kF16) IMEX_CONVERT(float, __half);
+  else if (in_dtype == kF32 && out_dtype == kBF16) IMEX_CONVERT(float, __nv_bfloat16);
+  else if (in_dtype == kF16 && out_dtype == kF32) IMEX_CONVERT(__half, float);
+  else if (in_dtype == kBF16 && out_dtype == kF32) IMEX_CONVERT(__nv_bfloat16, float);
+  else return cudaErrorInvalidValue;
+#undef IMEX_CONVERT
   return cudaGetLastError();
 }
 

@@ -77,6 +77,10 @@ cudaError_t launch_transpose3d_b32(const void *x, void *y, const int64_t dims[3]
 cudaError_t launch_eltwise_f32(const float *x, float *y, int64_t n, int epilogue,
                                cudaStream_t stream);
 
+// Y[i] = convert(X[i]): f32 <-> bf16 / f16 (arith.extf / arith.truncf generics)
+cudaError_t launch_convert(const void *x, void *y, int64_t n, int in_dtype, int out_dtype,
+                           cudaStream_t stream);
+
 // Seeded synthetic inputs.  uniform: lo + (hi-lo)*u24(seed, first+i), the same
 // integer hash as the CPU oracle (bit-identical in f32).  normal: Box-Muller.
 cudaError_t launch_fill_uniform(void *y, int64_t n, int dtype, uint64_t seed, int64_t first,

@@ -123,6 +123,30 @@ softmax_block_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t
   }
 }
 
+// Rows of at most 64 elements (the reference's golden tests: 10x20): one thread
+// per row walking the row in order, so the row sum is the very sequence of
+// f32 additions the loop nest performs; exp is evaluated in f64 and rounded
+// once, which agrees with glibc's correctly-rounded-in-practice expf.  The
+// printed six digits of test/PlaidML/OpTest.Softmax.mlir:98-109 depend on it.
+__global__ void __launch_bounds__(128)
+softmax_tiny_rows_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int cols,
+                         float max_init) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const float *xr = x + row * cols;
+  float *yr = y + row * cols;
+  float e[64];
+  float m = max_init;
+  for (int c = 0; c < cols; ++c) m = fmaxf(m, xr[c]);
+  float s = 0.0f;
+#pragma unroll 1
+  for (int c = 0; c < cols; ++c) {
+    e[c] = static_cast<float>(exp(static_cast<double>(__fsub_rn(xr[c], m))));
+    s = __fadd_rn(e[c], s);
+  }
+  for (int c = 0; c < cols; ++c) yr[c] = __fdiv_rn(e[c], s);
+}
+
 template <int V>
 cudaError_t launch_warp(const float *x, float *y, int64_t rows, int cols, float max_init,
                         cudaStream_t stream) {
@@ -138,6 +162,11 @@ cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t c
                                bool neg_inf_init, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return cudaSuccess;
   const float max_init = neg_inf_init ? -INFINITY : -FLT_MAX;
+  if (cols <= 64 && rows <= 65536) {
+    softmax_tiny_rows_kernel<<<static_cast<unsigned>((rows + 127) / 128), 128, 0, stream>>>(
+        x, y, rows, static_cast<int>(cols), max_init);
+    return cudaGetLastError();
+  }
   const bool vec_ok = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                       ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
   if (vec_ok && cols <= 128) return launch_warp<1>(x, y, rows, (int)cols, max_init, stream);

@@ -361,6 +361,14 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
   }
   case IMEX_OP_ELTWISE:
     need(2);
+    if (d.in_dtype != d.out_dtype) {  // extf / truncf
+      if (d.epilogue != IMEX_EPI_NONE)
+        throw std::runtime_error("gpuLaunchKernel: a converting eltwise kernel takes no epilogue");
+      s->last_kernel = "convert";
+      err = imex::launch_convert(ptrs[0], ptrs[1], d.dims[0], static_cast<int>(d.in_dtype),
+                                 static_cast<int>(d.out_dtype), s->stream);
+      break;
+    }
     if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: eltwise is f32 only");
     s->last_kernel = "eltwise";
     err = imex::launch_eltwise_f32(static_cast<const float *>(ptrs[0]), static_cast<float *>(ptrs[1]),
