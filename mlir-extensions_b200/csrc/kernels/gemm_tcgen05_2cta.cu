@@ -2,23 +2,30 @@
 //
 // Same op, epilogues and reference citations as gemm_tcgen05.cu.  Two CTAs of a
 // 2-CTA cluster share one 256x256 output tile: CTA r owns rows [128r, 128r+128)
-// of it (its own 128-lane TMEM accumulator) and loads, per 64-wide k block,
-// its own 128x64 slice of A and HALF of the B block (64 x 128 columns).  The
-// pair's tensor cores read both halves of B from both CTAs' shared memory, so
-// every byte of B is fetched from L2 once per pair instead of once per CTA:
-// 32 KB per CTA and stage instead of 48 KB, which is what bounds the 1-CTA
-// kernel (the tensor pipe waits for smem fills).  There is no TMA multicast:
-// each CTA issues plain tile loads into its own shared memory; only the
-// completion barrier lives in the leader CTA.
+// of it (its own 128-lane TMEM accumulator, double buffered: 2 x 256 columns)
+// and loads, per k block of BKT elements, its own 128 x BKT slice of A and HALF
+// of the B block (BKT x 128 columns).  The pair's tensor cores read both halves
+// of B from both CTAs' shared memory, so every byte of B is fetched from L2
+// once per pair instead of once per CTA.  There is no TMA multicast: each CTA
+// issues plain tile loads into its own shared memory; only the completion
+// barrier lives in the leader CTA.
 //
 //   warp 0 (both CTAs)   TMA producer: waits its own `empty[s]`, loads A and its
 //                        B half, completion bytes go to the LEADER's `full[s]`.
-//   warp 1 (leader only) waits `full[s]` (64 KB from both CTAs), issues 4 MMAs per
-//                        k block, tcgen05.commit multicast to `empty[s]` of both
-//                        CTAs; after the last k block commits to `acc_full[a]` of both.
-//   warps 2-5 (both)     epilogue on the CTA's own 128 rows: tcgen05.ld, + C0 / bias,
-//                        relu / silu, 128-bit stores; then arrive on the leader's
-//                        `acc_empty[a]` (8 arrivals: 4 warps x 2 CTAs).
+//   warp 1 (leader only) waits `full[s]`, issues BKT/16 MMAs per k block,
+//                        tcgen05.commit multicast to `empty[s]` of both CTAs; after
+//                        the last k block commits to `acc_full[a]` of both.
+//   warps 2-5 (both)     epilogue on the CTA's own 128 rows: tcgen05.ld, + bias,
+//                        relu / silu, 128B-swizzled smem staging, TMA tile stores
+//                        (C read-modify-written with 128-bit accesses when it is an
+//                        input); then arrive on the leader's `acc_empty[a]`
+//                        (8 arrivals: 4 warps x 2 CTAs).
+//
+// Default: 3 stages of BKT = 128 (64 KB per CTA and stage).  The MMA thread pays
+// a fixed cost per k block (barrier wait, fence, commit); with 64-wide blocks
+// that cost left the tensor pipe idle 12 % of the cycles even for a single pair
+// running alone, with 128-wide blocks 6 %.  In-kernel cycle counters (template
+// flag STATS, IMEX_GEMM_STATS=1) report where each role waits.
 // Waits are bounded; a wait that runs out records a status code and the role
 // leaves its loop, after which the pair drains, syncs and frees TMEM.
 #include "epilogue.cuh"
@@ -39,18 +46,21 @@ constexpr int BM = 128;       // rows per CTA
 constexpr int PAIR_M = 256;   // rows per CTA pair (UMMA M)
 constexpr int BN = 256;       // tile columns (UMMA N)
 constexpr int BN_HALF = 128;  // columns of B each CTA loads
-constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = 512;
-constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KB
-constexpr int B_BOX_BYTES = BK * 64 * 2;         // 8 KB: 64 k x 64 columns
-constexpr int B_STAGE_BYTES = BK * BN_HALF * 2;  // 16 KB = two boxes
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+// BKT = k elements per stage: 64 (one 128-byte swizzle row of A per box) or 128.
+constexpr int A_BOX_BYTES = BM * 64 * 2;                                // 16 KB: 128 rows x 64 k
+__host__ __device__ constexpr int a_stage_bytes(int bkt) { return BM * bkt * 2; }           // bkt/64 boxes
+__host__ __device__ constexpr int b_box_bytes(int bkt) { return bkt * 64 * 2; }             // bkt k x 64 columns
+__host__ __device__ constexpr int b_stage_bytes(int bkt) { return 2 * b_box_bytes(bkt); }   // this CTA's 128 columns
+__host__ __device__ constexpr int stage_bytes(int bkt) { return a_stage_bytes(bkt) + b_stage_bytes(bkt); }
 constexpr int NUM_THREADS = 192;
 constexpr int EPI_CHUNK_BYTES = 32 * 32 * 4;              // 32 rows x 32 f32 columns
 constexpr int EPI_BYTES = 4 * 2 * EPI_CHUNK_BYTES;        // 4 epilogue warps, double buffered
-constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + EPI_BYTES + 1024 + 256; }
+constexpr int smem_bytes(int stages, int bkt) {
+  return stages * stage_bytes(bkt) + EPI_BYTES + 1024 + 256;
+}
 
 struct PairParams {
   float *C;
@@ -69,50 +79,10 @@ struct PairParams {
   int prefetch_dist;  // k blocks the L2 prefetch runs ahead of the loads (0 = off)
 };
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
-}
-// Tile load of a CTA pair: data lands in this CTA's shared memory, completion
-// bytes are counted on a barrier that may live in the peer CTA.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
-                                                 uint32_t bar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-      "[%0], %1;" ::"r"(bar),
-      "h"(cta_mask)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc,
-                                                     uint64_t b_desc, uint32_t idesc,
-                                                     uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+// cycle counter for the optional in-kernel statistics; free when they are off
+template <bool STATS> __device__ __forceinline__ long long now() {
+  if constexpr (STATS) return clock64();
+  return 0;
 }
 
 __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams &p, int &mb, int &nb) {
@@ -125,11 +95,15 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams &p, 
   mb = first_m + t % rows_in_band;
 }
 
-template <int STAGES>
+template <int STAGES, int BKT, bool STATS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const PairParams p) {
+  constexpr int BK = BKT;
+  constexpr int STAGE_BYTES = stage_bytes(BKT);
+  constexpr int A_STAGE_BYTES = a_stage_bytes(BKT);
+  constexpr int B_BOX_BYTES = b_box_bytes(BKT);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi_base = smem_base + STAGES * STAGE_BYTES;  // 1024-byte aligned
@@ -182,7 +156,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      long long t_begin = clock64(), w_empty = 0, w_issue = 0;
+      long long t_begin = now<STATS>(), w_empty = 0, w_issue = 0;
       // L2 prefetch cursor: runs `prefetch_dist` k blocks ahead of the load cursor
       // over the same (tile, k block) sequence.  Clusters that share a row or
       // column block walk k in step, so without it every stage waits for the one
@@ -218,29 +192,31 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
         const int col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          const long long t0 = clock64();
+          const long long t0 = now<STATS>();
           if (!mbar_wait_relaxed(empty_bar(stage), phase ^ 1u, p.sleep_ns >> 2)) {
             report(p.status, kStatusTmaWaitTimeout);
             ok = false;
             break;
           }
-          w_empty += clock64() - t0;
-          const long long t1 = clock64();
+          w_empty += now<STATS>() - t0;
+          const long long t1 = now<STATS>();
           const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
           if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-          tma_load_2d_pair(a_dst, &tmap_a, kb * BK, row0, leader_full);
+#pragma unroll
+          for (int j = 0; j < BK / 64; ++j)
+            tma_load_2d_pair(a_dst + j * A_BOX_BYTES, &tmap_a, kb * BK + j * 64, row0, leader_full);
           tma_load_2d_pair(b_dst, &tmap_b, col0, kb * BK, leader_full);
           tma_load_2d_pair(b_dst + B_BOX_BYTES, &tmap_b, col0 + 64, kb * BK, leader_full);
-          w_issue += clock64() - t1;
+          w_issue += now<STATS>() - t1;
           if (p.prefetch_dist > 0) prefetch_step();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-      if (p.stats) {
+      if (STATS && p.stats) {
         long long *st = p.stats + 8 * blockIdx.x;
-        st[3] = clock64() - t_begin;  // producer: total
+        st[3] = now<STATS>() - t_begin;  // producer: total
         st[4] = w_empty;              // ... of which waiting for a free stage
         st[7] = w_issue;              // ... of which issuing the three tile loads
       }
@@ -260,44 +236,45 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      long long t_begin = clock64(), w_full = 0, w_acc = 0, w_mma = 0;
+      long long t_begin = now<STATS>(), w_full = 0, w_acc = 0, w_mma = 0;
       for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
-        long long t0 = clock64();
+        long long t0 = now<STATS>();
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
           report(p.status, kStatusMmaWaitTimeout);
           break;
         }
-        w_acc += clock64() - t0;
+        w_acc += now<STATS>() - t0;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          t0 = clock64();
+          t0 = now<STATS>();
           if (!mbar_wait(full_bar(stage), phase)) {
             report(p.status, kStatusMmaWaitTimeout);
             ok = false;
             break;
           }
-          w_full += clock64() - t0;
+          w_full += now<STATS>() - t0;
           tcgen05_fence_after();
-          t0 = clock64();
+          t0 = now<STATS>();
           const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = make_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t a_desc =
+                make_smem_desc(a_addr + (k >> 2) * A_BOX_BYTES + (k & 3) * (UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = make_smem_desc(b_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
             tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | k) ? 1u : 0u);
           }
           tcgen05_commit_pair(empty_bar(stage), 3);
-          w_mma += clock64() - t0;
+          w_mma += now<STATS>() - t0;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) tcgen05_commit_pair(acc_full_bar(acc), 3);
         if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
       }
-      if (p.stats) {
+      if (STATS && p.stats) {
         long long *st = p.stats + 8 * blockIdx.x;
-        st[0] = clock64() - t_begin;  // MMA thread: issue loop, total
+        st[0] = now<STATS>() - t_begin;  // MMA thread: issue loop, total
         st[1] = w_full;               // ... of which waiting for operands
         st[2] = w_acc;                // ... of which waiting for a free accumulator
         p.stats[8 * (blockIdx.x + 1) + 2] = w_mma;  // (peer's unused slot) issuing MMAs + commit
@@ -308,13 +285,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int lane_group = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    long long t_begin = clock64(), w_accfull = 0;
+    long long t_begin = now<STATS>(), w_accfull = 0;
     for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
       int mb, nb;
       pair_tile_coords(tile, p, mb, nb);
-      const long long t0 = clock64();
+      const long long t0 = now<STATS>();
       bool ok = mbar_wait_relaxed(acc_full_bar(acc), acc_phase, p.sleep_ns);
-      w_accfull += clock64() - t0;
+      w_accfull += now<STATS>() - t0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
@@ -400,9 +377,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) tma_store_wait_all<0>();  // all of this warp's tile stores have landed
-    if (p.stats && warp == 2 && lane == 0) {
+    if (STATS && p.stats && warp == 2 && lane == 0) {
       long long *st = p.stats + 8 * blockIdx.x;
-      st[5] = clock64() - t_begin;  // epilogue warp: total
+      st[5] = now<STATS>() - t_begin;  // epilogue warp: total
       st[6] = w_accfull;            // ... of which waiting for an accumulator
     }
   }
@@ -430,19 +407,22 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   if (!gemm_tcgen05_supported(g)) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  static int stages = 6;
+  static int variant = 1;  // 0: 6 stages x 64 k, 1: 3 stages x 128 k, 2: 4 stages x 64 k
+  static bool with_stats = false;
   std::call_once(once, [] {
-    if (const char *e = getenv("IMEX_GEMM_STAGES")) {
-      int v = atoi(e);
-      if (v == 4 || v == 5) stages = v;
-    }
-    auto set = [](const void *fn, int st) {
-      return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(st));
+    if (const char *e = getenv("IMEX_GEMM_VARIANT")) variant = atoi(e);
+    if (variant < 0 || variant > 2) variant = 1;
+    with_stats = getenv("IMEX_GEMM_STATS") != nullptr;
+    auto set = [](const void *fn, int bytes) {
+      return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     };
-    attr_err = stages == 4   ? set((const void *)gemm_tcgen05_2cta_kernel<4>, 4)
-               : stages == 5 ? set((const void *)gemm_tcgen05_2cta_kernel<5>, 5)
-                             : set((const void *)gemm_tcgen05_2cta_kernel<6>, 6);
+    cudaError_t e1 = set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false>, smem_bytes(3, 128));
+    cudaError_t e2 = set((const void *)gemm_tcgen05_2cta_kernel<3, 128, true>, smem_bytes(3, 128));
+    cudaError_t e3 = set((const void *)gemm_tcgen05_2cta_kernel<6, 64, false>, smem_bytes(6, 64));
+    cudaError_t e4 = set((const void *)gemm_tcgen05_2cta_kernel<4, 64, false>, smem_bytes(4, 64));
+    attr_err = e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3 != cudaSuccess ? e3 : e4;
   });
+  const int BK = variant == 1 ? 128 : 64;
   if (attr_err != cudaSuccess) return attr_err;
 
   const int64_t lda = g.lda > 0 ? g.lda : g.K;
@@ -475,7 +455,7 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   p.accumulate = g.accumulate ? 1 : 0;
   p.stats = nullptr;
   static long long *stats_buf = nullptr;
-  const bool want_stats = getenv("IMEX_GEMM_STATS") != nullptr;  // development aid
+  const bool want_stats = with_stats && variant == 1;  // development aid (IMEX_GEMM_STATS=1)
   if (want_stats) {
     if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 148 * sizeof(long long));
     p.stats = stats_buf;
@@ -495,11 +475,14 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   const int max_clusters = usable / 2;
   const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
   const dim3 grid(2 * clusters), block(NUM_THREADS);
-  switch (stages) {
-  case 4: gemm_tcgen05_2cta_kernel<4><<<grid, block, smem_bytes(4), stream>>>(ta, tb, tc_, p); break;
-  case 5: gemm_tcgen05_2cta_kernel<5><<<grid, block, smem_bytes(5), stream>>>(ta, tb, tc_, p); break;
-  default: gemm_tcgen05_2cta_kernel<6><<<grid, block, smem_bytes(6), stream>>>(ta, tb, tc_, p); break;
-  }
+  if (variant == 0)
+    gemm_tcgen05_2cta_kernel<6, 64, false><<<grid, block, smem_bytes(6, 64), stream>>>(ta, tb, tc_, p);
+  else if (variant == 2)
+    gemm_tcgen05_2cta_kernel<4, 64, false><<<grid, block, smem_bytes(4, 64), stream>>>(ta, tb, tc_, p);
+  else if (with_stats)
+    gemm_tcgen05_2cta_kernel<3, 128, true><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, p);
+  else
+    gemm_tcgen05_2cta_kernel<3, 128, false><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, p);
   if (want_stats && stats_buf) {
     cudaStreamSynchronize(stream);
     double a[8] = {0};

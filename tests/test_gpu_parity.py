@@ -236,6 +236,35 @@ def test_gemm_with_row_pitches(pkg, sess, kind):
         assert oracle.rel_frobenius(got[:, col_c:col_c + N], ref) <= GEMM_FROB_TOL
 
 
+@pytest.mark.parametrize("variant", ["0", "1", "2"])
+@pytest.mark.parametrize("shape", [(512, 1024, 128), (300, 520, 200), (1000, 1544, 72), (2304, 4608, 256),
+                                   (20000, 512, 64)])
+def test_gemm_pair_kernel_stage_variants(shape, variant):
+    """6 stages x 64 k, 3 stages x 128 k (default) and 4 stages x 64 k of the CTA-pair kernel;
+    the variant is read once per process, so each runs in a child process."""
+    import subprocess
+    import sys
+    M, N, K = shape
+    prog = (
+        "import sys, numpy as np; sys.path.insert(0, %r)\n"
+        "from __graft_entry__ import load_package; from oracle import oracle\n"
+        "pkg = load_package(); B = pkg.blob\n"
+        "M, N, K = %d, %d, %d\n"
+        "A = oracle.to_bf16_bits(oracle.fill_uniform((M, K), 3, -1.0, 1.0))\n"
+        "Bm = oracle.to_bf16_bits(oracle.fill_uniform((K, N), 4, -1.0, 1.0))\n"
+        "with pkg.Session(device=0) as s:\n"
+        "    dA, dB, dC = s.upload(A), s.upload(Bm), s.upload(np.full((M, N), np.nan, np.float32))\n"
+        "    s.run(B.gemm('g', M, N, K, B.BF16, B.EPI_SILU), [dA, dB, dC])\n"
+        "    assert s.last_kernel() == 'gemm_tcgen05_2cta', s.last_kernel()\n"
+        "    got = s.download(dC, (M, N), np.float32)\n"
+        "ref = oracle.silu(oracle.matmul_x16_f32(A, Bm, True))\n"
+        "err = oracle.rel_frobenius(got, ref)\n"
+        "assert not np.isnan(got).any() and err <= 1e-3, err\n" % (os.path.dirname(HERE), M, N, K))
+    env = dict(os.environ, IMEX_GEMM_VARIANT=variant)
+    r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
 def test_gemm_single_cta_kernel_still_matches(pkg, sess, monkeypatch):
     monkeypatch.setenv("IMEX_B200_GEMM_1CTA", "1")
     Ab = oracle.to_bf16_bits(oracle.fill_uniform((512, 320), 3, -1.0, 1.0))
