@@ -58,11 +58,13 @@ def measured_peaks():
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
 # captures summarised under profiles/; None where no capture has been taken.
 NCU_TRAFFIC = {
-    "gemm_cfg5": None,
+    # profiles/gemm_tcgen05_2cta_8192_silu.md: 1.104 GB read + 0.2446 GB written on 8192 rows
+    "gemm_cfg5_per_8192_rows": 1.104139e9 + 244.613888e6,
     "gemm_cfg3": None,
-    "softmax": None,
-    "reduce_rows": None,
-    "transpose2d": None,
+    # profiles/memory_bound_kernels.md
+    "softmax": None,            # config 2 fits L2; the 65536-row capture moved 268.5 + 212.2 MB
+    "reduce_rows": 1073.754e6 + 3.6e6,
+    "transpose2d": 268.44e6 + 218.1e6,
 }
 
 
@@ -461,7 +463,9 @@ def main():
                                       % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 else "none",
                        "l2": "inputs (1 GiB A shard + 128 MiB B) exceed the 126 MB L2"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC["gemm_cfg5"],
+                         "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC["gemm_cfg5_per_8192_rows"] * rows / 8192.0,
+                         "traffic_note": "ncu capture on 8192 rows scaled by rows/8192",
                          "kernel": gemm_kernel_name, "kernel_ms": kernel_ms,
                          "launches_per_step": len(gemm.slabs),
                          "peak_source": peaks["source"] + " (cuBLAS bf16 burst)",
