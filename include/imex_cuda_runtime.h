@@ -122,6 +122,13 @@ int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent);
  * 8 middle-third average. */
 float imexStat(int which, const float *values, size_t n);
 
+/* Failure-path self-test: enqueues a one-thread kernel whose bounded wait (about
+ * a millisecond, on a barrier nothing signals) runs out; the kernel records a
+ * status code and returns normally, and the next gpuWait on the stream reports
+ * "device kernel reported status 99" through the error convention.  No fault,
+ * trap or hang is involved; the context stays usable. */
+void imexSelfTestWaitTimeout(void *stream);
+
 /* Full sum of n f32 values without any allocation — no counterpart in the
  * reference (its runtime always allocates through the driver).
  *   *y = (accumulate ? *y : 0) + sum x[0..n)       x, y: device pointers

@@ -17,7 +17,8 @@ enum Status : unsigned {
   kStatusOk = 0,
   kStatusTmaWaitTimeout = 1,   // producer gave up waiting for a free smem stage
   kStatusMmaWaitTimeout = 2,   // MMA warp gave up waiting for operands / a free accumulator
-  kStatusEpiWaitTimeout = 3    // epilogue gave up waiting for an accumulator
+  kStatusEpiWaitTimeout = 3,   // epilogue gave up waiting for an accumulator
+  kStatusSelfTestTimeout = 99  // the wait self-test ran out, as it is meant to
 };
 
 struct GemmProblem {
@@ -49,6 +50,10 @@ cudaError_t launch_gemm_tcgen05(const GemmProblem &p, unsigned *status,
 bool gemm_tcgen05_2cta_preferred(const GemmProblem &p);
 cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &p, unsigned *status,
                                      cudaStream_t stream);
+
+// One thread waits (bounded, ~1 ms) on a barrier nothing signals and reports
+// kStatusSelfTestTimeout: exercises wait expiry -> status word -> gpuWait error.
+cudaError_t launch_wait_selftest(unsigned *status, cudaStream_t stream);
 
 // Row softmax over the last dim (one pass over HBM: read X once, write Y once).
 cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols,

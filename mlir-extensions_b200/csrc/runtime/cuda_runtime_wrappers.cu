@@ -640,6 +640,16 @@ int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent) {
   return shard * (extent / numShards) + (extra > 0 ? extra : 0);
 }
 
+void imexSelfTestWaitTimeout(void *stream) {
+  catchAll([&]() {
+    auto *s = static_cast<Stream *>(stream);
+    if (!s) throw std::runtime_error("imexSelfTestWaitTimeout: null stream");
+    CHECK_CUDA(cudaSetDevice(s->device));
+    check(imex::launch_wait_selftest(s->status_dev, s->stream), "launch of wait self-test");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  });
+}
+
 float imexStat(int which, const float *values, size_t n) {
   std::vector<float> v(values, values + n);
   switch (which) {

@@ -58,6 +58,7 @@ def _load():
         "imexShardSize": (C.c_int64, [C.c_int64, C.c_int64, C.c_int64]),
         "imexShardOffset": (C.c_int64, [C.c_int64, C.c_int64, C.c_int64]),
         "imexStat": (C.c_float, [C.c_int, C.POINTER(C.c_float), sz]),
+        "imexSelfTestWaitTimeout": (None, [vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

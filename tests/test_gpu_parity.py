@@ -527,3 +527,36 @@ def test_launch_counter_events_and_shared_memory(pkg, sess):
     host = np.ctypeslib.as_array((C.c_float * 64).from_address(y))
     assert oracle.max_rel_err(host.copy(), oracle.reduce_rows(X)) <= SOFTMAX_REDUCE_TOL
     assert rt.imexLaunchCount() - before == 2
+
+
+# ---------------------------------------------------------------- failure paths (no GPU fault involved)
+def _child(code):
+    import subprocess
+    import sys
+    prog = ("import sys, numpy as np; sys.path.insert(0, %r)\n"
+            "from __graft_entry__ import load_package\npkg = load_package(); rt, B = pkg.runtime, pkg.blob\n"
+            % os.path.dirname(HERE)) + code
+    return subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True)
+
+
+def test_bounded_wait_expiry_is_reported_by_gpu_wait():
+    """A device-side wait that runs out sets the stream's status word and the kernel returns;
+    gpuWait then fails through the reference's error convention, and the context stays usable
+    (the same process runs a reduction first and checks it)."""
+    r = _child("s = pkg.Session(device=0)\n"
+               "x = s.upload(np.ones(1000, np.float32)); y = s.alloc(4)\n"
+               "s.run(B.reduce_all('sum', 1000), [x, y])\n"
+               "print('sum', s.download(y, (1,), np.float32)[0], flush=True)\n"
+               "rt.library().imexSelfTestWaitTimeout(s.stream)\n"
+               "print('launched', flush=True)\n"
+               "rt.gpuWait(s.stream)\n"
+               "print('not reached')\n")
+    assert r.returncode < 0, r.stdout + r.stderr           # abort(), as the convention demands
+    assert "sum 1000.0" in r.stdout and "launched" in r.stdout and "not reached" not in r.stdout
+    assert "An exception was thrown: device kernel reported status 99" in r.stdout
+
+
+def test_allocation_failure_injected_on_the_host():
+    r = _child("import os; s = pkg.Session(device=0)\nos.environ['IMEX_B200_FAIL_ALLOC'] = '1'\n"
+               "s.alloc(1024)\nprint('not reached')\n")
+    assert r.returncode < 0 and "injected allocation failure" in r.stdout and "not reached" not in r.stdout
