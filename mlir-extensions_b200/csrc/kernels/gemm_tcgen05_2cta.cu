@@ -70,13 +70,22 @@ struct PairParams {
   long long ldc;
   int tiles_m, tiles_n, num_tiles, group_m;  // in 256x256 pair tiles
   int k_blocks;
+  // Tail of the persistent schedule: the last `split_tiles` tiles are cut along k into
+  // `split` parts each; a part leaves its raw f32 accumulator in `partials` (slot-major,
+  // 256x256 per slot) and gemm_splitk_fixup_kernel adds the parts up.  Work items are
+  // numbered: whole tiles first (item == tile), then split_tiles * split parts.
+  int whole_tiles, split_tiles, split, num_items;
+  float *partials;
   int epilogue;
   int accumulate;
   uint32_t idesc;
   long long *stats;   // optional per-CTA cycle counters (nullptr = off), 8 per CTA
-  unsigned sleep_ns;  // back-off of the non-critical waits
-  int fast_math;      // silu through ex2.approx / rcp.approx
-  int prefetch_dist;  // k blocks the L2 prefetch runs ahead of the loads (0 = off)
+};
+
+struct WorkItem {
+  int mb, nb;    // pair-tile coordinates
+  int kb0, kb1;  // k blocks [kb0, kb1)
+  int slot;      // partial slot, or -1 for a whole tile (normal epilogue)
 };
 
 // cycle counter for the optional in-kernel statistics; free when they are off
@@ -95,11 +104,30 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams &p, 
   mb = first_m + t % rows_in_band;
 }
 
+__device__ __forceinline__ WorkItem item_at(int idx, const PairParams &p) {
+  WorkItem w;
+  int tile = idx;
+  w.kb0 = 0;
+  w.kb1 = p.k_blocks;
+  w.slot = -1;
+  if (idx >= p.whole_tiles) {
+    const int s = idx - p.whole_tiles;
+    const int part = s % p.split;
+    tile = p.whole_tiles + s / p.split;
+    w.kb0 = p.k_blocks * part / p.split;
+    w.kb1 = p.k_blocks * (part + 1) / p.split;
+    w.slot = s;
+  }
+  pair_tile_coords(tile, p, w.mb, w.nb);
+  return w;
+}
+
 template <int STAGES, int BKT, bool STATS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ CUtensorMap tmap_c, const PairParams p) {
+                         const __grid_constant__ CUtensorMap tmap_c,
+                         const __grid_constant__ CUtensorMap tmap_p, const PairParams p) {
   constexpr int BK = BKT;
   constexpr int STAGE_BYTES = stage_bytes(BKT);
   constexpr int A_STAGE_BYTES = a_stage_bytes(BKT);
@@ -157,43 +185,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       long long t_begin = now<STATS>(), w_empty = 0, w_issue = 0;
-      // L2 prefetch cursor: runs `prefetch_dist` k blocks ahead of the load cursor
-      // over the same (tile, k block) sequence.  Clusters that share a row or
-      // column block walk k in step, so without it every stage waits for the one
-      // DRAM miss they all share.
-      int pf_tile = cluster_id, pf_kb = 0, pf_row0 = 0, pf_col0 = 0, pf_credit = 0;
-      if (p.prefetch_dist > 0 && pf_tile < p.num_tiles) {
-        int mb, nb;
-        pair_tile_coords(pf_tile, p, mb, nb);
-        pf_row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
-        pf_col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
-        pf_credit = p.prefetch_dist;  // k blocks the cursor may still advance
-      }
-      auto prefetch_step = [&]() {
-        if (pf_tile >= p.num_tiles) return;
-        tma_prefetch_2d(&tmap_a, pf_kb * BK, pf_row0);
-        tma_prefetch_2d(&tmap_b, pf_col0, pf_kb * BK);
-        tma_prefetch_2d(&tmap_b, pf_col0 + 64, pf_kb * BK);
-        if (++pf_kb == p.k_blocks) {
-          pf_kb = 0;
-          pf_tile += num_clusters;
-          if (pf_tile < p.num_tiles) {
-            int mb, nb;
-            pair_tile_coords(pf_tile, p, mb, nb);
-            pf_row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
-            pf_col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
-          }
-        }
-      };
-      for (; pf_credit > 0; --pf_credit) prefetch_step();
-      for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
-        int mb, nb;
-        pair_tile_coords(tile, p, mb, nb);
-        const int row0 = mb * PAIR_M + static_cast<int>(cta_rank) * BM;
-        const int col0 = nb * BN + static_cast<int>(cta_rank) * BN_HALF;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int item = cluster_id; item < p.num_items && ok; item += num_clusters) {
+        const WorkItem w = item_at(item, p);
+        const int row0 = w.mb * PAIR_M + static_cast<int>(cta_rank) * BM;
+        const int col0 = w.nb * BN + static_cast<int>(cta_rank) * BN_HALF;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           const long long t0 = now<STATS>();
-          if (!mbar_wait_relaxed(empty_bar(stage), phase ^ 1u, p.sleep_ns >> 2)) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
             report(p.status, kStatusTmaWaitTimeout);
             ok = false;
             break;
@@ -210,7 +208,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tma_load_2d_pair(b_dst, &tmap_b, col0, kb * BK, leader_full);
           tma_load_2d_pair(b_dst + B_BOX_BYTES, &tmap_b, col0 + 64, kb * BK, leader_full);
           w_issue += now<STATS>() - t1;
-          if (p.prefetch_dist > 0) prefetch_step();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -237,7 +234,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       long long t_begin = now<STATS>(), w_full = 0, w_acc = 0, w_mma = 0;
-      for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
+      for (int item = cluster_id; item < p.num_items && ok; item += num_clusters) {
+        const WorkItem w = item_at(item, p);
         long long t0 = now<STATS>();
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
           report(p.status, kStatusMmaWaitTimeout);
@@ -246,7 +244,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         w_acc += now<STATS>() - t0;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           t0 = now<STATS>();
           if (!mbar_wait(full_bar(stage), phase)) {
             report(p.status, kStatusMmaWaitTimeout);
@@ -263,7 +261,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t a_desc =
                 make_smem_desc(a_addr + (k >> 2) * A_BOX_BYTES + (k & 3) * (UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = make_smem_desc(b_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
-            tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | k) ? 1u : 0u);
+            tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb != w.kb0 || k) ? 1u : 0u);
           }
           tcgen05_commit_pair(empty_bar(stage), 3);
           w_mma += now<STATS>() - t0;
@@ -286,11 +284,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     long long t_begin = now<STATS>(), w_accfull = 0;
-    for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters) {
-      int mb, nb;
-      pair_tile_coords(tile, p, mb, nb);
+    for (int item = cluster_id; item < p.num_items; item += num_clusters) {
+      const WorkItem w = item_at(item, p);
+      const int mb = w.mb, nb = w.nb;
       const long long t0 = now<STATS>();
-      bool ok = mbar_wait_relaxed(acc_full_bar(acc), acc_phase, p.sleep_ns);
+      bool ok = mbar_wait(acc_full_bar(acc), acc_phase);
       w_accfull += now<STATS>() - t0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -309,7 +307,26 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_32x32(t_row + c0, r);
         tmem_ld_wait();
         const int col0 = nb * BN + c0;
-        if (p.accumulate) {
+        if (w.slot >= 0) {
+          // part of a k-split tile: the raw accumulator goes to its slot of the scratch
+          // buffer (same swizzled staging + tile store as below, no bias, no epilogue)
+          const uint32_t buf = my_bufs + ((c0 >> 5) & 1) * EPI_CHUNK_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                         __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            st_shared_v4(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4), v);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_p, buf, c0,
+                         w.slot * PAIR_M + static_cast<int>(cta_rank) * BM + lane_group * 32);
+            tma_store_commit();
+          }
+        } else if (p.accumulate) {
           // C is also an input: per-thread row segments, read-modify-write in place
           if (row < p.M && col0 < p.N) {
 #pragma unroll
@@ -350,17 +367,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
               }
             }
-            if (p.fast_math) {
-              v.x = apply_epilogue_fast(v.x, p.epilogue);
-              v.y = apply_epilogue_fast(v.y, p.epilogue);
-              v.z = apply_epilogue_fast(v.z, p.epilogue);
-              v.w = apply_epilogue_fast(v.w, p.epilogue);
-            } else {
-              v.x = apply_epilogue(v.x, p.epilogue);
-              v.y = apply_epilogue(v.y, p.epilogue);
-              v.z = apply_epilogue(v.z, p.epilogue);
-              v.w = apply_epilogue(v.w, p.epilogue);
-            }
+            v.x = apply_epilogue(v.x, p.epilogue);
+            v.y = apply_epilogue(v.y, p.epilogue);
+            v.z = apply_epilogue(v.z, p.epilogue);
+            v.w = apply_epilogue(v.w, p.epilogue);
             st_shared_v4(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4), v);
           }
           fence_async_smem();
@@ -396,7 +406,49 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+// Second step of a k-split tail: C tile = epilogue(C0 + bias + sum of the tile's parts,
+// parts added in order).  One block per 8 rows of a split tile.
+__global__ void __launch_bounds__(256)
+gemm_splitk_fixup_kernel(const PairParams p) {
+  const int t = blockIdx.x / (PAIR_M / 8);          // which split tile
+  const int strip = blockIdx.x % (PAIR_M / 8);      // which 8 rows of it
+  int mb, nb;
+  pair_tile_coords(p.whole_tiles + t, p, mb, nb);
+  const int col = nb * BN + (threadIdx.x & 63) * 4;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int lr = strip * 8 + (threadIdx.x >> 6) + 4 * h;  // row inside the tile
+    const int row = mb * PAIR_M + lr;
+    if (row >= p.M || col >= p.N) continue;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int part = 0; part < p.split; ++part) {
+      const float4 q = *reinterpret_cast<const float4 *>(
+          p.partials + (static_cast<size_t>(t * p.split + part) * PAIR_M + lr) * BN + (threadIdx.x & 63) * 4);
+      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    float *c = p.C + static_cast<size_t>(row) * p.ldc + col;
+    if (p.accumulate) {
+      const float4 c0 = *reinterpret_cast<const float4 *>(c);
+      v.x += c0.x; v.y += c0.y; v.z += c0.z; v.w += c0.w;
+    }
+    if (p.bias) {
+      const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
+      v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    v.x = apply_epilogue(v.x, p.epilogue);
+    v.y = apply_epilogue(v.y, p.epilogue);
+    v.z = apply_epilogue(v.z, p.epilogue);
+    v.w = apply_epilogue(v.w, p.epilogue);
+    *reinterpret_cast<float4 *>(c) = v;
+  }
+}
+
 } // namespace
+
+size_t gemm_tcgen05_workspace_bytes() {
+  // one 256x256 f32 slot per CTA pair in flight is the most a k-split tail can use
+  return static_cast<size_t>(sm_count() / 2) * PAIR_M * BN * sizeof(float);
+}
 
 bool gemm_tcgen05_2cta_preferred(const GemmProblem &p) {
   // a single row block gains nothing from pairing
@@ -460,12 +512,6 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
     if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 148 * sizeof(long long));
     p.stats = stats_buf;
   }
-  p.sleep_ns = 0;
-  if (const char *e = getenv("IMEX_GEMM_SLEEP_NS")) p.sleep_ns = static_cast<unsigned>(atoi(e));
-  p.prefetch_dist = 0;
-  if (const char *e = getenv("IMEX_GEMM_PREFETCH")) p.prefetch_dist = atoi(e);
-  p.fast_math = 0;
-  if (const char *e = getenv("IMEX_GEMM_FAST_EPILOGUE")) p.fast_math = atoi(e);
   const uint32_t fmt = g.in_dtype == kBF16 ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(PAIR_M >> 4) << 24);
@@ -473,16 +519,45 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   int usable = sm_count() - (g.sm_margin > 0 ? g.sm_margin : 0);
   if (usable < 2) usable = 2;
   const int max_clusters = usable / 2;
-  const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
+  // k-split tail: when the last wave would leave at least half of the pairs idle, its
+  // tiles are cut along k into as many parts as fill the machine (the sums then differ
+  // in the last bits from an unsplit run: IMEX_GEMM_NO_SPLITK=1 keeps every tile whole).
+  p.whole_tiles = p.num_tiles;
+  p.split_tiles = 0;
+  p.split = 1;
+  p.partials = static_cast<float *>(g.workspace);
+  {
+    const int rem = p.num_tiles % max_clusters;
+    int parts = rem > 0 ? max_clusters / rem : 1;
+    if (parts > 8) parts = 8;
+    while (parts > 1 && p.k_blocks / parts < 2) --parts;
+    const size_t need = static_cast<size_t>(rem) * parts * PAIR_M * BN * sizeof(float);
+    if (parts >= 2 && g.workspace && need <= g.workspace_bytes && !getenv("IMEX_GEMM_NO_SPLITK")) {
+      p.split_tiles = rem;
+      p.split = parts;
+      p.whole_tiles = p.num_tiles - rem;
+    }
+  }
+  p.num_items = p.whole_tiles + p.split_tiles * p.split;
+  CUtensorMap tp = tc_;  // placeholder when nothing is split (never dereferenced)
+  if (p.split_tiles &&
+      !make_map_f32_out(&tp, p.partials, BN, static_cast<int64_t>(p.split_tiles) * p.split * PAIR_M, BN))
+    return cudaErrorNotSupported;
+  const int clusters = p.num_items < max_clusters ? p.num_items : max_clusters;
   const dim3 grid(2 * clusters), block(NUM_THREADS);
   if (variant == 0)
-    gemm_tcgen05_2cta_kernel<6, 64, false><<<grid, block, smem_bytes(6, 64), stream>>>(ta, tb, tc_, p);
+    gemm_tcgen05_2cta_kernel<6, 64, false><<<grid, block, smem_bytes(6, 64), stream>>>(ta, tb, tc_, tp, p);
   else if (variant == 2)
-    gemm_tcgen05_2cta_kernel<4, 64, false><<<grid, block, smem_bytes(4, 64), stream>>>(ta, tb, tc_, p);
+    gemm_tcgen05_2cta_kernel<4, 64, false><<<grid, block, smem_bytes(4, 64), stream>>>(ta, tb, tc_, tp, p);
   else if (with_stats)
-    gemm_tcgen05_2cta_kernel<3, 128, true><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, p);
+    gemm_tcgen05_2cta_kernel<3, 128, true><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, tp, p);
   else
-    gemm_tcgen05_2cta_kernel<3, 128, false><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, p);
+    gemm_tcgen05_2cta_kernel<3, 128, false><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, tp, p);
+  if (p.split_tiles) {
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return le;
+    gemm_splitk_fixup_kernel<<<p.split_tiles * (PAIR_M / 8), 256, 0, stream>>>(p);
+  }
   if (want_stats && stats_buf) {
     cudaStreamSynchronize(stream);
     double a[8] = {0};

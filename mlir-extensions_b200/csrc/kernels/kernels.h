@@ -32,6 +32,8 @@ struct GemmProblem {
   int epilogue;       // Epilogue
   bool accumulate;    // C is read as the initial value
   int sm_margin = 0;  // SMs the persistent kernels leave unused
+  void *workspace = nullptr;   // device scratch for a k-split tail (optional)
+  size_t workspace_bytes = 0;
 };
 
 // f32 or 16-bit inputs, one thread per 4x4 outputs, k ascending with
@@ -48,6 +50,7 @@ cudaError_t launch_gemm_tcgen05(const GemmProblem &p, unsigned *status,
                                 cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05.mma.cta_group::2, 256x256 tile per pair).
 bool gemm_tcgen05_2cta_preferred(const GemmProblem &p);
+size_t gemm_tcgen05_workspace_bytes();  // scratch the pair kernel can use for a k-split tail
 cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &p, unsigned *status,
                                      cudaStream_t stream);
 

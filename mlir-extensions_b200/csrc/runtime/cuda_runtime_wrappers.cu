@@ -284,6 +284,9 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     const bool force_simt = getenv("IMEX_B200_FORCE_SIMT_GEMM") != nullptr;
     bool done = false;
     if (!force_simt && imex::gemm_tcgen05_2cta_preferred(g)) {
+      ensure_scratch(s, imex::gemm_tcgen05_workspace_bytes());
+      g.workspace = s->scratch;
+      g.workspace_bytes = s->scratch_bytes;
       s->last_kernel = "gemm_tcgen05_2cta";
       err = imex::launch_gemm_tcgen05_2cta(g, s->status_dev, s->stream);
       done = err != cudaErrorNotSupported;

@@ -300,7 +300,29 @@ def test_gemm_odd_shape_takes_exact_simt_path(pkg, sess):
     assert got.tobytes() == oracle.matmul_x16_f32(Ab, Bb, True).tobytes()
 
 
-def test_config3_gemm_bf16_4096_relu_sampled_rows(pkg, sess):
+@pytest.mark.parametrize("shape,epi", [((1024, 1024, 2048), 0), ((4096, 1280, 1024), 2),
+                                       ((700, 520, 4096), 1), ((2560, 2304, 512), 1)])
+def test_gemm_k_split_tail(pkg, sess, monkeypatch, shape, epi):
+    """Shapes whose last wave is cut along k (partials in scratch + fix-up kernel), with bias and
+    an initial C; against the oracle and against the same launch with every tile kept whole."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    Ab = oracle.to_bf16_bits(rng.uniform(-1, 1, (M, K)).astype(np.float32))
+    Bb = oracle.to_bf16_bits(rng.uniform(-1, 1, (K, N)).astype(np.float32))
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (M, N)).astype(np.float32) if epi == 1 else None
+    got = _gemm(pkg, sess, Ab, Bb, pkg.blob.BF16, epi, C0, bias)
+    assert sess.last_kernel() == "gemm_tcgen05_2cta"
+    ref = _oracle_gemm(Ab, Bb, "bf16", epi, C0, bias)
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= GEMM_FROB_TOL
+    monkeypatch.setenv("IMEX_GEMM_NO_SPLITK", "1")
+    whole = _gemm(pkg, sess, Ab, Bb, pkg.blob.BF16, epi, C0, bias)
+    assert oracle.rel_frobenius(got, whole) <= 1e-5
+    assert oracle.rel_frobenius(whole, ref) <= GEMM_FROB_TOL
+
+
+def test_config3_gemm_bf16_4096_relu_sampled_rows(pkg, sess, monkeypatch):
     """4096^3 + relu.  The oracle runs on 256 sampled rows (the full product is
     69 GMAC on the CPU); every other row is covered by linearity: rows of C
     depend on the matching rows of A only, so C(A with rows permuted) must be
@@ -317,11 +339,17 @@ def test_config3_gemm_bf16_4096_relu_sampled_rows(pkg, sess):
     rows = np.sort(np.random.default_rng(0).choice(n, 256, replace=False))
     ref = oracle.relu(oracle.matmul_x16_f32(A[rows], Bm, True))
     assert oracle.rel_frobenius(got[rows], ref) <= GEMM_FROB_TOL
+    # bit-for-bit equivariance holds when every tile is computed whole (the k-split tail adds
+    # the parts of its tiles in a different order: equal within rounding only)
+    monkeypatch.setenv("IMEX_GEMM_NO_SPLITK", "1")
+    sess.launch(k, [dA, dB, dC])
+    whole = sess.download(dC, (n, n), np.float32)
+    assert oracle.rel_frobenius(got, whole) <= 1e-5
     perm = np.random.default_rng(1).permutation(n)
     dA2 = sess.upload(A[perm])
     sess.launch(k, [dA2, dB, dC])
     got2 = sess.download(dC, (n, n), np.float32)
-    assert np.array_equal(got2, got[perm])
+    assert np.array_equal(got2, whole[perm])
 
 
 # ---------------------------------------------------------------- softmax
