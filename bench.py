@@ -541,12 +541,32 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
                 ms.append(a.elapsed_time(b))
         return float(np.median(ms)), float(np.min(ms))
 
+    def copy_floor_ms(nbytes):
+        """A plain device copy moving the same bytes (read half, write half), timed the same
+        way: context for problems too small to reach the streaming rate."""
+        n = max(nbytes // 2, 4)
+        src = torch.empty(n, dtype=torch.uint8, device=dev)
+        dst = torch.empty_like(src)
+        ms = []
+        for i in range(iters + 3):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dst.copy_(src)
+            b.record()
+            b.synchronize()
+            if i >= 3:
+                ms.append(a.elapsed_time(b))
+        return float(np.median(ms))
+
     def hbm_entry(name, key, nbytes, kernel, ptrs, note):
         med, mn = timed(kernel, ptrs, cold=True)
         wmed, _ = timed(kernel, ptrs, cold=False)
         ach = nbytes / (med * 1e-3) / 1e9
+        floor = copy_floor_ms(nbytes)
         out[name] = {"value": ach, "unit": "GB/s", "ms_cold_median": med, "ms_cold_min": mn,
                      "ms_warm_median": wmed, "algorithmic_bytes": nbytes,
+                     "ms_copy_of_same_bytes": floor, "speed_vs_copy_of_same_bytes": floor / med,
                      "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm, "unit": "GB/s",
                                   "frac": ach / hbm, "traffic": NCU_TRAFFIC[key],
                                   "peak_source": peaks["source"] + " (copy)",
