@@ -264,10 +264,14 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel section")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-gather", action="store_true", help="N>1: skip the optional all-gather of C")
     ap.add_argument("--rows", type=int, default=M_TOTAL, help="total rows of A (small runs)")
     ap.add_argument("--e2e-chunks", type=int, default=16, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--sm-margin", type=int, default=4,
                     help="SMs the GEMM leaves to the NCCL broadcast when N > 1")
+    ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "slabs"),
+                    choices=["slabs", "calls"],
+                    help="N>1: hide the replication of B inside a call (column slabs) or across calls")
     ap.add_argument("--case", default=None, choices=sorted(CASES),
                     help="run ONE small kernel case --iters times and exit (ncu captures)")
     ap.add_argument("--iters", type=int, default=3)
@@ -329,7 +333,7 @@ def main():
         os.environ.get("IMEX_BENCH_EPILOGUE", "silu")]  # experiments only; the metric is silu
     from mlir_extensions_b200.dist import RowShardedGemm
     gemm = RowShardedGemm(sess, rank, world, M_total, N_DIM, K_DIM, B.BF16, epi, src=0,
-                          sm_margin=args.sm_margin, device=dev)
+                          sm_margin=args.sm_margin, device=dev, overlap=args.overlap)
     assert (gemm.row0, gemm.rows) == (row0, rows)
 
     def step():
@@ -380,6 +384,29 @@ def main():
         kernel_ms = max_over_ranks(ka.elapsed_time(kb))
     flops_job = 2.0 * M_total * N_DIM * K_DIM
     value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # optional last step, outside the timed region and reported on its own: every rank
+    # gets all rows of C (NCCL all-gather of the row shards)
+    gather = None
+    if world > 1 and not args.no_gather:
+        from mlir_extensions_b200.dist import all_gather_rows
+        c_full = torch.empty((M_total, N_DIM), dtype=torch.float32, device=dev)
+        ms_list = []
+        for i in range(4):
+            barrier()
+            ga, gb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ga.record()
+            all_gather_rows(Cm, c_full, rank, world, M_total)
+            gb.record()
+            gb.synchronize()
+            if i:
+                ms_list.append(max_over_ranks(ga.elapsed_time(gb)))
+        same = bool(torch.equal(c_full[row0:row0 + rows], Cm))
+        g_ms = float(np.median(ms_list))
+        recv = (M_total - rows) * N_DIM * 4
+        gather = {"ms": g_ms, "bytes_received_per_rank": recv, "gbs_per_rank": recv / (g_ms * 1e-3) / 1e9,
+                  "own_block_intact": same, "note": "NCCL all-gather of the f32 row shards of C, not in ms_per_step"}
+        del c_full
 
     # parity guard: sampled rows of this rank's shard against the CPU oracle
     from oracle import oracle
@@ -457,10 +484,15 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_total": M_total, "rows_per_rank": rows,
                        "partition": "block rows, last extent%N shards one longer",
-                       "collective": ("NCCL broadcast of B from rank 0 inside every step, in column "
-                                      "slabs %s overlapped with the slab GEMMs; GEMM leaves %d SMs free"
+                       "collective": (("NCCL broadcast of B from rank 0 inside every step, "
+                                       + ("in column slabs %s overlapped with the slab GEMMs"
+                                          if gemm.overlap == "slabs" else
+                                          "as one slab %s into one of two replica buffers, overlapped with "
+                                          "the previous step's GEMM")
+                                       + "; GEMM leaves %d SMs free")
                                       % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 else "none",
-                       "l2": "inputs (1 GiB A shard + 128 MiB B) exceed the 126 MB L2"},
+                       "l2": "inputs (%d MiB A shard + 128 MiB B) and the %d MiB C shard exceed the 126 MB L2"
+                             % (rows * K_DIM * 2 >> 20, rows * N_DIM * 4 >> 20)},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC["gemm_cfg5_per_8192_rows"] * rows / 8192.0,
@@ -473,7 +505,7 @@ def main():
                          "frac_of_nominal_2250": achieved / 2250.0},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "parity": {"rel_frobenius_sampled_rows": frob, "tolerance": 1e-3},
-            "cpu_baseline": cpu, "kernels": kernels, "sharded_rows": sharded,
+            "cpu_baseline": cpu, "kernels": kernels, "sharded_rows": sharded, "all_gather_c": gather,
         }
         print(json.dumps(line), flush=True)
     sess.close()

@@ -18,6 +18,17 @@ Slabs are sized in whole waves of the persistent GEMM (tiles per slab a
 multiple of the CTA pairs in flight) so that cutting B costs no tail.  The
 GEMM leaves `sm_margin` SMs free so that the NCCL kernel of the next slab can
 run beside it.  Softmax and row-reduce shard by rows with no exchange at all.
+
+Two ways to hide the replication (`overlap=`):
+
+    "slabs"  inside one call, as above: several GEMM launches per call.
+    "calls"  across calls: B travels as ONE slab into one of two replica
+             buffers, the GEMM is a single launch over the whole width, and
+             the replication for call i+1 runs beside the GEMM of call i
+             (the host enqueues ahead).  Every extra GEMM launch costs a
+             pipeline ramp and an un-overlapped drain, so this is the faster
+             form for back-to-back calls; a lone call pays the whole
+             replication up front.
 """
 from . import blob as B
 from . import runtime as rt
@@ -90,14 +101,19 @@ class RowShardedGemm:
     from rank `src` inside every call."""
 
     def __init__(self, session, rank, world, m_total, n, k, in_dtype=B.BF16, epilogue=B.EPI_NONE,
-                 src=0, sm_margin=4, slabs=None, device=None):
+                 src=0, sm_margin=4, slabs=None, device=None, overlap="slabs"):
         import torch
         self.torch = torch
         self.sess, self.rank, self.world, self.src = session, rank, world, src
         self.m_total, self.n, self.k = m_total, n, k
         self.row0, self.rows = shard_rows(rank, world, m_total)
         self.margin = sm_margin if world > 1 else 0
-        self.slabs = slabs or plan_slabs(self.rows, n, world, sm_margin=sm_margin)
+        if overlap not in ("slabs", "calls"):
+            raise ValueError("overlap must be 'slabs' or 'calls'")
+        self.overlap = overlap
+        if slabs is None:
+            slabs = [(0, n)] if overlap == "calls" else plan_slabs(self.rows, n, world, sm_margin=sm_margin)
+        self.slabs = slabs
         self.device = device
         self.comm_stream = torch.cuda.Stream(device=device) if world > 1 else None
         elt = torch.bfloat16 if in_dtype == B.BF16 else torch.float16
@@ -152,3 +168,31 @@ class RowShardedGemm:
         done.record(cur)
         self.done_events[which] = done
         return len(self.slabs)
+
+
+def all_gather_rows(shard, full, rank, world, extent):
+    """Optional last step of a row-sharded op: every rank ends up with all rows.
+
+    shard [rows of this rank, ...] -> full [extent, ...] on every rank.  Rows are laid
+    out by the block partition rule, so rank r's block lands at its own offset.  Even
+    partitions travel as one all-gather straight into `full`; ragged ones as one
+    broadcast per rank into that rank's row block (NCCL all-gather wants equal
+    counts).  The reference leaves this to its distributed runtime's gather of the
+    local parts (`ndarray`/`dist` lowering to `_idtr_*` calls, not in the reference
+    tree); here it is NCCL over NVLink, or gloo on CPU tensors in the tests."""
+    import torch.distributed as dist
+    sizes = [rt.imexShardSize(r, world, extent) for r in range(world)]
+    if world == 1:
+        full.copy_(shard)
+        return full
+    if len(set(sizes)) == 1:
+        dist.all_gather_into_tensor(full, shard.contiguous())
+        return full
+    for r in range(world):
+        off = rt.imexShardOffset(r, world, extent)
+        block = full[off:off + sizes[r]]
+        if r == rank:
+            block.copy_(shard)
+        if sizes[r]:
+            dist.broadcast(block, src=r)
+    return full

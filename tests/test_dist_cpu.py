@@ -78,3 +78,45 @@ def test_world2_gloo_slab_replication(tmp_path):
     res = np.load(tmp_path / "result.npy")
     assert res[:, 2].all()                       # every rank reproduced its rows of A.B
     assert res[:, :2].tolist() == [[0, 5], [5, 5]]  # block rows of a 10-row A over 2 ranks
+
+
+def _gather_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import sys
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    load_package()
+    from mlir_extensions_b200 import dist as rows
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok = True
+    for extent in (10, 11, 1):  # even blocks, ragged blocks, a rank with no rows
+        truth = torch.arange(extent * 3, dtype=torch.float32).reshape(extent, 3)
+        row0, nrows = rows.shard_rows(rank, world, extent)
+        full = torch.full((extent, 3), float("nan"))
+        rows.all_gather_rows(truth[row0:row0 + nrows].clone(), full, rank, world, extent)
+        ok = ok and bool(torch.equal(full, truth))
+    gathered = [None] * world
+    dist.all_gather_object(gathered, ok)
+    if rank == 0:
+        np.save(os.path.join(tmp, "gather.npy"), np.array(gathered, dtype=np.int64))
+    dist.destroy_process_group()
+
+
+def test_world2_gloo_all_gather_rows(tmp_path):
+    world = 2
+    mp.spawn(_gather_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert np.load(tmp_path / "gather.npy").all()
+
+
+def test_overlap_across_calls_uses_one_full_width_slab():
+    from mlir_extensions_b200 import dist as rows
+
+    class _NoSession:
+        def kernel(self, blob):
+            return blob
+
+    import pytest
+    with pytest.raises(ValueError):
+        rows.RowShardedGemm(_NoSession(), 0, 1, 512, 512, 64, overlap="sometimes")
+    g = rows.RowShardedGemm(_NoSession(), 0, 1, 512, 512, 64, overlap="calls")
+    assert g.slabs == [(0, 512)]
