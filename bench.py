@@ -267,9 +267,11 @@ def main():
     ap.add_argument("--no-gather", action="store_true", help="N>1: skip the optional all-gather of C")
     ap.add_argument("--rows", type=int, default=M_TOTAL, help="total rows of A (small runs)")
     ap.add_argument("--e2e-chunks", type=int, default=16, help="row chunks of the host-buffer pipeline")
-    ap.add_argument("--sm-margin", type=int, default=4,
+    ap.add_argument("--sm-margin", type=int, default=None,
                     help="SMs the GEMM leaves to the NCCL broadcast when N > 1")
-    ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "slabs"),
+    ap.add_argument("--comm-ms", type=float, default=0.5,
+                    help="N>1, --overlap calls: how long the first GEMM launch (NCCL beside it) should last")
+    ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "calls"),
                     choices=["slabs", "calls"],
                     help="N>1: hide the replication of B inside a call (column slabs) or across calls")
     ap.add_argument("--case", default=None, choices=sorted(CASES),
@@ -333,7 +335,7 @@ def main():
         os.environ.get("IMEX_BENCH_EPILOGUE", "silu")]  # experiments only; the metric is silu
     from mlir_extensions_b200.dist import RowShardedGemm
     gemm = RowShardedGemm(sess, rank, world, M_total, N_DIM, K_DIM, B.BF16, epi, src=0,
-                          sm_margin=args.sm_margin, device=dev, overlap=args.overlap)
+                          sm_margin=args.sm_margin, device=dev, overlap=args.overlap, comm_ms=args.comm_ms)
     assert (gemm.row0, gemm.rows) == (row0, rows)
 
     def step():
@@ -377,8 +379,7 @@ def main():
         barrier()
         ka, kb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ka.record()
-        for (c0, w), buf, kern in zip(gemm.slabs, gemm.slab_bufs, gemm.kernels):
-            sess.launch(kern, [A.data_ptr(), buf.data_ptr(), Cm.data_ptr() + 4 * c0], wait=False)
+        gemm.launch_gemms(A, Cm)
         kb.record()
         kb.synchronize()
         kernel_ms = max_over_ranks(ka.elapsed_time(kb))
@@ -485,12 +486,13 @@ def main():
             "config": {"workload": WORKLOAD, "rows_total": M_total, "rows_per_rank": rows,
                        "partition": "block rows, last extent%N shards one longer",
                        "collective": (("NCCL broadcast of B from rank 0 inside every step, "
-                                       + ("in column slabs %s overlapped with the slab GEMMs"
-                                          if gemm.overlap == "slabs" else
+                                       + ("in column slabs %s overlapped with the slab GEMMs; every GEMM "
+                                          "launch leaves %d SMs free" if gemm.overlap == "slabs" else
                                           "as one slab %s into one of two replica buffers, overlapped with "
-                                          "the previous step's GEMM")
-                                       + "; GEMM leaves %d SMs free")
+                                          "the previous step's GEMM, whose first launch leaves %d SMs free "
+                                          "and whose second uses all SMs"))
                                       % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 else "none",
+                       "gemm_launch_columns": [int(k_.dims[1]) for k_ in gemm.launch_descs],
                        "l2": "inputs (%d MiB A shard + 128 MiB B) and the %d MiB C shard exceed the 126 MB L2"
                              % (rows * K_DIM * 2 >> 20, rows * N_DIM * 4 >> 20)},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
@@ -498,7 +500,7 @@ def main():
                          "traffic": NCU_TRAFFIC["gemm_cfg5_per_8192_rows"] * rows / 8192.0,
                          "traffic_note": "ncu capture on 8192 rows scaled by rows/8192",
                          "kernel": gemm_kernel_name, "kernel_ms": kernel_ms,
-                         "launches_per_step": len(gemm.slabs),
+                         "launches_per_step": len(gemm.launches),
                          "peak_source": peaks["source"] + " (cuBLAS bf16 burst)",
                          "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"])
                          if peaks.get("bf16_tflops_sustained") else None,

@@ -22,13 +22,14 @@ run beside it.  Softmax and row-reduce shard by rows with no exchange at all.
 Two ways to hide the replication (`overlap=`):
 
     "slabs"  inside one call, as above: several GEMM launches per call.
-    "calls"  across calls: B travels as ONE slab into one of two replica
-             buffers, the GEMM is a single launch over the whole width, and
-             the replication for call i+1 runs beside the GEMM of call i
-             (the host enqueues ahead).  Every extra GEMM launch costs a
-             pipeline ramp and an un-overlapped drain, so this is the faster
-             form for back-to-back calls; a lone call pays the whole
-             replication up front.
+    "calls"  across calls (default): B travels as ONE slab into one of two
+             replica buffers and the replication for call i+1 runs beside the
+             GEMM of call i (the host enqueues ahead).  NCCL's broadcast runs
+             32 CTAs and finishes only when all of them have had an SM, so the
+             GEMM is cut into two launches over column ranges of the same
+             replica: the first leaves 32 SMs free and lasts about as long as
+             the replication, the second uses the whole machine.  A lone call
+             pays the whole replication up front.
 """
 from . import blob as B
 from . import runtime as rt
@@ -96,21 +97,60 @@ class _NullCtx:
         return False
 
 
+def _wave_cost(tiles, clusters):
+    """Waves of the persistent GEMM that `tiles` tiles cost on `clusters` CTA pairs: whole
+    waves, plus a tail that the k-split shortens when it fills at most half of the pairs."""
+    full, rem = divmod(tiles, clusters)
+    if rem == 0:
+        return float(full)
+    parts = min(8, clusters // rem)
+    return full + (1.0 / parts + 0.1 if parts >= 2 else 1.0)
+
+
+def plan_two_parts(rows, n_cols, k, sm_count=148, comm_sms=32, comm_ms=0.5, tflops=1400.0):
+    """Column split (w1, w2) for `overlap="calls"`: the first launch leaves `comm_sms` SMs
+    to the NCCL kernel and covers the columns that keep it busy for about `comm_ms`
+    (the replication takes 0.2-0.4 ms for 128 MiB on 2-8 GPUs); the second launch has
+    the whole machine.  Among the widths within a few blocks of that target the one
+    with the cheapest tails wins.  w2 may be 0 (short GEMM: one launch with margin)."""
+    col_blocks = -(-n_cols // PAIR_TILE)
+    row_blocks = max(1, -(-rows // PAIR_TILE))
+    est_ms = 2.0 * rows * n_cols * k / (tflops * 1e9)
+    frac = min(1.0, comm_ms * (sm_count - comm_sms) / sm_count / max(est_ms, 1e-9))
+    if frac >= 0.85 or col_blocks < 4:
+        return n_cols, 0
+    target = max(1, round(frac * col_blocks))
+    c1 = (sm_count - comm_sms) // 2
+    c2 = sm_count // 2
+    best = None
+    for cb1 in range(target, min(col_blocks - 1, target + 3) + 1):
+        cost = _wave_cost(row_blocks * cb1, c1) * c2 / c1 + _wave_cost(row_blocks * (col_blocks - cb1), c2)
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, cb1)
+    w1 = min(best[1] * PAIR_TILE, n_cols)
+    return w1, n_cols - w1
+
+
 class RowShardedGemm:
     """C[rows of this rank, :] = epilogue(A[rows of this rank, :] . B), B replicated
     from rank `src` inside every call."""
 
     def __init__(self, session, rank, world, m_total, n, k, in_dtype=B.BF16, epilogue=B.EPI_NONE,
-                 src=0, sm_margin=4, slabs=None, device=None, overlap="slabs"):
+                 src=0, sm_margin=None, slabs=None, device=None, overlap="calls", comm_ms=0.5):
+        """overlap="slabs": sm_margin (default 8) SMs stay free during every slab GEMM.
+        overlap="calls": the first of two launches leaves sm_margin (default 32: NCCL
+        runs 32 CTAs here) SMs free, the second none (see plan_two_parts)."""
         import torch
         self.torch = torch
         self.sess, self.rank, self.world, self.src = session, rank, world, src
         self.m_total, self.n, self.k = m_total, n, k
         self.row0, self.rows = shard_rows(rank, world, m_total)
-        self.margin = sm_margin if world > 1 else 0
         if overlap not in ("slabs", "calls"):
             raise ValueError("overlap must be 'slabs' or 'calls'")
         self.overlap = overlap
+        if sm_margin is None:
+            sm_margin = 32 if overlap == "calls" else 8
+        self.margin = sm_margin if world > 1 else 0
         if slabs is None:
             slabs = [(0, n)] if overlap == "calls" else plan_slabs(self.rows, n, world, sm_margin=sm_margin)
         self.slabs = slabs
@@ -126,12 +166,38 @@ class RowShardedGemm:
             self.slab_sets = [[torch.empty((k, w), dtype=elt, device=device) for _, w in self.slabs]
                               for _ in range(2)]
             self.slab_bufs = self.slab_sets[0]
-        self.kernels = []
-        for j, (c0, w) in enumerate(self.slabs):
-            ldb = w if world > 1 else 0
-            self.kernels.append(session.kernel(B.gemm(
-                f"row_sharded_gemm_slab{j}", self.rows, w, k, in_dtype, epilogue,
-                ldb=ldb, ldc=n if w != n else 0, sm_margin=self.margin)))
+        # launches: (slab index, first column inside the slab, first column of C, kernel)
+        self.launches, self.launch_descs = [], []
+        if world > 1 and overlap == "calls" and len(self.slabs) == 1:
+            w1, w2 = plan_two_parts(self.rows, n, k, comm_sms=self.margin, comm_ms=comm_ms)
+            for j, (c0, w, margin) in enumerate([(0, w1, self.margin), (w1, w2, 0)]):
+                if w:
+                    desc = B.gemm(f"row_sharded_gemm_part{j}", self.rows, w, k, in_dtype, epilogue,
+                                  ldb=n if w != n else 0, ldc=n if w != n else 0, sm_margin=margin)
+                    self.launch_descs.append(desc)
+                    self.launches.append((0, c0, c0, session.kernel(desc)))
+        else:
+            for j, (c0, w) in enumerate(self.slabs):
+                ldb = w if world > 1 else 0
+                desc = B.gemm(f"row_sharded_gemm_slab{j}", self.rows, w, k, in_dtype, epilogue,
+                              ldb=ldb, ldc=n if w != n else 0, sm_margin=self.margin)
+                self.launch_descs.append(desc)
+                self.launches.append((j, 0, c0, session.kernel(desc)))
+        self.kernels = [l[3] for l in self.launches]
+        self.elt_bytes = 2
+
+    def launch_gemms(self, a_shard, c_shard, bufs=None, works=None):
+        """Enqueue the GEMM launches of one call on the current stream; with `works`
+        every launch first waits for the replication of its slab."""
+        bufs = bufs if bufs is not None else self.slab_bufs
+        waited = set()
+        for slab, b_col, c_col, kern in self.launches:
+            if works is not None and slab not in waited:
+                works[slab].wait()  # the current stream waits for this slab only
+                waited.add(slab)
+            self.sess.launch(kern, [a_shard.data_ptr(), bufs[slab].data_ptr() + self.elt_bytes * b_col,
+                                    c_shard.data_ptr() + 4 * c_col], wait=False)
+        return len(self.launches)
 
     def __call__(self, a_shard, b_full, c_shard, b_ready=None):
         """a_shard [rows,k], c_shard [rows,n] on this rank; b_full [k,n] valid on `src`
@@ -144,9 +210,7 @@ class RowShardedGemm:
                  event -> the broadcast waits for that CUDA event only."""
         torch = self.torch
         if self.world == 1:
-            self.sess.launch(self.kernels[0], [a_shard.data_ptr(), b_full.data_ptr(),
-                                               c_shard.data_ptr()], wait=False)
-            return 1
+            return self.launch_gemms(a_shard, c_shard, bufs=[b_full])
         cur = torch.cuda.current_stream()
         which = self.calls & 1
         self.calls += 1
@@ -158,16 +222,23 @@ class RowShardedGemm:
         # this set of slab buffers was last read by the GEMMs of two calls ago
         if self.done_events[which] is not None:
             self.comm_stream.wait_event(self.done_events[which])
-        works = replicate_slabs(b_full, bufs, self.slabs, self.src, self.rank == self.src,
-                                self.comm_stream)
-        for (c0, w), buf, work, kern in zip(self.slabs, bufs, works, self.kernels):
-            work.wait()  # the current stream waits for this slab only
-            self.sess.launch(kern, [a_shard.data_ptr(), buf.data_ptr(),
-                                    c_shard.data_ptr() + 4 * c0], wait=False)
+        if self.rank == self.src and len(self.slabs) == 1 and b_full.is_contiguous():
+            # one full-width slab: the source sends B from where it lies and multiplies
+            # with it in place (no packing copy competing with the GEMM for SMs)
+            if b_ready is not None and b_ready is not True:
+                cur.wait_event(b_ready)
+            bufs = self.slab_bufs = [b_full]
+            with torch.cuda.stream(self.comm_stream):
+                import torch.distributed as dist
+                works = [dist.broadcast(b_full, src=self.src, async_op=True)]
+        else:
+            works = replicate_slabs(b_full, bufs, self.slabs, self.src, self.rank == self.src,
+                                    self.comm_stream)
+        n_launch = self.launch_gemms(a_shard, c_shard, bufs, works)
         done = torch.cuda.Event()
         done.record(cur)
         self.done_events[which] = done
-        return len(self.slabs)
+        return n_launch
 
 
 def all_gather_rows(shard, full, rank, world, extent):

@@ -120,3 +120,19 @@ def test_overlap_across_calls_uses_one_full_width_slab():
         rows.RowShardedGemm(_NoSession(), 0, 1, 512, 512, 64, overlap="sometimes")
     g = rows.RowShardedGemm(_NoSession(), 0, 1, 512, 512, 64, overlap="calls")
     assert g.slabs == [(0, 512)]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_two_part_plan_for_the_benchmark_gemm(world):
+    """overlap="calls": the first launch (NCCL beside it) covers whole 256-column blocks and
+    about half a millisecond of work, the second the rest of the width."""
+    from mlir_extensions_b200 import dist as rows
+    n = k = 8192
+    w1, w2 = rows.plan_two_parts(65536 // world, n, k)
+    assert w1 + w2 == n and w1 % 256 == 0 and w1 > 0 and w2 > 0
+    est_ms = 2.0 * (65536 // world) * n * k / 1.4e12
+    first_ms = est_ms * (w1 / n) * 148 / 116
+    assert 0.4 <= first_ms <= 0.75
+    # a GEMM shorter than the replication keeps one launch with the margin
+    assert rows.plan_two_parts(1024, 8192, 1024) == (8192, 0)
+    assert rows.plan_two_parts(4096, 512, 512) == (512, 0)
