@@ -36,7 +36,13 @@ extern "C" {
  *                   dims = {M, N, K, lda, ldb, ldc}; row pitches in elements, 0 = dense
  *                   (memref strides are static in the IR, so they travel here too);
  *                   C = (C when IMEX_FLAG_ACCUMULATE else 0) + A.B, then + bias,
- *                   then epilogue
+ *                   then epilogue.  IMEX_FLAG_TRANS_A: A is stored [K,M] (C = A^T.B);
+ *                   IMEX_FLAG_TRANS_B: B is stored [N,K] (C = A.B^T); pitches are
+ *                   those of the arrays as stored.  out_dtype F32, or BF16 / F16:
+ *                   f32 accumulation, one rounding to 16 bits at the end (the
+ *                   f16-result GEMMs of test/Integration/Dialect/XeGPU/WG/
+ *                   gemm_4kx4kx4k_f16_f16_f16.mlir; operand layouts of
+ *                   gemm_4kx4kx4k_transpose_{a,b}.mlir)
  *   SOFTMAX         X[rows,cols], Y[rows,cols]           dims = {rows, cols}
  *   REDUCE_ROWS     X[rows,cols], Y[rows]                dims = {rows, cols}
  *                   Y[r] = (Y[r] when ACCUMULATE else 0) + sum_c X[r,c]
@@ -71,7 +77,9 @@ enum ImexEpilogue { IMEX_EPI_NONE = 0, IMEX_EPI_RELU = 1, IMEX_EPI_SILU = 2 };
 enum ImexFlags {
   IMEX_FLAG_ACCUMULATE = 1u << 0, /* output is read as the initial value */
   IMEX_FLAG_BIAS = 1u << 1,       /* GEMM: 4th pointer is bias[N] (f32)   */
-  IMEX_FLAG_SOFTMAX_NEG_INF = 1u << 2 /* PlaidML form: max starts at -inf, cmpf ogt */
+  IMEX_FLAG_SOFTMAX_NEG_INF = 1u << 2, /* PlaidML form: max starts at -inf, cmpf ogt */
+  IMEX_FLAG_TRANS_A = 1u << 3,    /* GEMM: A stored [K,M]                 */
+  IMEX_FLAG_TRANS_B = 1u << 4     /* GEMM: B stored [N,K]                 */
 };
 
 typedef struct ImexBlobHeader {

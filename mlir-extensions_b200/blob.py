@@ -14,7 +14,7 @@ OP_GEMM, OP_SOFTMAX, OP_REDUCE_ROWS, OP_REDUCE_LEADING, OP_REDUCE_ALL = 1, 2, 3,
 OP_TRANSPOSE2D, OP_TRANSPOSE3D, OP_ELTWISE, OP_FILL_UNIFORM, OP_FILL_NORMAL = 6, 7, 8, 9, 10
 F32, BF16, F16, I32 = 1, 2, 3, 4
 EPI_NONE, EPI_RELU, EPI_SILU = 0, 1, 2
-FLAG_ACCUMULATE, FLAG_BIAS, FLAG_SOFTMAX_NEG_INF = 1, 2, 4
+FLAG_ACCUMULATE, FLAG_BIAS, FLAG_SOFTMAX_NEG_INF, FLAG_TRANS_A, FLAG_TRANS_B = 1, 2, 4, 8, 16
 
 DTYPE_BYTES = {F32: 4, I32: 4, BF16: 2, F16: 2}
 _DESC = struct.Struct("<64s6I6q2f")  # ImexKernelDesc, 144 bytes
@@ -59,11 +59,14 @@ def unpack_blob(data):
 
 
 def gemm(name, M, N, K, in_dtype=BF16, epilogue=EPI_NONE, accumulate=False, bias=False,
-         lda=0, ldb=0, ldc=0, sm_margin=0):
-    """lda/ldb/ldc: row pitches in elements (0 = dense); sm_margin: SMs the
-    persistent kernel leaves free (for a collective running beside it)."""
-    flags = (FLAG_ACCUMULATE if accumulate else 0) | (FLAG_BIAS if bias else 0)
-    return KernelDesc(name, OP_GEMM, in_dtype, F32, epilogue, flags, (M, N, K, lda, ldb, ldc),
+         lda=0, ldb=0, ldc=0, sm_margin=0, trans_a=False, trans_b=False, out_dtype=F32):
+    """lda/ldb/ldc: row pitches of the arrays as stored, in elements (0 = dense);
+    sm_margin: SMs the persistent kernel leaves free (for a collective running
+    beside it); trans_a: A is stored [K,M]; trans_b: B is stored [N,K]; out_dtype
+    BF16/F16: f32 accumulation, one rounding at the end."""
+    flags = ((FLAG_ACCUMULATE if accumulate else 0) | (FLAG_BIAS if bias else 0)
+             | (FLAG_TRANS_A if trans_a else 0) | (FLAG_TRANS_B if trans_b else 0))
+    return KernelDesc(name, OP_GEMM, in_dtype, out_dtype, epilogue, flags, (M, N, K, lda, ldb, ldc),
                       sm_margin=sm_margin)
 
 

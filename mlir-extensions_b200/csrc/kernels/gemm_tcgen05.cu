@@ -277,6 +277,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 bool gemm_tcgen05_supported(const GemmProblem &p) {
   if (p.in_dtype != kBF16 && p.in_dtype != kF16) return false;
+  if (p.trans_a || p.trans_b || p.out_dtype != kF32) return false;  // the pair kernel takes those
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return false;
   if (p.K % 8 || p.N % 8) return false;  // TMA row pitch must be a multiple of 16 bytes
   if (p.lda % 8 || p.ldb % 8 || p.ldc % 4) return false;

@@ -32,6 +32,9 @@
 #include "tcgen05_host.h"
 #include "tcgen05_ptx.cuh"
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
@@ -78,6 +81,7 @@ struct PairParams {
   float *partials;
   int epilogue;
   int accumulate;
+  int out_dtype;  // kF32 (TMA tile stores) or kBF16 / kF16 (packed 16-byte stores)
   uint32_t idesc;
   long long *stats;   // optional per-CTA cycle counters (nullptr = off), 8 per CTA
 };
@@ -92,6 +96,14 @@ struct WorkItem {
 template <bool STATS> __device__ __forceinline__ long long now() {
   if constexpr (STATS) return clock64();
   return 0;
+}
+
+// 16-bit storage formats of C (dt = kBF16 or kF16), round to nearest even
+__device__ __forceinline__ uint16_t f32_to_half_bits(float v, int dt) {
+  return dt == kBF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
+__device__ __forceinline__ float half_bits_to_f32(uint16_t b, int dt) {
+  return dt == kBF16 ? __uint_as_float(static_cast<uint32_t>(b) << 16) : __half2float(__ushort_as_half(b));
 }
 
 __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams &p, int &mb, int &nb) {
@@ -122,7 +134,9 @@ __device__ __forceinline__ WorkItem item_at(int idx, const PairParams &p) {
   return w;
 }
 
-template <int STAGES, int BKT, bool STATS>
+// TA: A is stored [K,M] (M-major operand: boxes of 64 m x BKT k, like B below);
+// TB: B is stored [N,K] (K-major operand: boxes of 64 k x 128 n, like A below).
+template <int STAGES, int BKT, bool STATS, bool TA, bool TB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
@@ -202,11 +216,22 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          if constexpr (!TA) {
 #pragma unroll
-          for (int j = 0; j < BK / 64; ++j)
-            tma_load_2d_pair(a_dst + j * A_BOX_BYTES, &tmap_a, kb * BK + j * 64, row0, leader_full);
-          tma_load_2d_pair(b_dst, &tmap_b, col0, kb * BK, leader_full);
-          tma_load_2d_pair(b_dst + B_BOX_BYTES, &tmap_b, col0 + 64, kb * BK, leader_full);
+            for (int j = 0; j < BK / 64; ++j)
+              tma_load_2d_pair(a_dst + j * A_BOX_BYTES, &tmap_a, kb * BK + j * 64, row0, leader_full);
+          } else {
+            tma_load_2d_pair(a_dst, &tmap_a, row0, kb * BK, leader_full);
+            tma_load_2d_pair(a_dst + B_BOX_BYTES, &tmap_a, row0 + 64, kb * BK, leader_full);
+          }
+          if constexpr (!TB) {
+            tma_load_2d_pair(b_dst, &tmap_b, col0, kb * BK, leader_full);
+            tma_load_2d_pair(b_dst + B_BOX_BYTES, &tmap_b, col0 + 64, kb * BK, leader_full);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BK / 64; ++j)
+              tma_load_2d_pair(b_dst + j * A_BOX_BYTES, &tmap_b, kb * BK + j * 64, col0, leader_full);
+          }
           w_issue += now<STATS>() - t1;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -258,9 +283,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major operand: 64-k boxes of 128 rows, 32 bytes per K16 step inside a box;
+            // MN-major operand: boxes of 64 rows/columns x BKT k, 16 k-rows (2 KB) per step
             const uint64_t a_desc =
-                make_smem_desc(a_addr + (k >> 2) * A_BOX_BYTES + (k & 3) * (UMMA_K * 2), 16, 1024);
-            const uint64_t b_desc = make_smem_desc(b_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+                TA ? make_smem_desc(a_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024)
+                   : make_smem_desc(a_addr + (k >> 2) * A_BOX_BYTES + (k & 3) * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc =
+                TB ? make_smem_desc(b_addr + (k >> 2) * A_BOX_BYTES + (k & 3) * (UMMA_K * 2), 16, 1024)
+                   : make_smem_desc(b_addr + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
             tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb != w.kb0 || k) ? 1u : 0u);
           }
           tcgen05_commit_pair(empty_bar(stage), 3);
@@ -325,6 +355,42 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tma_store_2d(&tmap_p, buf, c0,
                          w.slot * PAIR_M + static_cast<int>(cta_rank) * BM + lane_group * 32);
             tma_store_commit();
+          }
+        } else if (p.out_dtype != kF32) {
+          // 16-bit C: each lane owns 32 consecutive columns of its row = 64 bytes,
+          // written as four 16-byte stores (f32 accumulate / bias / epilogue first,
+          // one rounding to bf16 or f16 at the end)
+          if (row < p.M && col0 < p.N) {
+            uint16_t *c16 = reinterpret_cast<uint16_t *>(p.C) + static_cast<size_t>(row) * p.ldc;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int col = col0 + j;
+              if (col < p.N) {  // N is a multiple of 8 on this path
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                if (p.accumulate) {
+                  const uint4 c = *reinterpret_cast<const uint4 *>(c16 + col);
+                  const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                  for (int e = 0; e < 8; ++e)
+                    v[e] += half_bits_to_f32(static_cast<uint16_t>(cw[e >> 1] >> ((e & 1) * 16)),
+                                             p.out_dtype);
+                }
+                if (p.bias) {
+                  const float4 b0 = *reinterpret_cast<const float4 *>(p.bias + col);
+                  const float4 b1 = *reinterpret_cast<const float4 *>(p.bias + col + 4);
+                  v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                  v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                }
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2)
+                  o[e >> 1] = static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v[e], p.epilogue), p.out_dtype)) |
+                              (static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v[e + 1], p.epilogue), p.out_dtype)) << 16);
+                *reinterpret_cast<uint4 *>(c16 + col) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
           }
         } else if (p.accumulate) {
           // C is also an input: per-thread row segments, read-modify-write in place
@@ -426,6 +492,27 @@ gemm_splitk_fixup_kernel(const PairParams p) {
           p.partials + (static_cast<size_t>(t * p.split + part) * PAIR_M + lr) * BN + (threadIdx.x & 63) * 4);
       v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
     }
+    if (p.out_dtype != kF32) {
+      uint16_t *c = reinterpret_cast<uint16_t *>(p.C) + static_cast<size_t>(row) * p.ldc + col;
+      if (p.accumulate) {
+        const uint2 c0 = *reinterpret_cast<const uint2 *>(c);
+        v.x += half_bits_to_f32(static_cast<uint16_t>(c0.x), p.out_dtype);
+        v.y += half_bits_to_f32(static_cast<uint16_t>(c0.x >> 16), p.out_dtype);
+        v.z += half_bits_to_f32(static_cast<uint16_t>(c0.y), p.out_dtype);
+        v.w += half_bits_to_f32(static_cast<uint16_t>(c0.y >> 16), p.out_dtype);
+      }
+      if (p.bias) {
+        const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      }
+      uint2 o;
+      o.x = static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.x, p.epilogue), p.out_dtype)) |
+            (static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.y, p.epilogue), p.out_dtype)) << 16);
+      o.y = static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.z, p.epilogue), p.out_dtype)) |
+            (static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.w, p.epilogue), p.out_dtype)) << 16);
+      *reinterpret_cast<uint2 *>(c) = o;
+      continue;
+    }
     float *c = p.C + static_cast<size_t>(row) * p.ldc + col;
     if (p.accumulate) {
       const float4 c0 = *reinterpret_cast<const float4 *>(c);
@@ -450,13 +537,31 @@ size_t gemm_tcgen05_workspace_bytes() {
   return static_cast<size_t>(sm_count() / 2) * PAIR_M * BN * sizeof(float);
 }
 
+bool gemm_tcgen05_2cta_supported(const GemmProblem &p) {
+  if (p.in_dtype != kBF16 && p.in_dtype != kF16) return false;
+  if (p.out_dtype != kF32 && p.out_dtype != kBF16 && p.out_dtype != kF16) return false;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return false;
+  if (p.M > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX) return false;
+  // TMA: the contiguous extent and the row pitch of every array are whole 16-byte units
+  const int64_t a_inner = p.trans_a ? p.M : p.K, b_inner = p.trans_b ? p.K : p.N;
+  const int64_t c_unit = p.out_dtype == kF32 ? 4 : 8;
+  if (a_inner % 8 || b_inner % 8 || p.N % c_unit) return false;
+  if (p.lda % 8 || p.ldb % 8 || p.ldc % c_unit) return false;
+  if ((p.lda && p.lda < a_inner) || (p.ldb && p.ldb < b_inner) || (p.ldc && p.ldc < p.N)) return false;
+  auto al = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  return al(p.A) && al(p.B) && al(p.C) && (!p.bias || al(p.bias));
+}
+
 bool gemm_tcgen05_2cta_preferred(const GemmProblem &p) {
-  // a single row block gains nothing from pairing
-  return gemm_tcgen05_supported(p) && p.M > 128 && !getenv("IMEX_B200_GEMM_1CTA");
+  // a single row block gains nothing from pairing, but only this kernel takes
+  // transposed operands and 16-bit outputs
+  if (!gemm_tcgen05_2cta_supported(p)) return false;
+  if (p.trans_a || p.trans_b || p.out_dtype != kF32) return true;
+  return p.M > 128 && !getenv("IMEX_B200_GEMM_1CTA");
 }
 
 cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cudaStream_t stream) {
-  if (!gemm_tcgen05_supported(g)) return cudaErrorInvalidValue;
+  if (!gemm_tcgen05_2cta_supported(g)) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int variant = 1;  // 0: 6 stages x 64 k, 1: 3 stages x 128 k, 2: 4 stages x 64 k
@@ -468,23 +573,33 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
     auto set = [](const void *fn, int bytes) {
       return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     };
-    cudaError_t e1 = set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false>, smem_bytes(3, 128));
-    cudaError_t e2 = set((const void *)gemm_tcgen05_2cta_kernel<3, 128, true>, smem_bytes(3, 128));
-    cudaError_t e3 = set((const void *)gemm_tcgen05_2cta_kernel<6, 64, false>, smem_bytes(6, 64));
-    cudaError_t e4 = set((const void *)gemm_tcgen05_2cta_kernel<4, 64, false>, smem_bytes(4, 64));
-    attr_err = e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3 != cudaSuccess ? e3 : e4;
+    const cudaError_t e[] = {
+        set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, false, false>, smem_bytes(3, 128)),
+        set((const void *)gemm_tcgen05_2cta_kernel<3, 128, true, false, false>, smem_bytes(3, 128)),
+        set((const void *)gemm_tcgen05_2cta_kernel<6, 64, false, false, false>, smem_bytes(6, 64)),
+        set((const void *)gemm_tcgen05_2cta_kernel<4, 64, false, false, false>, smem_bytes(4, 64)),
+        set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, true, false>, smem_bytes(3, 128)),
+        set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, false, true>, smem_bytes(3, 128)),
+        set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, true, true>, smem_bytes(3, 128))};
+    for (cudaError_t x : e)
+      if (x != cudaSuccess && attr_err == cudaSuccess) attr_err = x;
   });
-  const int BK = variant == 1 ? 128 : 64;
+  const bool transposed = g.trans_a || g.trans_b;  // served by the 3 x 128 kernels only
+  const int BK = (variant == 1 || transposed) ? 128 : 64;
   if (attr_err != cudaSuccess) return attr_err;
 
-  const int64_t lda = g.lda > 0 ? g.lda : g.K;
-  const int64_t ldb = g.ldb > 0 ? g.ldb : g.N;
+  const int64_t lda = g.lda > 0 ? g.lda : (g.trans_a ? g.M : g.K);
+  const int64_t ldb = g.ldb > 0 ? g.ldb : (g.trans_b ? g.K : g.N);
   const int64_t ldc = g.ldc > 0 ? g.ldc : g.N;
   CUtensorMap ta, tb;
-  if (!make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM, lda)) return cudaErrorNotSupported;
-  if (!make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK, ldb)) return cudaErrorNotSupported;
-  CUtensorMap tc_;
-  if (!make_map_f32_out(&tc_, g.C, g.N, g.M, ldc)) return cudaErrorNotSupported;
+  if (!(g.trans_a ? make_map(&ta, g.A, g.in_dtype, g.M, g.K, BK, lda)
+                  : make_map(&ta, g.A, g.in_dtype, g.K, g.M, BM, lda)))
+    return cudaErrorNotSupported;
+  if (!(g.trans_b ? make_map(&tb, g.B, g.in_dtype, g.K, g.N, BN_HALF, ldb)
+                  : make_map(&tb, g.B, g.in_dtype, g.N, g.K, BK, ldb)))
+    return cudaErrorNotSupported;
+  CUtensorMap tc_{};  // the f32 store side; a 16-bit C is written with plain stores
+  if (g.out_dtype == kF32 && !make_map_f32_out(&tc_, g.C, g.N, g.M, ldc)) return cudaErrorNotSupported;
 
   PairParams p;
   p.C = g.C;
@@ -505,15 +620,18 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   p.k_blocks = (p.K + BK - 1) / BK;
   p.epilogue = g.epilogue;
   p.accumulate = g.accumulate ? 1 : 0;
+  p.out_dtype = g.out_dtype;
   p.stats = nullptr;
   static long long *stats_buf = nullptr;
-  const bool want_stats = with_stats && variant == 1;  // development aid (IMEX_GEMM_STATS=1)
+  const bool want_stats = with_stats && variant == 1 && !transposed;  // development aid (IMEX_GEMM_STATS=1)
   if (want_stats) {
     if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 148 * sizeof(long long));
     p.stats = stats_buf;
   }
   const uint32_t fmt = g.in_dtype == kBF16 ? 1u : 0u;
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
+  // bit 15 / 16: A / B operand is MN-major (A when stored [K,M]; B when stored [K,N])
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.trans_a ? 1u : 0u) << 15) |
+            ((g.trans_b ? 0u : 1u) << 16) |
             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(PAIR_M >> 4) << 24);
 
   int usable = sm_count() - (g.sm_margin > 0 ? g.sm_margin : 0);
@@ -545,14 +663,21 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
     return cudaErrorNotSupported;
   const int clusters = p.num_items < max_clusters ? p.num_items : max_clusters;
   const dim3 grid(2 * clusters), block(NUM_THREADS);
-  if (variant == 0)
-    gemm_tcgen05_2cta_kernel<6, 64, false><<<grid, block, smem_bytes(6, 64), stream>>>(ta, tb, tc_, tp, p);
+  const int sm3 = smem_bytes(3, 128);
+  if (g.trans_a && g.trans_b)
+    gemm_tcgen05_2cta_kernel<3, 128, false, true, true><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
+  else if (g.trans_a)
+    gemm_tcgen05_2cta_kernel<3, 128, false, true, false><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
+  else if (g.trans_b)
+    gemm_tcgen05_2cta_kernel<3, 128, false, false, true><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
+  else if (variant == 0)
+    gemm_tcgen05_2cta_kernel<6, 64, false, false, false><<<grid, block, smem_bytes(6, 64), stream>>>(ta, tb, tc_, tp, p);
   else if (variant == 2)
-    gemm_tcgen05_2cta_kernel<4, 64, false><<<grid, block, smem_bytes(4, 64), stream>>>(ta, tb, tc_, tp, p);
+    gemm_tcgen05_2cta_kernel<4, 64, false, false, false><<<grid, block, smem_bytes(4, 64), stream>>>(ta, tb, tc_, tp, p);
   else if (with_stats)
-    gemm_tcgen05_2cta_kernel<3, 128, true><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, tp, p);
+    gemm_tcgen05_2cta_kernel<3, 128, true, false, false><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
   else
-    gemm_tcgen05_2cta_kernel<3, 128, false><<<grid, block, smem_bytes(3, 128), stream>>>(ta, tb, tc_, tp, p);
+    gemm_tcgen05_2cta_kernel<3, 128, false, false, false><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
   if (p.split_tiles) {
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return le;

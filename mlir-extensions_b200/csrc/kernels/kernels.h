@@ -22,13 +22,18 @@ enum Status : unsigned {
 };
 
 struct GemmProblem {
-  const void *A;      // [M,K] row-major, in_dtype
-  const void *B;      // [K,N] row-major, in_dtype
-  float *C;           // [M,N] row-major f32
-  const float *bias;  // [N] or nullptr
+  const void *A;      // [M,K] row-major, in_dtype ([K,M] when trans_a)
+  const void *B;      // [K,N] row-major, in_dtype ([N,K] when trans_b)
+  float *C;           // [M,N] row-major; elements are out_dtype (f32 unless stated)
+  const float *bias;  // [N] f32 or nullptr
   int64_t M, N, K;
-  int64_t lda = 0, ldb = 0, ldc = 0;  // row pitches in elements; 0 = dense (K, N, N)
+  // row pitches of the arrays as stored, in elements; 0 = dense
+  int64_t lda = 0, ldb = 0, ldc = 0;
   int in_dtype;       // DType
+  int out_dtype = kF32;  // kF32, or kBF16 / kF16: f32 accumulation (and f32 C input when
+                         // `accumulate`), one rounding to 16 bits after bias + epilogue
+  bool trans_a = false;  // C = A^T . B with A stored [K,M]
+  bool trans_b = false;  // C = A . B^T with B stored [N,K]
   int epilogue;       // Epilogue
   bool accumulate;    // C is read as the initial value
   int sm_margin = 0;  // SMs the persistent kernels leave unused
@@ -43,12 +48,14 @@ cudaError_t launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
 
 // bf16/f16 -> f32 on the 5th-gen tensor cores (tcgen05.mma, TMEM
 // accumulators, TMA-fed 128B-swizzled smem ring, persistent tiles).
-// Needs K % 8 == 0, N % 8 == 0, pitches that keep rows 16-byte aligned and
-// 16-byte aligned A, B, C.
+// Needs the contiguous extents of A and B (K or M; N or K) to be multiples of
+// 8, pitches that keep rows 16-byte aligned and 16-byte aligned A, B, C.
 bool gemm_tcgen05_supported(const GemmProblem &p);
 cudaError_t launch_gemm_tcgen05(const GemmProblem &p, unsigned *status,
                                 cudaStream_t stream);
-// Same contract on CTA pairs (tcgen05.mma.cta_group::2, 256x256 tile per pair).
+// CTA pairs (tcgen05.mma.cta_group::2, 256x256 tile per pair); also takes
+// transposed operands (trans_a / trans_b) and bf16 / f16 outputs.
+bool gemm_tcgen05_2cta_supported(const GemmProblem &p);
 bool gemm_tcgen05_2cta_preferred(const GemmProblem &p);
 size_t gemm_tcgen05_workspace_bytes();  // scratch the pair kernel can use for a k-split tail
 cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &p, unsigned *status,

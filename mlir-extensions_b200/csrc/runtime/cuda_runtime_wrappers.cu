@@ -261,8 +261,8 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
   case IMEX_OP_GEMM: {
     const bool has_bias = d.flags & IMEX_FLAG_BIAS;
     need(has_bias ? 4 : 3);
-    if (d.out_dtype != IMEX_F32)
-      throw std::runtime_error("gpuLaunchKernel: gemm output must be f32");
+    if (d.out_dtype != IMEX_F32 && d.out_dtype != IMEX_BF16 && d.out_dtype != IMEX_F16)
+      throw std::runtime_error("gpuLaunchKernel: gemm output must be f32, bf16 or f16");
     imex::GemmProblem g;
     g.A = ptrs[0];
     g.B = ptrs[1];
@@ -275,11 +275,15 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     g.ldb = d.dims[4];
     g.ldc = d.dims[5];
     g.in_dtype = static_cast<int>(d.in_dtype);
+    g.out_dtype = static_cast<int>(d.out_dtype);
+    g.trans_a = d.flags & IMEX_FLAG_TRANS_A;
+    g.trans_b = d.flags & IMEX_FLAG_TRANS_B;
     g.epilogue = static_cast<int>(d.epilogue);
     g.accumulate = acc;
     g.sm_margin = static_cast<int>(d.sm_margin);
     if (g.M < 0 || g.N < 0 || g.K < 0) throw std::runtime_error("gpuLaunchKernel: negative gemm dims");
-    if ((g.lda && g.lda < g.K) || (g.ldb && g.ldb < g.N) || (g.ldc && g.ldc < g.N))
+    if ((g.lda && g.lda < (g.trans_a ? g.M : g.K)) || (g.ldb && g.ldb < (g.trans_b ? g.K : g.N)) ||
+        (g.ldc && g.ldc < g.N))
       throw std::runtime_error("gpuLaunchKernel: gemm row pitch smaller than the row");
     const bool force_simt = getenv("IMEX_B200_FORCE_SIMT_GEMM") != nullptr;
     bool done = false;

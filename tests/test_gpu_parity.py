@@ -236,6 +236,108 @@ def test_gemm_with_row_pitches(pkg, sess, kind):
         assert oracle.rel_frobenius(got[:, col_c:col_c + N], ref) <= GEMM_FROB_TOL
 
 
+# --------------------------------------------- transposed operands, 16-bit results
+# (reference: test/Integration/Dialect/XeGPU/WG/gemm_4kx4kx4k_transpose_{a,b}.mlir store
+#  A as [K,M] / B as [N,K]; gemm_4kx4kx4k_f16_f16_f16.mlir returns f16.  The reference
+#  checks against its own CPU GEMM of the un-transposed arrays — so does this.)
+def _gemm_general(pkg, sess, A_bits, B_bits, in_dtype, trans_a=False, trans_b=False, out="f32",
+                  epilogue=0, C_init=None, bias=None):
+    """A_bits [M,K], B_bits [K,N] in logical orientation; stored transposed on request."""
+    B = pkg.blob
+    M, K = A_bits.shape
+    _, N = B_bits.shape
+    A_st = np.ascontiguousarray(A_bits.T) if trans_a else A_bits
+    B_st = np.ascontiguousarray(B_bits.T) if trans_b else B_bits
+    out_dt = {"f32": B.F32, "bf16": B.BF16, "f16": B.F16}[out]
+    np_out = np.float32 if out == "f32" else np.uint16
+    dA, dB = sess.upload(A_st), sess.upload(B_st)
+    if C_init is not None:
+        dC = sess.upload(C_init)
+    else:
+        poison = np.full((M, N), np.nan, np.float32) if out == "f32" else np.full((M, N), 0x7FC1, np.uint16)
+        dC = sess.upload(poison)
+    args = [dA, dB, dC] + ([sess.upload(bias)] if bias is not None else [])
+    sess.run(B.gemm("general", M, N, K, in_dtype, epilogue, accumulate=C_init is not None,
+                    bias=bias is not None, trans_a=trans_a, trans_b=trans_b, out_dtype=out_dt), args)
+    return sess.download(dC, (M, N), np_out)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16"])
+@pytest.mark.parametrize("trans", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (512, 768, 320), (264, 520, 200), (1000, 1000, 1000),
+                                   (128, 256, 64), (4096, 512, 2048)])
+def test_gemm_transposed_operands(pkg, sess, kind, trans, shape):
+    M, N, K = shape
+    conv = oracle.to_bf16_bits if kind == "bf16" else oracle.to_f16_bits
+    Ab = conv(oracle.fill_uniform((M, K), 13, -1.0, 1.0))
+    Bb = conv(oracle.fill_uniform((K, N), 14, -1.0, 1.0))
+    dt = pkg.blob.BF16 if kind == "bf16" else pkg.blob.F16
+    got = _gemm_general(pkg, sess, Ab, Bb, dt, trans_a=trans[0], trans_b=trans[1])
+    assert sess.last_kernel() == "gemm_tcgen05_2cta"
+    ref = oracle.matmul_x16_f32(Ab, Bb, kind == "bf16")
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= GEMM_FROB_TOL
+    assert oracle.allclose(got, ref)
+    # the same products in the same k order as the plain layout: identical bits
+    plain = _gemm(pkg, sess, Ab, Bb, dt)
+    if sess.last_kernel() == "gemm_tcgen05_2cta":
+        assert got.tobytes() == plain.tobytes()
+
+
+@pytest.mark.parametrize("kind,out", [("f16", "f16"), ("bf16", "bf16"), ("bf16", "f16")])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (520, 264, 200), (1000, 1000, 1000), (64, 512, 4096)])
+def test_gemm_16bit_result(pkg, sess, kind, out, shape):
+    M, N, K = shape
+    conv = oracle.to_bf16_bits if kind == "bf16" else oracle.to_f16_bits
+    rnd = oracle.to_bf16_bits if out == "bf16" else oracle.to_f16_bits
+    back = oracle.bf16_bits_to_f32 if out == "bf16" else oracle.f16_bits_to_f32
+    Ab = conv(oracle.fill_uniform((M, K), 15, -1.0, 1.0))
+    Bb = conv(oracle.fill_uniform((K, N), 16, -1.0, 1.0))
+    dt = pkg.blob.BF16 if kind == "bf16" else pkg.blob.F16
+    got = _gemm_general(pkg, sess, Ab, Bb, dt, out=out)
+    assert sess.last_kernel() == "gemm_tcgen05_2cta"
+    ref32 = oracle.matmul_x16_f32(Ab, Bb, kind == "bf16")
+    # exactly the f32 result of the f32-output kernel, rounded once
+    got32 = _gemm(pkg, sess, Ab, Bb, dt)
+    if sess.last_kernel() == "gemm_tcgen05_2cta":
+        assert got.tobytes() == rnd(got32).tobytes()
+    assert oracle.rel_frobenius(back(got), back(rnd(ref32))) <= GEMM_FROB_TOL + 2.0 ** -8
+
+
+def test_gemm_16bit_result_with_bias_epilogue_accumulate_and_transposes(pkg, sess):
+    M, N, K = 520, 776, 264
+    rng = np.random.default_rng(17)
+    Ab = oracle.to_f16_bits(rng.normal(0, 0.5, (M, K)).astype(np.float32))
+    Bb = oracle.to_f16_bits(rng.normal(0, 0.5, (K, N)).astype(np.float32))
+    C0 = oracle.to_f16_bits(rng.normal(0, 1, (M, N)).astype(np.float32))
+    bias = rng.normal(0, 1, N).astype(np.float32)
+    got = _gemm_general(pkg, sess, Ab, Bb, pkg.blob.F16, trans_a=True, trans_b=True, out="f16",
+                        epilogue=2, C_init=C0.copy(), bias=bias)
+    assert sess.last_kernel() == "gemm_tcgen05_2cta"
+    ref = _oracle_gemm(Ab, Bb, "f16", 2, oracle.f16_bits_to_f32(C0), bias)
+    assert oracle.rel_frobenius(oracle.f16_bits_to_f32(got), ref) <= GEMM_FROB_TOL + 2.0 ** -10
+
+
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+def test_gemm_transposed_and_16bit_on_the_exact_simt_path(pkg, sess, kind):
+    """Shapes TMA cannot take (extents not multiples of 8) and f32 inputs: same flags,
+    bit-exact against the oracle's loop order."""
+    M, N, K = 37, 53, 29
+    A = oracle.fill_uniform((M, K), 18, -1.0, 1.0)
+    Bm = oracle.fill_uniform((K, N), 19, -1.0, 1.0)
+    if kind == "bf16":
+        Ab, Bb, dt = oracle.to_bf16_bits(A), oracle.to_bf16_bits(Bm), pkg.blob.BF16
+        ref = oracle.matmul_x16_f32(Ab, Bb, True)
+    else:
+        Ab, Bb, dt = A, Bm, pkg.blob.F32
+        ref = oracle.matmul_f32(A, Bm)
+    got = _gemm_general(pkg, sess, Ab, Bb, dt, trans_a=True, trans_b=True)
+    assert sess.last_kernel() == "gemm_simt"
+    assert got.tobytes() == ref.tobytes()
+    got16 = _gemm_general(pkg, sess, Ab, Bb, dt, trans_b=True, out="f16")
+    assert got16.tobytes() == oracle.to_f16_bits(ref).tobytes()
+
+
 @pytest.mark.parametrize("variant", ["0", "1", "2"])
 @pytest.mark.parametrize("shape", [(512, 1024, 128), (300, 520, 200), (1000, 1544, 72), (2304, 4608, 256),
                                    (20000, 512, 64)])
