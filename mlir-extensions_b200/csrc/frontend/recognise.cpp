@@ -11,6 +11,8 @@ const char *kindName(Kind k) {
   switch (k) {
   case Kind::Unknown: return "unknown";
   case Kind::Matmul: return "matmul";
+  case Kind::Add: return "add";
+  case Kind::BroadcastRow: return "broadcast_row";
   case Kind::Relu: return "relu";
   case Kind::Sigmoid: return "sigmoid";
   case Kind::Mul: return "mul";
@@ -121,9 +123,12 @@ bool isRowVectorMap(const AffineMap &m) {
 
 Classified classify(const Op &op, const ConstantTable &constants) {
   Classified c;
-  if (op.name == "linalg.matmul") {
+  if (op.name == "linalg.matmul" || op.name == "linalg.matmul_transpose_a" ||
+      op.name == "linalg.matmul_transpose_b") {
     c.kind = Kind::Matmul;
-    c.expr = "linalg.matmul";
+    c.expr = op.name;
+    c.transA = op.name == "linalg.matmul_transpose_a";
+    c.transB = op.name == "linalg.matmul_transpose_b";
     return c;
   }
   if (op.name == "linalg.fill") {
@@ -158,10 +163,12 @@ Classified classify(const Op &op, const ConstantTable &constants) {
   // ---- contractions ------------------------------------------------------
   if (nd == 3 && nIn == 2 && nOut == 1 && op.iterators.size() == 3 &&
       op.iterators[0] == "parallel" && op.iterators[1] == "parallel" &&
-      op.iterators[2] == "reduction" && mapIs(op.maps[0], {0, 2}) && mapIs(op.maps[1], {2, 1}) &&
-      mapIs(outMap, {0, 1})) {
+      op.iterators[2] == "reduction" && (mapIs(op.maps[0], {0, 2}) || mapIs(op.maps[0], {2, 0})) &&
+      (mapIs(op.maps[1], {2, 1}) || mapIs(op.maps[1], {1, 2})) && mapIs(outMap, {0, 1})) {
     if (y == "addf(mulf(in0,in1),out0)" || y == "addf(mulf(extf(in0),extf(in1)),out0)") {
       c.kind = Kind::Matmul;
+      c.transA = mapIs(op.maps[0], {2, 0});
+      c.transB = mapIs(op.maps[1], {1, 2});
       return c;
     }
     c.why = "matmul-shaped generic with body " + y + " (only f32 mulf/addf is mapped to a GEMM)";
@@ -248,6 +255,14 @@ Classified classify(const Op &op, const ConstantTable &constants) {
   }
   if (identityAll && nIn == 2 && y == "mulf(in0,in1)") {
     c.kind = Kind::Mul;
+    return c;
+  }
+  if (identityAll && nIn == 2 && (y == "addf(in0,in1)" || y == "addf(in1,in0)")) {
+    c.kind = Kind::Add;
+    return c;
+  }
+  if (nd == 2 && nIn == 1 && nOut == 1 && y == "in0" && mapIs(op.maps[0], {1}) && outMap.isIdentity()) {
+    c.kind = Kind::BroadcastRow;
     return c;
   }
   if (nd == 2 && nIn == 2 && op.maps[0].isIdentity() && isRowVectorMap(op.maps[1]) &&

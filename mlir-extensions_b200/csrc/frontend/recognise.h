@@ -23,7 +23,10 @@ namespace fe {
 
 enum class Kind {
   Unknown,
-  Matmul,        // C[d0,d1] += A[d0,d2] * B[d2,d1]   (named op or generic)
+  Matmul,        // C[d0,d1] += A[d0,d2] * B[d2,d1]   (named op or generic; transA / transB:
+                 // A indexed [d2,d0] / B indexed [d1,d2], linalg.matmul_transpose_a / _b)
+  Add,           // elementwise x + y
+  BroadcastRow,  // out[i,j] = v[j]   (the bias broadcast in front of an Add)
   Relu,          // select(cmpf ugt x, 0 ; x, 0)
   Sigmoid,       // 1 / (exp(-x) + 1)
   Mul,           // elementwise x * y
@@ -46,6 +49,8 @@ struct Classified {
   Kind kind = Kind::Unknown;
   std::string expr;           // canonical form of the body, for diagnostics
   bool rowMaxOgt = false;     // RowMax written as cmpf ogt + select (init -inf form)
+  bool transA = false;        // Matmul: A is stored [K,M]
+  bool transB = false;        // Matmul: B is stored [N,K]
   std::vector<int> perm;      // Transpose: output dim i = input dim perm[i]
   std::string why;            // reason when Unknown
 };

@@ -514,28 +514,61 @@ private:
       if (A.type.elt != Bv.type.elt) die(where + "matmul operands of different element types");
       if (outT.elt != "f32") die(where + "matmul accumulating in " + outT.elt + " is not mapped to a GEMM (f32 accumulate only)");
       Value &C0 = get(fr, op.outs[0], op);
-      const int64_t M = A.type.shape[0], K = A.type.shape[1], N = Bv.type.shape[1];
-      if (Bv.type.shape[0] != K || outT.shape[0] != M || outT.shape[1] != N) die(where + "matmul shape mismatch");
-      // epilogue fusion: the single user is relu, or sigmoid(x) followed by mul(sigmoid, x)
-      uint32_t epi = IMEX_EPI_NONE;
+      // stored shapes: A [M,K] ([K,M] when transposed), B [K,N] ([N,K] when transposed)
+      const int64_t M = A.type.shape[c.transA ? 1 : 0], K = A.type.shape[c.transA ? 0 : 1];
+      const int64_t N = Bv.type.shape[c.transB ? 0 : 1];
+      if (Bv.type.shape[c.transB ? 1 : 0] != K || outT.shape[0] != M || outT.shape[1] != N)
+        die(where + "matmul shape mismatch");
+      // fusions behind the matmul, in the order the IR applies them:
+      //   + bias   add(result, broadcast_row(v[N]))
+      //   epilogue relu, or sigmoid(x) followed by mul(sigmoid, x)
+      //   truncf   the f32 result rounded once to bf16 / f16
       std::string finalRes = res;
-      auto us = usersOf(res, b);
+      const Value *biasV = nullptr;
+      auto us = usersOf(finalRes, b);
+      if (us.size() == 1 && classOf(us[0], fr).kind == Kind::Add) {
+        const std::string &other = us[0]->ins[0] == finalRes ? us[0]->ins[1] : us[0]->ins[0];
+        const Op *bp = producer(other, defs);
+        if (classOf(bp, fr).kind == Kind::BroadcastRow) {
+          const Value &v = get(fr, bp->ins[0], *bp);
+          if (v.type.elt == "f32" && v.type.shape.size() == 1 && v.type.shape[0] == N) {
+            biasV = &v;
+            absorbed.insert(us[0]);
+            finalRes = us[0]->results[0];
+            us = usersOf(finalRes, b);
+          }
+        }
+      }
+      uint32_t epi = IMEX_EPI_NONE;
       if (us.size() == 1 && classOf(us[0], fr).kind == Kind::Relu) {
         epi = IMEX_EPI_RELU;
         absorbed.insert(us[0]);
         finalRes = us[0]->results[0];
+        us = usersOf(finalRes, b);
       } else if (us.size() == 2 && classOf(us[0], fr).kind == Kind::Sigmoid &&
                  classOf(us[1], fr).kind == Kind::Mul && us[1]->ins[0] == us[0]->results[0] &&
-                 us[1]->ins[1] == res) {
+                 us[1]->ins[1] == finalRes) {
         epi = IMEX_EPI_SILU;
         absorbed.insert(us[0]);
         absorbed.insert(us[1]);
         finalRes = us[1]->results[0];
+        us = usersOf(finalRes, b);
       }
-      Value out = makeTensor(stream, outT);
-      ImexKernelDesc d = desc(IMEX_OP_GEMM, dtypeCode(inElt), IMEX_F32);
-      d.epilogue = epi;
+      Type finalT = outT;
+      if (us.size() == 1 && classOf(us[0], fr).kind == Kind::TruncF) {
+        finalT = us[0]->resultTypes.empty() ? us[0]->outsTypes[0] : us[0]->resultTypes[0];
+        absorbed.insert(us[0]);
+        finalRes = us[0]->results[0];
+      }
       const bool zeroInit = C0.isFill && C0.fillValue == 0.0;
+      if (!zeroInit && finalT.elt != "f32")
+        die(where + "matmul with a non-zero f32 initial value and a 16-bit result is not mapped");
+      Value out = makeTensor(stream, finalT);
+      ImexKernelDesc d = desc(IMEX_OP_GEMM, dtypeCode(inElt), dtypeCode(finalT.elt));
+      d.epilogue = epi;
+      if (c.transA) d.flags |= IMEX_FLAG_TRANS_A;
+      if (c.transB) d.flags |= IMEX_FLAG_TRANS_B;
+      if (biasV) d.flags |= IMEX_FLAG_BIAS;
       if (!zeroInit) {  // C is also an input: start from a copy of it
         d.flags |= IMEX_FLAG_ACCUMULATE;
         trace("gpuMemCopy(device -> device, " + std::to_string(out.buf->bytes) + " bytes)  // C init");
@@ -544,12 +577,33 @@ private:
       d.dims[0] = M;
       d.dims[1] = N;
       d.dims[2] = K;
-      launch(stream, d, {A.buf->ptr, Bv.buf->ptr, out.buf->ptr},
-             std::string("gemm ") + inElt + "->f32" + (epi == IMEX_EPI_RELU ? " +relu" : epi == IMEX_EPI_SILU ? " +silu" : ""));
+      std::vector<void *> ptrs = {A.buf->ptr, Bv.buf->ptr, out.buf->ptr};
+      if (biasV) ptrs.push_back(biasV->buf->ptr);
+      launch(stream, d, ptrs,
+             std::string("gemm ") + inElt + "->" + finalT.elt + (c.transA ? " A^T" : "") + (c.transB ? " B^T" : "") +
+                 (biasV ? " +bias" : "") + (epi == IMEX_EPI_RELU ? " +relu" : epi == IMEX_EPI_SILU ? " +silu" : ""));
       fr.vals[finalRes] = out;
       if (finalRes != res) fr.vals[res] = out;
       break;
     }
+    case Kind::BroadcastRow: {
+      // only as the bias of a matmul: nothing is materialised, the GEMM epilogue adds v[j]
+      auto us = usersOf(res, b);
+      bool feedsBias = !us.empty();
+      for (auto *u : us) {
+        bool okUser = classOf(u, fr).kind == Kind::Add;
+        if (okUser) {
+          const std::string &other = u->ins[0] == res ? u->ins[1] : u->ins[0];
+          okUser = classOf(producer(other, defs), fr).kind == Kind::Matmul;
+        }
+        feedsBias = feedsBias && okUser;
+      }
+      if (!feedsBias) die(where + "row broadcast that is not the bias of a matmul; no CPU fallback");
+      fr.vals[res] = get(fr, op.ins[0], op);
+      break;
+    }
+    case Kind::Add:
+      die(where + "elementwise add that is not the bias of a matmul; no CPU fallback");
     case Kind::ExtF: {
       // as the producer of matmul operands only, nothing is materialised: the GEMM reads
       // the 16-bit data itself

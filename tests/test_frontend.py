@@ -62,6 +62,17 @@ def test_fusions():
     assert "flags=0" in kernels(out)[0]  # -FLT_MAX / maximumf form
 
 
+def test_transposed_operands_bias_and_16bit_result_fuse_into_one_launch():
+    rc, out, err = plan(os.path.join(MLIR, "matmul_f16_transposed_bias.mlir"))
+    assert rc == 0, err
+    ks = kernels(out)
+    # matmul(B stored [N,K]) + broadcast bias + add + relu + truncf: flags = BIAS | TRANS_B
+    assert ks[0] == "gemm f16->f16 B^T +bias +relu dims=[8,16,64] epilogue=1 flags=18"
+    assert ks[2] == "gemm f16->f32 A^T dims=[8,16,64] epilogue=0 flags=8"
+    assert len(ks) == 3
+    assert out.count("gpuLaunchKernel(4 pointer params)") == 2  # A, B, C, bias
+
+
 def test_ir_outside_the_hot_path_is_refused():
     rc, out, err = plan(os.path.join(MLIR, "unrecognised.mlir"))
     assert rc == 1
@@ -114,7 +125,7 @@ needs_reference = pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="no re
     ("test/PlaidML/OpTest.GEMM_FLOAT32.mlir", ["gemm"] * 100),
     ("test/PlaidML/CppEdsl.Dot.mlir", ["gemm"]),
     ("test/PlaidML/CppEdsl.BigDot.mlir", ["gemm"]),
-    ("test/PlaidML/CppEdsl.DotF16_AccF32.mlir", ["gemm", "convert", "convert"]),
+    ("test/PlaidML/CppEdsl.DotF16_AccF32.mlir", ["gemm", "convert"]),  # extf, matmul, truncf: one launch,
     ("test/PlaidML/OpTest.Softmax.mlir", ["softmax"]),
     ("test/PlaidML/OpTest.Sum.mlir", ["reduce_all"]),
     ("test/PlaidML/OpTest.Transpose.mlir", ["transpose2d"]),
@@ -171,7 +182,7 @@ def test_reference_benchmark_templates_are_recognised(tmp_path, name, subst, exp
 # ---------------------------------------------------------------- on the GPU
 @pytest.mark.gpu
 @pytest.mark.parametrize("fixture", ["matmul_f32.mlir", "matmul_bf16_relu_silu.mlir",
-                                     "softmax_silu_transpose.mlir"])
+                                     "softmax_silu_transpose.mlir", "matmul_f16_transposed_bias.mlir"])
 def test_fixture_runs_and_matches_its_check_lines(fixture):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "mlir-extensions_b200", "imex_runner.py"),
                         "-i", os.path.join(MLIR, fixture), "-f", os.path.join(MLIR, "linalg-to-gpu.pp"),
