@@ -52,6 +52,19 @@ extern "C" {
  *   TRANSPOSE3D     X[d0,d1,d2], Y[permuted]             dims = {d0,d1,d2,p0,p1,p2}
  *   ELTWISE         X[n], Y[n] with `epilogue` applied   dims = {n}
  *                   (in_dtype != out_dtype: arith.extf / arith.truncf, no epilogue)
+ *   EXPR            X0 .. X(k-1), Y: a chain of elementwise generics fused into one pass
+ *                   (benchmarks/kLoopFusion/kLoopFusion.mlir.in:4-30).  dims = {rows, cols,
+ *                   p0, p1, p2, p3}: the four p words hold up to 32 bytes of postfix
+ *                   program (ImexExprCode, little endian, first byte = lowest byte of p0,
+ *                   IMEX_X_END-terminated when shorter).  Inputs are full [rows,cols]
+ *                   tensors, row vectors [cols] or column vectors [rows], as the push
+ *                   opcode says; all of in_dtype.  Every operation rounds to in_dtype
+ *                   (f16/bf16 arithmetic is extend - operate in f32 - truncate, per
+ *                   operation, as the reference's CPU lowering of 16-bit float ops does).
+ *                   IMEX_FLAG_REDUCE_LEADING: Y[cols] = (Y when ACCUMULATE else 0) +
+ *                   sum over rows, ascending, of the expression (the elementwise chain
+ *                   feeding a column reduce, benchmarks/kInputFusion/kInputFusion.mlir.in:
+ *                   6-41); otherwise Y[rows,cols] of out_dtype.
  *   FILL_UNIFORM    Y[n]  dims = {n, seed, first}; fparams = {lo, hi}
  *   FILL_NORMAL     Y[n]  dims = {n, seed, first}; fparams = {mean, stddev}
  */
@@ -65,8 +78,40 @@ enum ImexOp {
   IMEX_OP_TRANSPOSE3D = 7,
   IMEX_OP_ELTWISE = 8,
   IMEX_OP_FILL_UNIFORM = 9,
-  IMEX_OP_FILL_NORMAL = 10
+  IMEX_OP_FILL_NORMAL = 10,
+  IMEX_OP_EXPR = 11
 };
+
+/* Postfix code of IMEX_OP_EXPR.  Pushes take the element of input k at the current
+ * (row, col); unary operations replace the top of the stack, binary ones pop b then a
+ * and push a (op) b.  The stack holds at most IMEX_EXPR_MAX_STACK values. */
+enum ImexExprCode {
+  IMEX_X_END = 0,
+  IMEX_X_IN = 1,    /* +k, k = 0..3: X_k[row, col]                    */
+  IMEX_X_ROWV = 5,  /* +k: X_k[col]   (one value per column)          */
+  IMEX_X_COLV = 9,  /* +k: X_k[row]   (one value per row)             */
+  IMEX_X_C0 = 13,   /* fparams[0] */
+  IMEX_X_C1 = 14,   /* fparams[1] */
+  IMEX_X_ZERO = 15,
+  IMEX_X_ONE = 16,
+  IMEX_X_NEG = 32,
+  IMEX_X_ABS = 33,
+  IMEX_X_LOG = 34,
+  IMEX_X_EXP = 35,
+  IMEX_X_SQRT = 36,
+  IMEX_X_RSQRT = 37,
+  IMEX_X_TANH = 38,
+  IMEX_X_RELU = 39, /* select(cmpf ugt x, 0 ; x, 0) */
+  IMEX_X_ADD = 64,
+  IMEX_X_SUB = 65,
+  IMEX_X_MUL = 66,
+  IMEX_X_DIV = 67,
+  IMEX_X_MAX = 68,  /* arith.maximumf: NaN if either is NaN */
+  IMEX_X_MIN = 69
+};
+#define IMEX_EXPR_MAX_CODE 32
+#define IMEX_EXPR_MAX_INPUTS 4
+#define IMEX_EXPR_MAX_STACK 8
 
 enum ImexDType { IMEX_F32 = 1, IMEX_BF16 = 2, IMEX_F16 = 3, IMEX_I32 = 4 };
 
@@ -79,7 +124,8 @@ enum ImexFlags {
   IMEX_FLAG_BIAS = 1u << 1,       /* GEMM: 4th pointer is bias[N] (f32)   */
   IMEX_FLAG_SOFTMAX_NEG_INF = 1u << 2, /* PlaidML form: max starts at -inf, cmpf ogt */
   IMEX_FLAG_TRANS_A = 1u << 3,    /* GEMM: A stored [K,M]                 */
-  IMEX_FLAG_TRANS_B = 1u << 4     /* GEMM: B stored [N,K]                 */
+  IMEX_FLAG_TRANS_B = 1u << 4,    /* GEMM: B stored [N,K]                 */
+  IMEX_FLAG_REDUCE_LEADING = 1u << 5 /* EXPR: sum the expression over the rows */
 };
 
 typedef struct ImexBlobHeader {

@@ -12,9 +12,11 @@ NAME_MAX = 64
 
 OP_GEMM, OP_SOFTMAX, OP_REDUCE_ROWS, OP_REDUCE_LEADING, OP_REDUCE_ALL = 1, 2, 3, 4, 5
 OP_TRANSPOSE2D, OP_TRANSPOSE3D, OP_ELTWISE, OP_FILL_UNIFORM, OP_FILL_NORMAL = 6, 7, 8, 9, 10
+OP_EXPR = 11
 F32, BF16, F16, I32 = 1, 2, 3, 4
 EPI_NONE, EPI_RELU, EPI_SILU = 0, 1, 2
 FLAG_ACCUMULATE, FLAG_BIAS, FLAG_SOFTMAX_NEG_INF, FLAG_TRANS_A, FLAG_TRANS_B = 1, 2, 4, 8, 16
+FLAG_REDUCE_LEADING = 32
 
 DTYPE_BYTES = {F32: 4, I32: 4, BF16: 2, F16: 2}
 _DESC = struct.Struct("<64s6I6q2f")  # ImexKernelDesc, 144 bytes
@@ -68,6 +70,46 @@ def gemm(name, M, N, K, in_dtype=BF16, epilogue=EPI_NONE, accumulate=False, bias
              | (FLAG_TRANS_A if trans_a else 0) | (FLAG_TRANS_B if trans_b else 0))
     return KernelDesc(name, OP_GEMM, in_dtype, out_dtype, epilogue, flags, (M, N, K, lda, ldb, ldc),
                       sm_margin=sm_margin)
+
+
+# postfix code of OP_EXPR (ImexExprCode)
+X_END, X_IN, X_ROWV, X_COLV, X_C0, X_C1, X_ZERO, X_ONE = 0, 1, 5, 9, 13, 14, 15, 16
+X_UNARY = {"neg": 32, "abs": 33, "log": 34, "exp": 35, "sqrt": 36, "rsqrt": 37, "tanh": 38, "relu": 39}
+X_BINARY = {"add": 64, "sub": 65, "mul": 66, "div": 67, "max": 68, "min": 69}
+EXPR_MAX_CODE = 32
+
+
+def assemble_expr(text):
+    """Postfix text -> code bytes.  Tokens: in0..in3 (full tensors), row0..row3 (row
+    vectors [cols]), col0..col3 (column vectors [rows]), c0, c1 (fparams), zero, one,
+    and the operation names of X_UNARY / X_BINARY.  "in0 log in1 abs add in0 sub" is
+    (log(x0) + |x1|) - x0."""
+    code = []
+    for tok in text.split():
+        if tok[:-1] in ("in", "row", "col") and tok[-1].isdigit() and int(tok[-1]) < 4:
+            code.append({"in": X_IN, "row": X_ROWV, "col": X_COLV}[tok[:-1]] + int(tok[-1]))
+        elif tok in ("c0", "c1", "zero", "one"):
+            code.append({"c0": X_C0, "c1": X_C1, "zero": X_ZERO, "one": X_ONE}[tok])
+        elif tok in X_UNARY:
+            code.append(X_UNARY[tok])
+        elif tok in X_BINARY:
+            code.append(X_BINARY[tok])
+        else:
+            raise ValueError("unknown token %r in expression" % tok)
+    if not 0 < len(code) <= EXPR_MAX_CODE:
+        raise ValueError("expression programs hold 1..%d operations" % EXPR_MAX_CODE)
+    return bytes(code)
+
+
+def expr(name, rows, cols, program, dtype=F32, out_dtype=None, reduce_leading=False,
+         accumulate=False, consts=(0.0, 0.0)):
+    """Fused elementwise chain: pointers = the inputs in order, then Y.  `program` is
+    postfix text (assemble_expr) or code bytes."""
+    code = assemble_expr(program) if isinstance(program, str) else bytes(program)
+    words = struct.unpack("<4q", code.ljust(EXPR_MAX_CODE, b"\0"))
+    flags = (FLAG_REDUCE_LEADING if reduce_leading else 0) | (FLAG_ACCUMULATE if accumulate else 0)
+    return KernelDesc(name, OP_EXPR, dtype, dtype if out_dtype is None else out_dtype, 0, flags,
+                      (rows, cols) + words, fparams=consts)
 
 
 def softmax(name, rows, cols, neg_inf_init=False):

@@ -32,6 +32,7 @@ RUNTIME_SOURCES = [
     "kernels/reduce_all_static.cu",
     "kernels/transpose.cu",
     "kernels/eltwise_fill.cu",
+    "kernels/eltwise_expr.cu",
     "kernels/wait_selftest.cu",
     "runtime/cuda_runtime_wrappers.cu",
     "runtime/stats.cpp",

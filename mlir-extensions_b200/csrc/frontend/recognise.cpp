@@ -1,7 +1,11 @@
 // Classification of linalg ops; see recognise.h.
 #include "recognise.h"
 
+#include "../../../include/imex_b200_blob.h"
+
 #include <algorithm>
+#include <cctype>
+#include <cstdlib>
 #include <sstream>
 
 namespace imex {
@@ -26,6 +30,7 @@ const char *kindName(Kind k) {
   case Kind::ReduceAll: return "reduce_all";
   case Kind::ExtF: return "extf";
   case Kind::TruncF: return "truncf";
+  case Kind::Elementwise: return "elementwise";
   case Kind::Fill: return "fill";
   }
   return "?";
@@ -270,8 +275,130 @@ Classified classify(const Op &op, const ConstantTable &constants) {
     if (y == "subf(in0,in1)") { c.kind = Kind::SubRowBcast; return c; }
     if (y == "divf(in0,in1)") { c.kind = Kind::DivRowBcast; return c; }
   }
+  ElementwiseInfo info;
+  if (classifyElementwise(op, constants, info)) {
+    c.kind = Kind::Elementwise;
+    return c;
+  }
   c.why = "elementwise body " + y + " matches no hot-path op";
   return c;
+}
+
+namespace {
+struct ExprParser {
+  const std::string &s;
+  size_t pos = 0;
+  explicit ExprParser(const std::string &text) : s(text) {}
+
+  // the text of one balanced sub-expression starting at pos (without consuming it)
+  std::string peekTerm() const {
+    size_t i = pos;
+    int depth = 0;
+    for (; i < s.size(); ++i) {
+      if (s[i] == '(') ++depth;
+      else if (s[i] == ')') { if (depth == 0) break; --depth; }
+      else if (s[i] == ',' && depth == 0) break;
+    }
+    return s.substr(pos, i - pos);
+  }
+  bool eat(char c) {
+    if (pos < s.size() && s[pos] == c) { ++pos; return true; }
+    return false;
+  }
+  std::shared_ptr<ExprTree> term() {
+    size_t i = pos;
+    while (i < s.size() && (std::isalnum(static_cast<unsigned char>(s[i])) || s[i] == '_')) ++i;
+    const std::string name = s.substr(pos, i - pos);
+    auto node = std::make_shared<ExprTree>();
+    if (name.size() > 2 && name.compare(0, 2, "in") == 0 && std::isdigit(static_cast<unsigned char>(name[2])) &&
+        (i == s.size() || s[i] != '(')) {
+      node->kind = ExprTree::Input;
+      node->index = std::atoi(name.c_str() + 2);
+      pos = i;
+      return node;
+    }
+    if (i >= s.size() || s[i] != '(') return nullptr;
+    pos = i + 1;
+    if (name == "c") {
+      size_t j = s.find(')', pos);
+      if (j == std::string::npos) return nullptr;
+      node->kind = ExprTree::Const;
+      node->value = std::strtod(s.substr(pos, j - pos).c_str(), nullptr);
+      pos = j + 1;
+      return node;
+    }
+    if (name == "select") {
+      // only relu: select(cmpf(ugt,X,c(0)),X,c(0))
+      if (s.compare(pos, 9, "cmpf(ugt,") != 0) return nullptr;
+      pos += 9;
+      const std::string x = peekTerm();
+      auto xa = term();
+      if (!xa || !eat(',')) return nullptr;
+      auto zero = term();
+      if (!zero || zero->kind != ExprTree::Const || zero->value != 0 || !eat(')') || !eat(',')) return nullptr;
+      if (peekTerm() != x) return nullptr;
+      auto xb = term();
+      if (!xb || !eat(',')) return nullptr;
+      auto zero2 = term();
+      if (!zero2 || zero2->kind != ExprTree::Const || zero2->value != 0 || !eat(')')) return nullptr;
+      node->kind = ExprTree::Unary;
+      node->opcode = IMEX_X_RELU;
+      node->a = xa;
+      return node;
+    }
+    static const std::map<std::string, int> unary = {
+        {"negf", IMEX_X_NEG}, {"absf", IMEX_X_ABS}, {"log", IMEX_X_LOG}, {"exp", IMEX_X_EXP},
+        {"sqrt", IMEX_X_SQRT}, {"rsqrt", IMEX_X_RSQRT}, {"tanh", IMEX_X_TANH}};
+    static const std::map<std::string, int> binary = {
+        {"addf", IMEX_X_ADD}, {"subf", IMEX_X_SUB}, {"mulf", IMEX_X_MUL}, {"divf", IMEX_X_DIV},
+        {"maximumf", IMEX_X_MAX}, {"minimumf", IMEX_X_MIN}};
+    auto u = unary.find(name);
+    auto bn = binary.find(name);
+    if (u == unary.end() && bn == binary.end()) return nullptr;
+    node->a = term();
+    if (!node->a) return nullptr;
+    if (u != unary.end()) {
+      node->kind = ExprTree::Unary;
+      node->opcode = u->second;
+    } else {
+      if (!eat(',')) return nullptr;
+      node->b = term();
+      if (!node->b) return nullptr;
+      node->kind = ExprTree::Binary;
+      node->opcode = bn->second;
+    }
+    if (!eat(')')) return nullptr;
+    return node;
+  }
+};
+} // namespace
+
+std::shared_ptr<ExprTree> parseElementwiseExpr(const std::string &expr) {
+  ExprParser p(expr);
+  auto t = p.term();
+  return (t && p.pos == expr.size()) ? t : nullptr;
+}
+
+bool classifyElementwise(const Op &op, const ConstantTable &constants, ElementwiseInfo &info) {
+  if (op.name != "linalg.generic" || !op.body || op.outs.size() != 1 || op.ins.empty()) return false;
+  if (op.maps.size() != op.ins.size() + 1 || !allParallel(op)) return false;
+  const AffineMap &outMap = op.maps[op.ins.size()];
+  if (!outMap.isIdentity()) return false;
+  info.inputMode.clear();
+  for (size_t i = 0; i < op.ins.size(); ++i) {
+    const AffineMap &m = op.maps[i];
+    if (m.isIdentity()) info.inputMode.push_back(0);
+    else if (m.numDims == 2 && mapIs(m, {1})) info.inputMode.push_back(1);
+    else if (m.numDims == 2 && (mapIs(m, {0}) || mapIs(m, {0, -1}))) info.inputMode.push_back(2);
+    else return false;
+  }
+  std::string why;
+  std::vector<std::string> ys = bodyExpressions(op, constants, why);
+  if (!why.empty() || ys.size() != 1) return false;
+  if (ys[0].find("out") != std::string::npos || ys[0].find("index") != std::string::npos) return false;
+  info.expr = ys[0];
+  info.tree = parseElementwiseExpr(info.expr);
+  return info.tree != nullptr;
 }
 
 } // namespace fe

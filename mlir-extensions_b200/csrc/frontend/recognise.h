@@ -14,6 +14,7 @@
 #include "mlir_text.h"
 
 #include <map>
+#include <memory>
 #include <set>
 #include <string>
 #include <vector>
@@ -40,6 +41,7 @@ enum class Kind {
   ReduceAll,     // sum of everything
   ExtF,          // 16-bit -> f32
   TruncF,        // f32 -> 16-bit
+  Elementwise,   // any other supported elementwise body (see classifyElementwise)
   Fill
 };
 
@@ -55,10 +57,31 @@ struct Classified {
   std::string why;            // reason when Unknown
 };
 
+// Any all-parallel generic whose body is a tree of the operations the fused
+// elementwise kernel knows (IMEX_OP_EXPR) and whose operands are read at the loop
+// point itself, as a row vector ((d0,d1)->(d1)) or as a column vector
+// ((d0,d1)->(d0) / (d0,0)).  Chains of these fuse into one launch
+// (benchmarks/kLoopFusion/kLoopFusion.mlir.in:4-30).
+struct ExprTree {
+  enum { Input, Const, Unary, Binary } kind = Input;
+  int index = 0;     // Input: which operand
+  double value = 0;  // Const
+  int opcode = 0;    // Unary / Binary: ImexExprCode
+  std::shared_ptr<ExprTree> a, b;
+};
+struct ElementwiseInfo {
+  std::string expr;            // canonical body expression over in0.. and c(value)
+  std::vector<int> inputMode;  // per input: 0 = full tensor, 1 = row vector, 2 = column vector
+  std::shared_ptr<ExprTree> tree;
+};
+// Tree of a canonical body expression; null when it uses anything the fused kernel lacks.
+std::shared_ptr<ExprTree> parseElementwiseExpr(const std::string &expr);
+
 // Scalar constants visible to linalg bodies: SSA name -> value.
 using ConstantTable = std::map<std::string, double>;
 
 Classified classify(const Op &op, const ConstantTable &constants);
+bool classifyElementwise(const Op &op, const ConstantTable &constants, ElementwiseInfo &info);
 
 } // namespace fe
 } // namespace imex

@@ -117,11 +117,23 @@ struct Buffer {  // a device allocation, freed with the last reference
   }
 };
 
+// A fused elementwise chain that has not been launched yet: leaves are device buffers.
+struct XNode {
+  enum { Leaf, Const, Unary, Binary } kind = Leaf;
+  int opcode = 0;               // ImexExprCode of a Unary / Binary node
+  double value = 0;             // Const
+  std::shared_ptr<Buffer> buf;  // Leaf
+  int mode = 0;                 // Leaf: 0 full tensor, 1 row vector, 2 column vector
+  std::shared_ptr<XNode> a, b;
+};
+using XNodeP = std::shared_ptr<XNode>;
+
 struct Value {
   enum { Empty, Scalar, Tensor } kind = Empty;
   Type type;
   double scalar = 0;
   std::shared_ptr<Buffer> buf;
+  XNodeP lazy;  // set instead of buf while the chain producing this tensor is still open
   // what is known about the contents without reading them back
   bool isFill = false;
   double fillValue = 0;
@@ -153,6 +165,7 @@ private:
   const Module &mod;
   std::map<const Op *, SoftmaxPlan> pendingSoftmax;  // keyed by the chain's final divide
   int kernelCounter = 0;
+  void *curStream = nullptr;  // stream of the function being interpreted
   std::vector<std::unique_ptr<std::vector<char>>> blobs;  // modules are cached by blob address
 
   // ---- device helpers ---------------------------------------------------
@@ -265,7 +278,10 @@ private:
     std::map<std::string, const Op *> defs;
     std::map<std::string, int> uses;
     index(f.body, defs, uses);
+    void *outerStream = curStream;
+    curStream = stream;
     std::vector<Value> results = runBlock(f.body, fr, stream, absorbed, defs, uses);
+    curStream = outerStream;
     fr.vals.clear();  // frees this function's buffers (results hold their own references)
     if (!g_plan) {
       // results must outlive the stream handle they were allocated with
@@ -287,10 +303,197 @@ private:
     }
   }
 
+  // The value with its contents in device memory (an open elementwise chain is launched).
   Value &get(Frame &fr, const std::string &name, const Op &at) {
+    Value &v = peek(fr, name, at);
+    if (v.lazy) materialise(v);
+    return v;
+  }
+  // The value as it is: possibly an open elementwise chain (v.lazy) without a buffer.
+  Value &peek(Frame &fr, const std::string &name, const Op &at) {
     auto it = fr.vals.find(name);
     if (it == fr.vals.end()) die("line " + std::to_string(at.line) + ": use of undefined value " + name);
     return it->second;
+  }
+
+  // ---- fused elementwise chains ---------------------------------------------------
+  struct ExprProgram {
+    std::vector<unsigned char> code;
+    std::vector<std::shared_ptr<Buffer>> inputs;
+    float consts[2] = {0, 0};
+    int nconsts = 0;
+  };
+  // Postfix code of a tree; false when it needs more than the kernel has (4 inputs, two
+  // free constants, 32 operations, 8 stack slots).
+  bool emit(const XNodeP &n, ExprProgram &p, int &sp, int &maxsp) {
+    switch (n->kind) {
+    case XNode::Leaf: {
+      size_t k = 0;
+      for (; k < p.inputs.size(); ++k)
+        if (p.inputs[k] == n->buf) break;
+      if (k == p.inputs.size()) {
+        if (k == IMEX_EXPR_MAX_INPUTS) return false;
+        p.inputs.push_back(n->buf);
+      }
+      p.code.push_back(static_cast<unsigned char>((n->mode == 0 ? IMEX_X_IN : n->mode == 1 ? IMEX_X_ROWV : IMEX_X_COLV) + k));
+      maxsp = std::max(maxsp, ++sp);
+      break;
+    }
+    case XNode::Const: {
+      const float f = static_cast<float>(n->value);
+      if (f == 0.0f && !std::signbit(f)) p.code.push_back(IMEX_X_ZERO);
+      else if (f == 1.0f) p.code.push_back(IMEX_X_ONE);
+      else {
+        int k = 0;
+        for (; k < p.nconsts; ++k)
+          if (std::memcmp(&p.consts[k], &f, 4) == 0) break;
+        if (k == p.nconsts) {
+          if (k == 2) return false;
+          p.consts[p.nconsts++] = f;
+        }
+        p.code.push_back(static_cast<unsigned char>(IMEX_X_C0 + k));
+      }
+      maxsp = std::max(maxsp, ++sp);
+      break;
+    }
+    case XNode::Unary:
+      if (!emit(n->a, p, sp, maxsp)) return false;
+      p.code.push_back(static_cast<unsigned char>(n->opcode));
+      break;
+    case XNode::Binary:
+      if (!emit(n->a, p, sp, maxsp) || !emit(n->b, p, sp, maxsp)) return false;
+      p.code.push_back(static_cast<unsigned char>(n->opcode));
+      --sp;
+      break;
+    }
+    return p.code.size() <= IMEX_EXPR_MAX_CODE && maxsp <= IMEX_EXPR_MAX_STACK;
+  }
+  bool compile(const XNodeP &tree, ExprProgram &p) {
+    int sp = 0, maxsp = 0;
+    return emit(tree, p, sp, maxsp);
+  }
+  static void shape2d(const Type &t, int64_t &rows, int64_t &cols) {
+    cols = t.shape.empty() ? 1 : t.shape.back();
+    rows = cols ? t.count() / cols : 0;
+  }
+  ImexKernelDesc exprDesc(const ExprProgram &p, const Type &in, uint32_t outDtype, int64_t rows, int64_t cols) {
+    ImexKernelDesc d = desc(IMEX_OP_EXPR, dtypeCode(in.elt), outDtype);
+    d.dims[0] = rows;
+    d.dims[1] = cols;
+    unsigned char code[IMEX_EXPR_MAX_CODE] = {0};
+    std::memcpy(code, p.code.data(), p.code.size());
+    std::memcpy(&d.dims[2], code, sizeof code);
+    d.fparams[0] = p.consts[0];
+    d.fparams[1] = p.consts[1];
+    return d;
+  }
+  std::string exprText(const ExprProgram &p) {
+    std::ostringstream os;
+    os << "expr[" << p.code.size() << " ops, " << p.inputs.size() << " inputs]";
+    return os.str();
+  }
+  // Launches the open chain of `v` into a fresh buffer.
+  void materialise(Value &v) {
+    ExprProgram p;
+    if (!compile(v.lazy, p)) die("internal: an elementwise chain outgrew the fused kernel");
+    Value out = makeTensor(curStream, v.type);
+    int64_t rows, cols;
+    shape2d(v.type, rows, cols);
+    std::vector<void *> ptrs;
+    for (auto &b : p.inputs) ptrs.push_back(b->ptr);
+    ptrs.push_back(out.buf->ptr);
+    launch(curStream, exprDesc(p, v.type, dtypeCode(v.type.elt), rows, cols), ptrs, exprText(p) + " " + v.type.elt);
+    v.buf = out.buf;
+    v.lazy.reset();
+  }
+  XNodeP substitute(const std::shared_ptr<ExprTree> &t, const std::vector<XNodeP> &operands) {
+    auto n = std::make_shared<XNode>();
+    switch (t->kind) {
+    case ExprTree::Input:
+      if (t->index < 0 || static_cast<size_t>(t->index) >= operands.size()) die("internal: operand index");
+      return operands[t->index];
+    case ExprTree::Const:
+      n->kind = XNode::Const;
+      n->value = t->value;
+      return n;
+    case ExprTree::Unary:
+      n->kind = XNode::Unary;
+      n->opcode = t->opcode;
+      n->a = substitute(t->a, operands);
+      return n;
+    case ExprTree::Binary:
+      n->kind = XNode::Binary;
+      n->opcode = t->opcode;
+      n->a = substitute(t->a, operands);
+      n->b = substitute(t->b, operands);
+      return n;
+    }
+    return n;
+  }
+  static XNodeP leaf(const Value &v, int mode) {
+    auto n = std::make_shared<XNode>();
+    n->kind = XNode::Leaf;
+    n->buf = v.buf;
+    n->mode = mode;
+    return n;
+  }
+  // An elementwise generic outside the named chains: joins the chain of its operands; is
+  // launched at once unless every user can take it over (another elementwise generic reading
+  // it at the loop point, or the column reduce of kInputFusion.mlir.in:29-39).
+  void elementwiseOp(const Op &op, const Block &b, Frame &fr, const std::string &where) {
+    ElementwiseInfo info;
+    if (!classifyElementwise(op, fr.constants, info))
+      die(where + op.name + " is not a recognised hot-path op; no CPU fallback");
+    const Type outT = op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0];
+    if (outT.elt != "f32" && outT.elt != "f16" && outT.elt != "bf16") die(where + "elementwise ops on " + outT.elt);
+    bool broadcast = false;
+    for (int m : info.inputMode) broadcast = broadcast || m != 0;
+    if (broadcast && outT.shape.size() != 2) die(where + "broadcasting elementwise ops are rank 2 only");
+    auto build = [&](bool inlineLazy) {
+      std::vector<XNodeP> operands;
+      for (size_t i = 0; i < op.ins.size(); ++i) {
+        Value &v = peek(fr, op.ins[i], op);
+        if (v.kind != Value::Tensor) die(where + "elementwise operand that is not a tensor");
+        if (v.type.elt != outT.elt) die(where + "elementwise op mixing " + v.type.elt + " and " + outT.elt);
+        if (v.lazy && inlineLazy && info.inputMode[i] == 0 && v.type.count() == outT.count())
+          operands.push_back(v.lazy);
+        else
+          operands.push_back(leaf(get(fr, op.ins[i], op), info.inputMode[i]));
+      }
+      return substitute(info.tree, operands);
+    };
+    XNodeP tree = build(true);
+    ExprProgram probe;
+    if (!compile(tree, probe)) {
+      tree = build(false);  // the operands' chains are launched on their own
+      ExprProgram alone;
+      if (!compile(tree, alone)) die(where + "elementwise body too large for one fused kernel");
+    }
+    Value out;
+    out.kind = Value::Tensor;
+    out.type = outT;
+    out.lazy = tree;
+    const std::string res = op.results.empty() ? "" : op.results[0];
+    bool defer = !res.empty();
+    auto us = usersOf(res, b);
+    defer = defer && !us.empty();
+    for (auto *u : us) {
+      bool ok = false;
+      ElementwiseInfo ui;
+      const Classified uc = classOf(u, fr);
+      if (uc.kind == Kind::Elementwise || uc.kind == Kind::Add || uc.kind == Kind::Mul || uc.kind == Kind::Exp) {
+        ok = classifyElementwise(*u, fr.constants, ui);
+        for (size_t i = 0; ok && i < u->ins.size(); ++i)
+          if (u->ins[i] == res) ok = ui.inputMode[i] == 0;
+        for (auto &o : u->outs) ok = ok && o != res;
+      } else if (uc.kind == Kind::ReduceLeading) {
+        ok = u->ins.size() == 1 && u->ins[0] == res && outT.shape.size() == 2;
+      }
+      defer = defer && ok;
+    }
+    if (!defer) materialise(out);
+    else trace("deferred: " + info.expr + "  // joins the next elementwise kernel");
+    fr.vals[res] = out;
   }
 
   std::vector<Value> runBlock(const Block &b, Frame &fr, void *stream, std::set<const Op *> &absorbed,
@@ -603,7 +806,9 @@ private:
       break;
     }
     case Kind::Add:
-      die(where + "elementwise add that is not the bias of a matmul; no CPU fallback");
+    case Kind::Elementwise:
+      elementwiseOp(op, b, fr, where);
+      break;
     case Kind::ExtF: {
       // as the producer of matmul operands only, nothing is materialised: the GEMM reads
       // the 16-bit data itself
@@ -705,6 +910,32 @@ private:
     case Kind::RowSum:
     case Kind::ReduceLeading:
     case Kind::ReduceAll: {
+      Value &maybeOpen = peek(fr, op.ins[0], op);
+      if (c.kind == Kind::ReduceLeading && maybeOpen.type.shape.size() == 2 &&
+          (maybeOpen.lazy || maybeOpen.type.elt != "f32")) {
+        // an elementwise chain feeding the column sum (kInputFusion.mlir.in:6-41), or a
+        // 16-bit input: one pass, every add rounded to the element type
+        Value &init = get(fr, op.outs[0], op);
+        if (init.type.elt != maybeOpen.type.elt) die(where + "reduction changing the element type");
+        XNodeP tree = maybeOpen.lazy ? maybeOpen.lazy : leaf(maybeOpen, 0);
+        ExprProgram p;
+        if (!compile(tree, p)) die("internal: an elementwise chain outgrew the fused kernel");
+        Value out = makeTensor(stream, outT);
+        ImexKernelDesc d = exprDesc(p, maybeOpen.type, dtypeCode(outT.elt), maybeOpen.type.shape[0],
+                                    maybeOpen.type.shape[1]);
+        d.flags |= IMEX_FLAG_REDUCE_LEADING;
+        if (!(init.isFill && init.fillValue == 0.0)) {
+          d.flags |= IMEX_FLAG_ACCUMULATE;
+          trace("gpuMemCopy(device -> device, " + std::to_string(out.buf->bytes) + " bytes)  // reduction init");
+          if (!g_plan) gpuMemCopy(stream, out.buf->ptr, init.buf->ptr, out.buf->bytes);
+        }
+        std::vector<void *> ptrs;
+        for (auto &bf : p.inputs) ptrs.push_back(bf->ptr);
+        ptrs.push_back(out.buf->ptr);
+        launch(stream, d, ptrs, exprText(p) + " " + outT.elt + " +reduce_leading");
+        fr.vals[res] = out;
+        break;
+      }
       Value &X = get(fr, op.ins[0], op);
       Value &init = get(fr, op.outs[0], op);
       if (X.type.elt != "f32") die(where + "sum reductions are f32 only");
@@ -754,8 +985,14 @@ private:
       fr.vals[res] = out;
       break;
     }
-    default:
+    default: {
+      ElementwiseInfo standalone;
+      if (classifyElementwise(op, fr.constants, standalone)) {  // e.g. an exp or a mul on its own
+        elementwiseOp(op, b, fr, where);
+        break;
+      }
       die(where + std::string(kindName(c.kind)) + " generic outside the chain it belongs to (softmax / silu); no CPU fallback");
+    }
     }
     (void)uses;
   }

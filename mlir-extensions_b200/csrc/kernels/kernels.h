@@ -92,6 +92,14 @@ cudaError_t launch_transpose3d_b32(const void *x, void *y, const int64_t dims[3]
 cudaError_t launch_eltwise_f32(const float *x, float *y, int64_t n, int epilogue,
                                cudaStream_t stream);
 
+// A fused chain of elementwise ops as a postfix program (ImexExprCode): Y[r,c] =
+// program(X_k[r,c] | X_k[c] | X_k[r] ...), every operation rounded to `dtype`; with
+// reduce_leading Y[c] = (acc ? Y[c] : 0) + sum_r program(...), r ascending.
+int expr_validate(const unsigned char *code, int max_len, int n_inputs);
+cudaError_t launch_expr(const void *const *inputs, int n_inputs, void *out, int64_t rows, int64_t cols,
+                        const unsigned char *code, int ncode, float c0, float c1, int dtype,
+                        int out_dtype, bool reduce_leading, bool accumulate, cudaStream_t stream);
+
 // Y[i] = convert(X[i]): f32 <-> bf16 / f16 (arith.extf / arith.truncf generics)
 cudaError_t launch_convert(const void *x, void *y, int64_t n, int in_dtype, int out_dtype,
                            cudaStream_t stream);

@@ -12,6 +12,7 @@
 #include "../kernels/kernels.h"
 #include "stats.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -93,6 +94,7 @@ const char *op_name(uint32_t op) {
   case IMEX_OP_ELTWISE: return "eltwise";
   case IMEX_OP_FILL_UNIFORM: return "fill_uniform";
   case IMEX_OP_FILL_NORMAL: return "fill_normal";
+  case IMEX_OP_EXPR: return "expr";
   }
   return nullptr;
 }
@@ -381,6 +383,25 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     err = imex::launch_eltwise_f32(static_cast<const float *>(ptrs[0]), static_cast<float *>(ptrs[1]),
                                    d.dims[0], static_cast<int>(d.epilogue), s->stream);
     break;
+  case IMEX_OP_EXPR: {
+    // dims = {rows, cols, 32 bytes of postfix code}; pointers = inputs in order, then Y
+    unsigned char code[IMEX_EXPR_MAX_CODE];
+    std::memcpy(code, &d.dims[2], sizeof code);
+    int n_inputs = 0;
+    for (int i = 0; i < IMEX_EXPR_MAX_CODE && code[i] != IMEX_X_END; ++i)
+      if (code[i] >= IMEX_X_IN && code[i] < IMEX_X_C0) n_inputs = std::max(n_inputs, (code[i] - 1) % 4 + 1);
+    const int ncode = imex::expr_validate(code, IMEX_EXPR_MAX_CODE, n_inputs);
+    if (ncode < 1) throw std::runtime_error("gpuLaunchKernel: malformed expression program");
+    need(static_cast<size_t>(n_inputs) + 1);
+    const bool reduce = d.flags & IMEX_FLAG_REDUCE_LEADING;
+    if (reduce && d.out_dtype != d.in_dtype)
+      throw std::runtime_error("gpuLaunchKernel: a reducing expression keeps its element type");
+    s->last_kernel = reduce ? "expr_reduce_leading" : "expr";
+    err = imex::launch_expr(ptrs, n_inputs, ptrs[n_inputs], d.dims[0], d.dims[1], code, ncode,
+                            d.fparams[0], d.fparams[1], static_cast<int>(d.in_dtype),
+                            static_cast<int>(d.out_dtype), reduce, acc, s->stream);
+    break;
+  }
   case IMEX_OP_FILL_UNIFORM:
     need(1);
     s->last_kernel = "fill_uniform";

@@ -258,6 +258,69 @@ void oracle_epilogue_f32(float *c, int64_t n, int epilogue) {
 }
 
 /* ------------------------------------------------------------------------
+ * single elementwise generics in the IR's element type */
+static inline float maximumf_(float a, float b);
+static inline float minimumf_(float a, float b) {
+  if (a != a || b != b)
+    return NAN;
+  if (a < b)
+    return a;
+  if (b < a)
+    return b;
+  return signbit(a) ? a : b; /* minimumf(+0,-0) = -0 */
+}
+
+float oracle_round_as(float v, int dtype) {
+  if (dtype == ORACLE_DT_BF16)
+    return oracle_bf16_to_f32(oracle_f32_to_bf16(v));
+  if (dtype == ORACLE_DT_F16)
+    return oracle_f16_to_f32(oracle_f32_to_f16(v));
+  return v;
+}
+
+int oracle_unary(int op, int dtype, const float *x, float *y, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    float v = x[i], r;
+    switch (op) {
+    case ORACLE_OP_NEGF: r = -v; break;
+    case ORACLE_OP_ABSF: r = fabsf(v); break;
+    case ORACLE_OP_LOG: r = logf(v); break;
+    case ORACLE_OP_EXP: r = expf(v); break;
+    case ORACLE_OP_SQRT: r = sqrtf(v); break;
+    case ORACLE_OP_RSQRT: r = 1.0f / sqrtf(v); break;
+    case ORACLE_OP_TANH: r = tanhf(v); break;
+    case ORACLE_OP_RELU: r = !(v <= 0.0f) ? v : 0.0f; break; /* cmpf ugt ; select */
+    default: return -1;
+    }
+    y[i] = oracle_round_as(r, dtype);
+  }
+  return 0;
+}
+
+int oracle_binary(int op, int dtype, const float *a, const float *b, float *y, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    float r;
+    switch (op) {
+    case ORACLE_OP_ADDF: r = a[i] + b[i]; break;
+    case ORACLE_OP_SUBF: r = a[i] - b[i]; break;
+    case ORACLE_OP_MULF: r = a[i] * b[i]; break;
+    case ORACLE_OP_DIVF: r = a[i] / b[i]; break;
+    case ORACLE_OP_MAXIMUMF: r = maximumf_(a[i], b[i]); break;
+    case ORACLE_OP_MINIMUMF: r = minimumf_(a[i], b[i]); break;
+    default: return -1;
+    }
+    y[i] = oracle_round_as(r, dtype);
+  }
+  return 0;
+}
+
+void oracle_reduce_leading_as(int dtype, const float *x, float *y, int64_t lead, int64_t inner) {
+  for (int64_t j = 0; j < inner; ++j)   /* d0: the output element */
+    for (int64_t i = 0; i < lead; ++i)  /* d1: the reduction */
+      y[j] = oracle_round_as(y[j] + x[i * inner + j], dtype);
+}
+
+/* ------------------------------------------------------------------------
  * softmax: the chain of generics with its full-size temporaries */
 static inline float maximumf_(float a, float b) {
   if (a != a || b != b)

@@ -76,6 +76,28 @@ void oracle_relu_f32(const float *x, float *y, int64_t n);
 void oracle_silu_f32(const float *x, float *y, int64_t n);
 void oracle_epilogue_f32(float *c, int64_t n, int epilogue);
 
+/* --- one elementwise generic at a time, in the element type of the IR ------
+ * The fused-chain benchmarks (benchmarks/kLoopFusion/kLoopFusion.mlir.in:4-30,
+ * benchmarks/kInputFusion/kInputFusion.mlir.in:6-41) are chains of these, each
+ * with its own full-size result; @dtype@ is f32, f16 or bf16
+ * (kLoopFusion.dtypes.in).  Arrays hold the values as f32; `dtype` (ORACLE_DT_*)
+ * says which type they stand for: a 16-bit operation is extend, operate in f32,
+ * round to nearest even back (how LLVM legalises half / bfloat arithmetic where
+ * the CPU has none).  The mnemonics are those of the IR. */
+enum { ORACLE_DT_F32 = 1, ORACLE_DT_BF16 = 2, ORACLE_DT_F16 = 3 };
+enum {
+  ORACLE_OP_NEGF = 32, ORACLE_OP_ABSF = 33, ORACLE_OP_LOG = 34, ORACLE_OP_EXP = 35,
+  ORACLE_OP_SQRT = 36, ORACLE_OP_RSQRT = 37, ORACLE_OP_TANH = 38, ORACLE_OP_RELU = 39,
+  ORACLE_OP_ADDF = 64, ORACLE_OP_SUBF = 65, ORACLE_OP_MULF = 66, ORACLE_OP_DIVF = 67,
+  ORACLE_OP_MAXIMUMF = 68, ORACLE_OP_MINIMUMF = 69
+};
+float oracle_round_as(float v, int dtype);
+int oracle_unary(int op, int dtype, const float *x, float *y, int64_t n);
+int oracle_binary(int op, int dtype, const float *a, const float *b, float *y, int64_t n);
+/* y[j] = init[j] + sum_i x[i,j], i ascending, every add rounded to dtype: the
+ * column reduce of kInputFusion.mlir.in:29-39 (maps (d0,d1)->(d1,d0), (d0,d1)->(d0)) */
+void oracle_reduce_leading_as(int dtype, const float *x, float *y, int64_t lead, int64_t inner);
+
 /* --- softmax over the last dim ------------------------------------------
  * BENCH  : fill -FLT_MAX; maximumf; x-max; exp; fill 0; sum (in+out); div
  *          (benchmarks/softmax/softmax_gpu.mlir.in:8-42)

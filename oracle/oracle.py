@@ -62,6 +62,12 @@ def _load():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = None
+    lib.oracle_unary.argtypes = [C.c_int, C.c_int, _fp, _fp, _i64]
+    lib.oracle_unary.restype = C.c_int
+    lib.oracle_binary.argtypes = [C.c_int, C.c_int, _fp, _fp, _fp, _i64]
+    lib.oracle_binary.restype = C.c_int
+    lib.oracle_reduce_leading_as.argtypes = [C.c_int, _fp, _fp, _i64, _i64]
+    lib.oracle_reduce_leading_as.restype = None
     lib.oracle_allclose_f32.argtypes = [_fp, _fp, _i64]
     lib.oracle_allclose_f32.restype = C.c_int
     lib.oracle_max_rel_err_f32.argtypes = [_fp, _fp, _i64, C.c_double]
@@ -197,6 +203,48 @@ def relu(x):
 
 def silu(x):
     return epilogue(x, EPI_SILU)
+
+
+DT_F32, DT_BF16, DT_F16 = 1, 2, 3
+UNARY = {"negf": 32, "absf": 33, "log": 34, "exp": 35, "sqrt": 36, "rsqrt": 37, "tanh": 38, "relu": 39}
+BINARY = {"addf": 64, "subf": 65, "mulf": 66, "divf": 67, "maximumf": 68, "minimumf": 69}
+
+
+def round_as(x, dtype):
+    """f32 array holding the values of `x` rounded to dtype (DT_*)."""
+    x = f32c(x)
+    if dtype == DT_BF16:
+        return bf16_bits_to_f32(to_bf16_bits(x))
+    if dtype == DT_F16:
+        return f16_bits_to_f32(to_f16_bits(x))
+    return x
+
+
+def unary(op, x, dtype=DT_F32):
+    """One elementwise generic `op` (IR mnemonic) in element type dtype; f32 array in and out."""
+    x = f32c(x)
+    y = np.empty_like(x)
+    if lib().oracle_unary(UNARY[op], dtype, _f(x), _f(y), x.size):
+        raise ValueError(op)
+    return y
+
+
+def binary(op, a, b, dtype=DT_F32):
+    a, b = f32c(a), f32c(b)
+    assert a.shape == b.shape
+    y = np.empty_like(a)
+    if lib().oracle_binary(BINARY[op], dtype, _f(a), _f(b), _f(y), a.size):
+        raise ValueError(op)
+    return y
+
+
+def reduce_leading_as(x, dtype=DT_F32, init=None):
+    """y[j] = init[j] + sum_i x[i,j] with every add rounded to dtype."""
+    x = f32c(x)
+    lead, inner = x.shape[0], int(np.prod(x.shape[1:]))
+    y = np.zeros(x.shape[1:], np.float32) if init is None else f32c(init).copy()
+    lib().oracle_reduce_leading_as(dtype, _f(x), _f(y), lead, inner)
+    return y
 
 
 def softmax(x, flavour=SOFTMAX_BENCH):

@@ -7,7 +7,7 @@ module {
     %0 = tensor.empty() : tensor<2x2xf32>
     %1 = linalg.generic {indexing_maps = [#map, #map], iterator_types = ["parallel", "parallel"]} ins(%x : tensor<2x2xf32>) outs(%0 : tensor<2x2xf32>) {
     ^bb0(%in: f32, %out: f32):
-      %s = math.sqrt %in : f32
+      %s = math.erf %in : f32
       linalg.yield %s : f32
     } -> tensor<2x2xf32>
     return

@@ -73,10 +73,19 @@ def test_transposed_operands_bias_and_16bit_result_fuse_into_one_launch():
     assert out.count("gpuLaunchKernel(4 pointer params)") == 2  # A, B, C, bias
 
 
+def test_elementwise_chains_fuse_into_one_launch_each():
+    rc, out, err = plan(os.path.join(MLIR, "fused_elementwise.mlir"))
+    assert rc == 0, err
+    ks = kernels(out)
+    assert [k.split(" dims")[0] for k in ks] == ["expr[7 ops, 2 inputs] f32", "expr[7 ops, 2 inputs] f16",
+                                                 "expr[4 ops, 2 inputs] f32 +reduce_leading"]
+    assert out.count("deferred:") == 8  # the generics that joined a later kernel
+
+
 def test_ir_outside_the_hot_path_is_refused():
     rc, out, err = plan(os.path.join(MLIR, "unrecognised.mlir"))
     assert rc == 1
-    assert "line 8" in err and "sqrt(in0)" in err and "no CPU fallback" in err
+    assert "line 8" in err and "erf(in0)" in err and "no CPU fallback" in err
 
 
 def test_parse_errors_name_the_line(tmp_path):
@@ -158,6 +167,11 @@ def test_f16_multiply_add_is_not_sent_to_the_tensor_cores():
      ["transpose2d dims=[1024,512"]),
     ("transpose/transpose3d_gpu", None, None),
     ("reduce/reduce_gpu", {}, ["reduce_leading dims=[32,4194304"]),
+    # four generics (log, absf, addf, subf) -> one launch; with the column reduce behind: still one
+    ("kLoopFusion/kLoopFusion", {}, ["expr[7 ops, 2 inputs] f32 dims=[512,1024"]),
+    ("kLoopFusion/kLoopFusion", {"dtype": "f16"}, ["expr[7 ops, 2 inputs] f16 dims=[512,1024"]),
+    ("kInputFusion/kInputFusion", {}, ["expr[5 ops, 2 inputs] f32 +reduce_leading dims=[512,1024"]),
+    ("kInputFusion/kInputFusion", {"dtype": "bf16"}, ["expr[5 ops, 2 inputs] bf16 +reduce_leading dims=[512,1024"]),
 ])
 def test_reference_benchmark_templates_are_recognised(tmp_path, name, subst, expect):
     src = open(os.path.join(REFERENCE, "benchmarks", name + ".mlir.in")).read()
@@ -165,7 +179,7 @@ def test_reference_benchmark_templates_are_recognised(tmp_path, name, subst, exp
         subst = {"in_shape": "16x96x96", "out_shape": "96x16x96", "affine_map_in": "d0, d1, d2",
                  "affine_map_out": "d1, d0, d2", "perm": "1, 0, 2"}
         expect = ["transpose3d"]
-    subst = dict(subst, dtype="f32")
+    subst = dict({"dtype": "f32"}, **subst)
     for k, v in subst.items():
         src = src.replace("@" + k + "@", v)
     leftover = re.findall(r"@[a-z_]+@", src)
@@ -182,7 +196,8 @@ def test_reference_benchmark_templates_are_recognised(tmp_path, name, subst, exp
 # ---------------------------------------------------------------- on the GPU
 @pytest.mark.gpu
 @pytest.mark.parametrize("fixture", ["matmul_f32.mlir", "matmul_bf16_relu_silu.mlir",
-                                     "softmax_silu_transpose.mlir", "matmul_f16_transposed_bias.mlir"])
+                                     "softmax_silu_transpose.mlir", "matmul_f16_transposed_bias.mlir",
+                                     "fused_elementwise.mlir"])
 def test_fixture_runs_and_matches_its_check_lines(fixture):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "mlir-extensions_b200", "imex_runner.py"),
                         "-i", os.path.join(MLIR, fixture), "-f", os.path.join(MLIR, "linalg-to-gpu.pp"),

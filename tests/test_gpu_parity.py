@@ -690,3 +690,117 @@ def test_allocation_failure_injected_on_the_host():
     r = _child("import os; s = pkg.Session(device=0)\nos.environ['IMEX_B200_FAIL_ALLOC'] = '1'\n"
                "s.alloc(1024)\nprint('not reached')\n")
     assert r.returncode < 0 and "injected allocation failure" in r.stdout and "not reached" not in r.stdout
+
+
+# ---------------------------------------------------------------- fused elementwise chains
+_NP16 = {"f16": (oracle.DT_F16, oracle.to_f16_bits, oracle.f16_bits_to_f32),
+         "bf16": (oracle.DT_BF16, oracle.to_bf16_bits, oracle.bf16_bits_to_f32)}
+
+
+def _typed(pkg, kind, values):
+    """(blob dtype, oracle dtype, device array, f32 view of the stored values)."""
+    B = pkg.blob
+    if kind == "f32":
+        v = oracle.f32c(values)
+        return B.F32, oracle.DT_F32, v, v
+    dt, to_bits, back = _NP16[kind]
+    bits = to_bits(values)
+    return (B.F16 if kind == "f16" else B.BF16), dt, bits, back(bits)
+
+
+def _from_device(kind, raw):
+    return raw if kind == "f32" else _NP16[kind][2](raw)
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("shape", [(512, 1024), (33, 1000), (7, 13)])
+def test_fused_chain_of_the_loop_fusion_benchmark(pkg, sess, kind, shape):
+    """(log(x0) + |x1|) - x0: the four generics of benchmarks/kLoopFusion/kLoopFusion.mlir.in:4-30
+    in one pass; the oracle runs them one at a time with full-size temporaries."""
+    B = pkg.blob
+    rows, cols = shape
+    bdt, odt, x0_dev, x0 = _typed(pkg, kind, oracle.fill_uniform(shape, 31, 0.5, 4.0))
+    _, _, x1_dev, x1 = _typed(pkg, kind, oracle.fill_uniform(shape, 32, -2.0, 2.0))
+    d0, d1 = sess.upload(x0_dev), sess.upload(x1_dev)
+    dy = sess.alloc(x0_dev.nbytes)
+    sess.run(B.expr("loop_fusion", rows, cols, "in0 log in1 abs add in0 sub", bdt), [d0, d1, dy])
+    assert sess.last_kernel() == "expr"
+    got = _from_device(kind, sess.download(dy, shape, x0_dev.dtype))
+    ref = oracle.binary("subf", oracle.binary("addf", oracle.unary("log", x0, odt),
+                                              oracle.unary("absf", x1, odt), odt), x0, odt)
+    # logf of the device and of glibc may differ in the last f32 bit; everything else is exact
+    ulp = {"f32": 2.0 ** -22, "f16": 2.0 ** -10, "bf16": 2.0 ** -7}[kind]
+    err = np.abs(got - ref)
+    assert np.all(err <= ulp * np.maximum(np.abs(ref), 1.0))
+    assert np.mean(got != ref) <= (0.35 if kind == "f32" else 0.01)
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind):
+    """neg, abs, add, sub, mul, max, min, relu and the broadcast forms round identically on
+    both sides: relu(max(x0 * row, -x1) - |col|) + min(x0, x1) * c0."""
+    B = pkg.blob
+    rows, cols = 70, 136
+    bdt, odt, x0_dev, x0 = _typed(pkg, kind, oracle.fill_uniform((rows, cols), 33, -3.0, 3.0))
+    _, _, x1_dev, x1 = _typed(pkg, kind, oracle.fill_uniform((rows, cols), 34, -3.0, 3.0))
+    _, _, rv_dev, rv = _typed(pkg, kind, oracle.fill_uniform((cols,), 35, -2.0, 2.0))
+    _, _, cv_dev, cv = _typed(pkg, kind, oracle.fill_uniform((rows,), 36, -2.0, 2.0))
+    ptrs = [sess.upload(a) for a in (x0_dev, x1_dev, rv_dev, cv_dev)]
+    dy = sess.alloc(x0_dev.nbytes)
+    prog = "in0 row2 mul in1 neg max col3 abs sub relu in0 in1 min c0 mul add"
+    sess.run(B.expr("exact", rows, cols, prog, bdt, consts=(0.75, 0.0)), ptrs + [dy])
+    got = sess.download(dy, (rows, cols), x0_dev.dtype)
+    R = np.broadcast_to(rv, (rows, cols)).copy()
+    Cv = np.broadcast_to(cv[:, None], (rows, cols)).copy()
+    c0 = np.full((rows, cols), 0.75, np.float32)
+    t = oracle.binary("maximumf", oracle.binary("mulf", x0, R, odt), oracle.unary("negf", x1, odt), odt)
+    t = oracle.unary("relu", oracle.binary("subf", t, oracle.unary("absf", Cv, odt), odt), odt)
+    u = oracle.binary("mulf", oracle.binary("minimumf", x0, x1, odt), c0, odt)
+    ref = oracle.binary("addf", t, u, odt)
+    ref_dev = ref if kind == "f32" else _NP16[kind][1](ref)
+    assert got.tobytes() == ref_dev.tobytes()
+
+
+@pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
+def test_fused_chain_into_column_reduce(pkg, sess, kind):
+    """|x0| + x1 summed over the rows, ascending, every step in the element type: the shape of
+    benchmarks/kInputFusion/kInputFusion.mlir.in:6-41 with exact operations -> bit-exact;
+    then the benchmark's own chain (with log) within a last-bit budget."""
+    B = pkg.blob
+    rows, cols = 512, 1024
+    bdt, odt, x0_dev, x0 = _typed(pkg, kind, oracle.fill_uniform((rows, cols), 37, -1.0, 1.0))
+    _, _, x1_dev, x1 = _typed(pkg, kind, oracle.fill_uniform((rows, cols), 38, 0.5, 2.0))
+    d0, d1 = sess.upload(x0_dev), sess.upload(x1_dev)
+    esz = x0_dev.dtype.itemsize
+    dy = sess.alloc(cols * esz)
+    sess.run(B.expr("input_fusion_exact", rows, cols, "in0 abs in1 add", bdt, reduce_leading=True), [d0, d1, dy])
+    assert sess.last_kernel() == "expr_reduce_leading"
+    got = sess.download(dy, (cols,), x0_dev.dtype)
+    ref = oracle.reduce_leading_as(oracle.binary("addf", oracle.unary("absf", x0, odt), x1, odt), odt)
+    ref_dev = ref if kind == "f32" else _NP16[kind][1](ref)
+    assert got.tobytes() == ref_dev.tobytes()
+    # accumulate: Y is read as the initial value
+    sess.run(B.expr("input_fusion_acc", rows, cols, "in0 abs in1 add", bdt, reduce_leading=True,
+                    accumulate=True), [d0, d1, dy])
+    got2 = sess.download(dy, (cols,), x0_dev.dtype)
+    ref2 = oracle.reduce_leading_as(oracle.binary("addf", oracle.unary("absf", x0, odt), x1, odt), odt, init=ref)
+    assert got2.tobytes() == (ref2 if kind == "f32" else _NP16[kind][1](ref2)).tobytes()
+    # the benchmark's chain: log(x1) + |x0|
+    sess.run(B.expr("input_fusion", rows, cols, "in1 log in0 abs add", bdt, reduce_leading=True), [d0, d1, dy])
+    got3 = _from_device(kind, sess.download(dy, (cols,), x0_dev.dtype))
+    ref3 = oracle.reduce_leading_as(oracle.binary("addf", oracle.unary("log", x1, odt),
+                                                  oracle.unary("absf", x0, odt), odt), odt)
+    tol = {"f32": 1e-5, "f16": 2.0 ** -8, "bf16": 2.0 ** -5}[kind]
+    assert oracle.max_rel_err(got3, ref3, 1e-3) <= tol
+
+
+def test_malformed_expression_programs_are_refused():
+    """Underflowing, leftover-value, unknown-opcode and too-deep programs fail through the
+    reference's error convention before anything is launched."""
+    B = load_package().blob
+    for bad in ([B.X_BINARY["add"]], [B.X_IN, B.X_IN], [200], [B.X_IN] * 9 + [B.X_BINARY["add"]] * 8):
+        r = _child("s = pkg.Session(device=0)\n"
+                   "x = s.upload(np.zeros((4, 4), np.float32)); y = s.alloc(64)\n"
+                   "s.run(B.expr('bad', 4, 4, bytes(%r)), [x, y])\nprint('not reached')\n" % (bad,))
+        assert r.returncode < 0 and "malformed expression program" in r.stdout
+        assert "not reached" not in r.stdout
