@@ -627,6 +627,19 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
               sess.kernel(B.transpose2d("transpose", 8192, 8192)), [T.data_ptr(), U.data_ptr()],
               "config 4b")
     del T, U
+    # the reference's fusion benchmark chain (log, absf, addf, subf: kLoopFusion), scaled up to
+    # 8192 x 8192 so that it streams from HBM; its own 512 x 1024 shape moves 6 MiB
+    for tag, tdt, bdt, esz in (("f32", torch.float32, B.F32, 4), ("f16", torch.float16, B.F16, 2)):
+        F0 = torch.empty((8192, 8192), dtype=tdt, device=dev).uniform_(0.5, 4.0)
+        F1 = torch.empty((8192, 8192), dtype=tdt, device=dev).uniform_(-2.0, 2.0)
+        F2 = torch.empty_like(F0)
+        NCU_TRAFFIC.setdefault("expr_" + tag, None)
+        hbm_entry("loop_fusion_8192x8192_" + tag, "expr_" + tag, 3 * F0.numel() * esz,
+                  sess.kernel(B.expr("loop_fusion", 8192, 8192, "in0 log in1 abs add in0 sub", bdt)),
+                  [F0.data_ptr(), F1.data_ptr(), F2.data_ptr()],
+                  "four elementwise generics fused into one pass: two reads (x0 is read twice, the "
+                  "second time from cache) and one write per element")
+        del F0, F1, F2
     # config 3: GEMM 4096^3 + relu
     n = 4096
     A = (torch.rand((n, n), device=dev) * 2 - 1).to(torch.bfloat16)
