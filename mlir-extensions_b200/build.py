@@ -33,6 +33,7 @@ RUNTIME_SOURCES = [
     "kernels/transpose.cu",
     "kernels/eltwise_fill.cu",
     "kernels/eltwise_expr.cu",
+    "kernels/expr_jit.cu",
     "kernels/wait_selftest.cu",
     "runtime/cuda_runtime_wrappers.cu",
     "runtime/stats.cpp",
@@ -91,7 +92,7 @@ def build(force=False, verbose=False):
     objs = _compile(RUNTIME_SOURCES, force, verbose)
     rt = os.path.join(LIB, "libimex_cuda_runtime.so")
     if force or _stale(rt, objs):
-        _run([_nvcc(), "-shared", "-o", rt] + objs + ["-cudart", "static"], verbose)
+        _run([_nvcc(), "-shared", "-o", rt] + objs + ["-cudart", "static", "-ldl"], verbose)
     if all(os.path.exists(os.path.join(CSRC, s)) for s in UTILS_SOURCES):
         objs = _compile(UTILS_SOURCES, force, verbose)
         ut = os.path.join(LIB, "libimex_runner_utils.so")

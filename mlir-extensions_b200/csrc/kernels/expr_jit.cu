@@ -1,0 +1,368 @@
+// Fused elementwise chains compiled at first use.
+//
+// The reference compiles its kernels when a module is first loaded (SPIR-V handed to
+// the driver's JIT, lib/ExecutionEngine/LEVELZERORUNTIME/LevelZeroRuntimeWrappers.cpp:
+// 402-431).  The expression programs of IMEX_OP_EXPR get the same treatment: the postfix
+// code is turned into straight-line CUDA C++ inside a fixed, hand-written kernel frame
+// (128-bit loads and stores, four or eight elements per thread), compiled for sm_100a
+// with NVRTC, loaded through the driver API and cached per (device, program, types).
+// NVRTC and the driver entry points are looked up at run time; when either is missing
+// or a compilation fails, the caller uses the interpreting kernel in eltwise_expr.cu
+// instead (same arithmetic, same results, slower).
+//
+// Arithmetic is that of eltwise_expr.cu: every operation in f32, rounded to the element
+// type after every operation, no contraction.
+#include "kernels.h"
+
+#include <cuda.h>
+#include <dlfcn.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+namespace imex {
+namespace {
+
+// ---- NVRTC, through dlopen ------------------------------------------------------
+struct Nvrtc {
+  using Program = void *;
+  int (*createProgram)(Program *, const char *, const char *, int, const char *const *,
+                       const char *const *) = nullptr;
+  int (*compileProgram)(Program, int, const char *const *) = nullptr;
+  int (*getCUBINSize)(Program, size_t *) = nullptr;
+  int (*getCUBIN)(Program, char *) = nullptr;
+  int (*getProgramLogSize)(Program, size_t *) = nullptr;
+  int (*getProgramLog)(Program, char *) = nullptr;
+  int (*destroyProgram)(Program *) = nullptr;
+  bool ok = false;
+};
+
+const Nvrtc &nvrtc() {
+  static Nvrtc n = [] {
+    Nvrtc r;
+    void *h = nullptr;
+    for (const char *name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
+                             "/usr/local/cuda/lib64/libnvrtc.so"}) {
+      h = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+      if (h) break;
+    }
+    if (!h) return r;
+    auto sym = [&](const char *s) { return dlsym(h, s); };
+    r.createProgram = reinterpret_cast<decltype(r.createProgram)>(sym("nvrtcCreateProgram"));
+    r.compileProgram = reinterpret_cast<decltype(r.compileProgram)>(sym("nvrtcCompileProgram"));
+    r.getCUBINSize = reinterpret_cast<decltype(r.getCUBINSize)>(sym("nvrtcGetCUBINSize"));
+    r.getCUBIN = reinterpret_cast<decltype(r.getCUBIN)>(sym("nvrtcGetCUBIN"));
+    r.getProgramLogSize = reinterpret_cast<decltype(r.getProgramLogSize)>(sym("nvrtcGetProgramLogSize"));
+    r.getProgramLog = reinterpret_cast<decltype(r.getProgramLog)>(sym("nvrtcGetProgramLog"));
+    r.destroyProgram = reinterpret_cast<decltype(r.destroyProgram)>(sym("nvrtcDestroyProgram"));
+    r.ok = r.createProgram && r.compileProgram && r.getCUBINSize && r.getCUBIN && r.destroyProgram;
+    return r;
+  }();
+  return n;
+}
+
+// ---- the three driver calls needed to run a cubin -------------------------------------
+struct Driver {
+  CUresult (*moduleLoadData)(CUmodule *, const void *) = nullptr;
+  CUresult (*moduleGetFunction)(CUfunction *, CUmodule, const char *) = nullptr;
+  CUresult (*launchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                           unsigned, CUstream, void **, void **) = nullptr;
+  bool ok = false;
+};
+
+const Driver &driver() {
+  static Driver d = [] {
+    Driver r;
+    auto get = [](const char *name) -> void * {
+      void *p = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess ||
+          q != cudaDriverEntryPointSuccess)
+        return nullptr;
+      return p;
+    };
+    r.moduleLoadData = reinterpret_cast<decltype(r.moduleLoadData)>(get("cuModuleLoadData"));
+    r.moduleGetFunction = reinterpret_cast<decltype(r.moduleGetFunction)>(get("cuModuleGetFunction"));
+    r.launchKernel = reinterpret_cast<decltype(r.launchKernel)>(get("cuLaunchKernel"));
+    r.ok = r.moduleLoadData && r.moduleGetFunction && r.launchKernel;
+    return r;
+  }();
+  return d;
+}
+
+// ---- source generation -----------------------------------------------------------------
+const char *kPrelude = R"SRC(
+typedef unsigned short u16;
+__device__ __forceinline__ float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
+__device__ __forceinline__ u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+__device__ __forceinline__ float b2f(u16 h) { return __uint_as_float(((unsigned)h) << 16); }
+__device__ __forceinline__ u16 f2b(float f) { u16 h; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+__device__ __forceinline__ float maximumf(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
+__device__ __forceinline__ float minimumf(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
+__device__ __forceinline__ float relu_ugt(float x) { return !(x <= 0.0f) ? x : 0.0f; }
+)SRC";
+
+struct TypeInfo {
+  const char *ctype;   // storage type
+  const char *load;    // storage -> f32
+  const char *round;   // f32 -> f32 rounded to the type
+  const char *store;   // f32 -> storage
+};
+TypeInfo type_info(int dt) {
+  if (dt == kF16) return {"u16", "h2f", "RH", "f2h"};
+  if (dt == kBF16) return {"u16", "b2f", "RB", "f2b"};
+  return {"float", "", "", ""};
+}
+
+// Straight-line code of the program: statements defining t0, t1, ...; returns the name
+// of the result.  Input k at the current element is `x<k>`.
+std::string emit_body(const unsigned char *code, int ncode, const std::string &round,
+                      std::ostringstream &os) {
+  std::vector<std::string> st;
+  int t = 0;
+  auto def = [&](const std::string &rhs, bool rounded) {
+    const std::string name = "t" + std::to_string(t++);
+    os << "    const float " << name << " = " << (rounded && !round.empty() ? round + "(" + rhs + ")" : rhs)
+       << ";\n";
+    return name;
+  };
+  for (int i = 0; i < ncode; ++i) {
+    const int op = code[i];
+    if (op >= 1 && op <= 12) {
+      st.push_back("x" + std::to_string((op - 1) % 4));
+    } else if (op == 13 || op == 14) {
+      st.push_back(def(op == 13 ? "c0" : "c1", true));
+    } else if (op == 15) {
+      st.push_back("0.0f");
+    } else if (op == 16) {
+      st.push_back("1.0f");
+    } else if (op < 64) {
+      const std::string a = st.back();
+      st.pop_back();
+      const char *f = op == 32 ? "-" : op == 33 ? "fabsf" : op == 34 ? "logf" : op == 35 ? "expf"
+                      : op == 36 ? "__fsqrt_rn" : op == 38 ? "tanhf" : op == 39 ? "relu_ugt" : "";
+      st.push_back(def(op == 37 ? "__fdiv_rn(1.0f, __fsqrt_rn(" + a + "))" : std::string(f) + "(" + a + ")", true));
+    } else {
+      const std::string b = st.back();
+      st.pop_back();
+      const std::string a = st.back();
+      st.pop_back();
+      const char *f = op == 64 ? "__fadd_rn" : op == 65 ? "__fsub_rn" : op == 66 ? "__fmul_rn"
+                      : op == 67 ? "__fdiv_rn" : op == 68 ? "maximumf" : "minimumf";
+      st.push_back(def(std::string(f) + "(" + a + ", " + b + ")", true));
+    }
+  }
+  return st.back();
+}
+
+struct Shape {
+  int mode[4];  // per input: 0 full, 1 row vector, 2 column vector, -1 unused
+  int n_inputs;
+};
+
+Shape input_shape(const unsigned char *code, int ncode, int n_inputs) {
+  Shape s;
+  s.n_inputs = n_inputs;
+  for (int k = 0; k < 4; ++k) s.mode[k] = -1;
+  for (int i = 0; i < ncode; ++i)
+    if (code[i] >= 1 && code[i] <= 12) s.mode[(code[i] - 1) % 4] = (code[i] - 1) / 4;
+  return s;
+}
+
+// One input may be pushed in one mode only (the front end never mixes them).
+bool single_mode(const unsigned char *code, int ncode) {
+  int seen[4] = {-1, -1, -1, -1};
+  for (int i = 0; i < ncode; ++i)
+    if (code[i] >= 1 && code[i] <= 12) {
+      const int k = (code[i] - 1) % 4, m = (code[i] - 1) / 4;
+      if (seen[k] >= 0 && seen[k] != m) return false;
+      seen[k] = m;
+    }
+  return true;
+}
+
+std::string generate(const unsigned char *code, int ncode, int n_inputs, int dtype, int out_dtype,
+                     bool reduce, int vec) {
+  const TypeInfo in = type_info(dtype), out = type_info(reduce ? dtype : out_dtype);
+  const Shape sh = input_shape(code, ncode, n_inputs);
+  std::ostringstream os;
+  os << kPrelude;
+  os << "#define RH(x) h2f(f2h(x))\n#define RB(x) b2f(f2b(x))\n";
+  os << "extern \"C\" __global__ void __launch_bounds__(256) expr_kernel(";
+  for (int k = 0; k < n_inputs; ++k) os << "const " << in.ctype << " *__restrict__ p" << k << ", ";
+  os << out.ctype << " *__restrict__ y, long long rows, long long cols, float c0, float c1, int accumulate) {\n";
+  auto load = [&](int k, const std::string &idx) {
+    return std::string(in.load) + "(p" + std::to_string(k) + "[" + idx + "])";
+  };
+  if (reduce) {
+    os << "  const long long col = blockIdx.x * (long long)blockDim.x + threadIdx.x;\n"
+       << "  if (col >= cols) return;\n"
+       << "  float acc = accumulate ? " << in.load << "(y[col]) : 0.0f;\n"
+       << "  for (long long row = 0; row < rows; ++row) {\n";
+    for (int k = 0; k < n_inputs; ++k)
+      if (sh.mode[k] >= 0)
+        os << "    const float x" << k << " = "
+           << load(k, sh.mode[k] == 0 ? "row * cols + col" : sh.mode[k] == 1 ? "col" : "row") << ";\n";
+    const std::string r = emit_body(code, ncode, in.round, os);
+    os << "    acc = " << (in.round[0] ? std::string(in.round) + "(__fadd_rn(acc, " + r + "))" : "__fadd_rn(acc, " + r + ")")
+       << ";\n  }\n"
+       << "  y[col] = " << out.store << "(acc);\n}\n";
+    return os.str();
+  }
+  // elementwise: `vec` consecutive columns of one row per thread and iteration
+  os << "  const long long groups_per_row = cols / " << vec << ", total = rows * groups_per_row;\n"
+     << "  for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < total;\n"
+     << "       g += (long long)gridDim.x * blockDim.x) {\n"
+     << "    const long long row = g / groups_per_row, col = (g % groups_per_row) * " << vec << ";\n"
+     << "    const long long base = row * cols + col;\n";
+  const int in_bytes = dtype == kF32 ? 4 : 2, out_bytes = (out_dtype == kF32 ? 4 : 2);
+  auto vec_type = [](int bytes) { return bytes == 16 ? "uint4" : bytes == 8 ? "uint2" : bytes == 4 ? "unsigned" : "u16"; };
+  // packed loads of the full-tensor and row-vector inputs
+  for (int k = 0; k < n_inputs; ++k) {
+    if (sh.mode[k] < 0) continue;
+    if (sh.mode[k] == 2) {
+      os << "    const float s" << k << " = " << load(k, "row") << ";\n";
+      continue;
+    }
+    if (vec == 1) {
+      os << "    const " << in.ctype << " v" << k << "[1] = {p" << k << "[" << (sh.mode[k] == 0 ? "base" : "col") << "]};\n";
+    } else {
+      os << "    __align__(16) " << in.ctype << " v" << k << "[" << vec << "];\n"
+         << "    *reinterpret_cast<" << vec_type(vec * in_bytes) << " *>(v" << k << ") = *reinterpret_cast<const "
+         << vec_type(vec * in_bytes) << " *>(p" << k << " + " << (sh.mode[k] == 0 ? "base" : "col") << ");\n";
+    }
+  }
+  os << "    __align__(16) " << out.ctype << " r[" << vec << "];\n"
+     << "#pragma unroll\n    for (int e = 0; e < " << vec << "; ++e) {\n";
+  for (int k = 0; k < n_inputs; ++k) {
+    if (sh.mode[k] < 0) continue;
+    if (sh.mode[k] == 2) os << "    const float x" << k << " = s" << k << ";\n";
+    else os << "    const float x" << k << " = " << in.load << "(v" << k << "[e]);\n";
+  }
+  const std::string r = emit_body(code, ncode, in.round, os);
+  os << "    r[e] = " << out.store << "(" << r << ");\n    }\n";
+  if (vec == 1) os << "    y[base] = r[0];\n";
+  else
+    os << "    *reinterpret_cast<" << vec_type(vec * out_bytes) << " *>(y + base) = *reinterpret_cast<const "
+       << vec_type(vec * out_bytes) << " *>(r);\n";
+  os << "  }\n}\n";
+  return os.str();
+}
+
+struct Compiled {
+  CUfunction fn = nullptr;
+  bool failed = false;
+};
+
+std::mutex g_mu;
+std::map<std::string, Compiled> g_cache;
+
+Compiled compile(const std::string &src) {
+  Compiled c;
+  const Nvrtc &n = nvrtc();
+  const Driver &d = driver();
+  Nvrtc::Program prog = nullptr;
+  if (n.createProgram(&prog, src.c_str(), "imex_expr.cu", 0, nullptr, nullptr) != 0) {
+    c.failed = true;
+    return c;
+  }
+  const char *opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", "--fmad=false"};
+  const int rc = n.compileProgram(prog, 4, opts);
+  if (rc != 0) {
+    if (getenv("IMEX_B200_JIT_VERBOSE") && n.getProgramLogSize && n.getProgramLog) {
+      size_t sz = 0;
+      n.getProgramLogSize(prog, &sz);
+      std::string log(sz, '\0');
+      n.getProgramLog(prog, &log[0]);
+      fprintf(stderr, "[imex expr jit] compilation failed:\n%s\n%s\n", log.c_str(), src.c_str());
+    }
+    n.destroyProgram(&prog);
+    c.failed = true;
+    return c;
+  }
+  size_t size = 0;
+  std::vector<char> cubin;
+  if (n.getCUBINSize(prog, &size) == 0 && size > 0) {
+    cubin.resize(size);
+    if (n.getCUBIN(prog, cubin.data()) != 0) cubin.clear();
+  }
+  n.destroyProgram(&prog);
+  CUmodule mod = nullptr;
+  if (cubin.empty() || d.moduleLoadData(&mod, cubin.data()) != CUDA_SUCCESS ||
+      d.moduleGetFunction(&c.fn, mod, "expr_kernel") != CUDA_SUCCESS) {
+    c.fn = nullptr;
+    c.failed = true;
+  }
+  return c;
+}
+
+} // namespace
+
+// cudaErrorNotSupported: no compiled kernel for this call (NVRTC or the driver entry
+// points are missing, the compilation failed, or IMEX_B200_NO_JIT is set); the caller
+// then runs the interpreting kernel.
+cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, int64_t rows, int64_t cols,
+                            const unsigned char *code, int ncode, float c0, float c1, int dtype,
+                            int out_dtype, bool reduce_leading, bool accumulate, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  if (getenv("IMEX_B200_NO_JIT") || !nvrtc().ok || !driver().ok) return cudaErrorNotSupported;
+  if (n_inputs < 0 || n_inputs > 4 || ncode < 1 || ncode > 32) return cudaErrorInvalidValue;
+  if (expr_validate(code, ncode, n_inputs) != ncode || !single_mode(code, ncode)) return cudaErrorNotSupported;
+  // elements per thread: 16 bytes of the narrower of input and output type, when the
+  // row length and the alignment allow it
+  int vec = 1;
+  if (!reduce_leading) {
+    bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    for (int i = 0; i < n_inputs; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(inputs[i]) & 15) == 0;
+    const int want = (dtype == kF32 || out_dtype == kF32) ? 4 : 8;
+    if (aligned && cols % want == 0) vec = want;
+    else if (aligned && cols % 4 == 0) vec = 4;
+  }
+  int device = 0;
+  cudaGetDevice(&device);
+  std::string key(reinterpret_cast<const char *>(code), static_cast<size_t>(ncode));
+  key += "|" + std::to_string(device) + "|" + std::to_string(dtype) + "|" + std::to_string(out_dtype) + "|" +
+         std::to_string(reduce_leading) + "|" + std::to_string(vec) + "|" + std::to_string(n_inputs);
+  Compiled c;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_cache.find(key);
+    if (it == g_cache.end()) {
+      cudaFree(nullptr);  // the primary context exists before the module is loaded into it
+      it = g_cache.emplace(key, compile(generate(code, ncode, n_inputs, dtype, out_dtype, reduce_leading, vec))).first;
+    }
+    c = it->second;
+  }
+  if (c.failed || !c.fn) return cudaErrorNotSupported;
+  const void *in[4] = {nullptr, nullptr, nullptr, nullptr};
+  for (int i = 0; i < n_inputs; ++i) in[i] = inputs[i];
+  long long r = rows, cl = cols;
+  int acc = accumulate ? 1 : 0;
+  std::vector<void *> args;
+  for (int i = 0; i < n_inputs; ++i) args.push_back(&in[i]);
+  args.push_back(&out);
+  args.push_back(&r);
+  args.push_back(&cl);
+  args.push_back(&c0);
+  args.push_back(&c1);
+  args.push_back(&acc);
+  unsigned blocks;
+  if (reduce_leading) {
+    blocks = static_cast<unsigned>((cols + 255) / 256);
+  } else {
+    const long long groups = rows * (cols / vec);
+    long long b = (groups + 255) / 256;
+    const long long cap = 148LL * 32;
+    blocks = static_cast<unsigned>(b > cap ? cap : b);
+  }
+  const CUresult rc = driver().launchKernel(c.fn, blocks, 1, 1, 256, 1, 1, 0, stream, args.data(), nullptr);
+  return rc == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
+}
+
+} // namespace imex

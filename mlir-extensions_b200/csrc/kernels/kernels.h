@@ -100,6 +100,12 @@ cudaError_t launch_expr(const void *const *inputs, int n_inputs, void *out, int6
                         const unsigned char *code, int ncode, float c0, float c1, int dtype,
                         int out_dtype, bool reduce_leading, bool accumulate, cudaStream_t stream);
 
+// The same call served by a kernel compiled for this program at first use (NVRTC);
+// cudaErrorNotSupported when no compiled kernel can be had: use launch_expr then.
+cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, int64_t rows, int64_t cols,
+                            const unsigned char *code, int ncode, float c0, float c1, int dtype,
+                            int out_dtype, bool reduce_leading, bool accumulate, cudaStream_t stream);
+
 // Y[i] = convert(X[i]): f32 <-> bf16 / f16 (arith.extf / arith.truncf generics)
 cudaError_t launch_convert(const void *x, void *y, int64_t n, int in_dtype, int out_dtype,
                            cudaStream_t stream);

@@ -396,10 +396,17 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     const bool reduce = d.flags & IMEX_FLAG_REDUCE_LEADING;
     if (reduce && d.out_dtype != d.in_dtype)
       throw std::runtime_error("gpuLaunchKernel: a reducing expression keeps its element type");
-    s->last_kernel = reduce ? "expr_reduce_leading" : "expr";
-    err = imex::launch_expr(ptrs, n_inputs, ptrs[n_inputs], d.dims[0], d.dims[1], code, ncode,
-                            d.fparams[0], d.fparams[1], static_cast<int>(d.in_dtype),
-                            static_cast<int>(d.out_dtype), reduce, acc, s->stream);
+    // compiled for this program when NVRTC is there, interpreted otherwise
+    s->last_kernel = reduce ? "expr_reduce_leading_jit" : "expr_jit";
+    err = imex::launch_expr_jit(ptrs, n_inputs, ptrs[n_inputs], d.dims[0], d.dims[1], code, ncode,
+                                d.fparams[0], d.fparams[1], static_cast<int>(d.in_dtype),
+                                static_cast<int>(d.out_dtype), reduce, acc, s->stream);
+    if (err == cudaErrorNotSupported) {
+      s->last_kernel = reduce ? "expr_reduce_leading" : "expr";
+      err = imex::launch_expr(ptrs, n_inputs, ptrs[n_inputs], d.dims[0], d.dims[1], code, ncode,
+                              d.fparams[0], d.fparams[1], static_cast<int>(d.in_dtype),
+                              static_cast<int>(d.out_dtype), reduce, acc, s->stream);
+    }
     break;
   }
   case IMEX_OP_FILL_UNIFORM:

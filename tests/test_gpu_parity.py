@@ -712,9 +712,18 @@ def _from_device(kind, raw):
     return raw if kind == "f32" else _NP16[kind][2](raw)
 
 
+@pytest.fixture(params=["compiled", "interpreted"])
+def expr_path(request, monkeypatch):
+    """Both servers of IMEX_OP_EXPR: the kernel compiled for the program at first use and the
+    interpreting kernel that takes over where no compiler is to be had."""
+    if request.param == "interpreted":
+        monkeypatch.setenv("IMEX_B200_NO_JIT", "1")
+    return "_jit" if request.param == "compiled" else ""
+
+
 @pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("shape", [(512, 1024), (33, 1000), (7, 13)])
-def test_fused_chain_of_the_loop_fusion_benchmark(pkg, sess, kind, shape):
+def test_fused_chain_of_the_loop_fusion_benchmark(pkg, sess, kind, shape, expr_path):
     """(log(x0) + |x1|) - x0: the four generics of benchmarks/kLoopFusion/kLoopFusion.mlir.in:4-30
     in one pass; the oracle runs them one at a time with full-size temporaries."""
     B = pkg.blob
@@ -724,7 +733,7 @@ def test_fused_chain_of_the_loop_fusion_benchmark(pkg, sess, kind, shape):
     d0, d1 = sess.upload(x0_dev), sess.upload(x1_dev)
     dy = sess.alloc(x0_dev.nbytes)
     sess.run(B.expr("loop_fusion", rows, cols, "in0 log in1 abs add in0 sub", bdt), [d0, d1, dy])
-    assert sess.last_kernel() == "expr"
+    assert sess.last_kernel() == "expr" + expr_path
     got = _from_device(kind, sess.download(dy, shape, x0_dev.dtype))
     ref = oracle.binary("subf", oracle.binary("addf", oracle.unary("log", x0, odt),
                                               oracle.unary("absf", x1, odt), odt), x0, odt)
@@ -736,7 +745,7 @@ def test_fused_chain_of_the_loop_fusion_benchmark(pkg, sess, kind, shape):
 
 
 @pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
-def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind):
+def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind, expr_path):
     """neg, abs, add, sub, mul, max, min, relu and the broadcast forms round identically on
     both sides: relu(max(x0 * row, -x1) - |col|) + min(x0, x1) * c0."""
     B = pkg.blob
@@ -749,6 +758,7 @@ def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind):
     dy = sess.alloc(x0_dev.nbytes)
     prog = "in0 row2 mul in1 neg max col3 abs sub relu in0 in1 min c0 mul add"
     sess.run(B.expr("exact", rows, cols, prog, bdt, consts=(0.75, 0.0)), ptrs + [dy])
+    assert sess.last_kernel() == "expr" + expr_path
     got = sess.download(dy, (rows, cols), x0_dev.dtype)
     R = np.broadcast_to(rv, (rows, cols)).copy()
     Cv = np.broadcast_to(cv[:, None], (rows, cols)).copy()
@@ -759,10 +769,14 @@ def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind):
     ref = oracle.binary("addf", t, u, odt)
     ref_dev = ref if kind == "f32" else _NP16[kind][1](ref)
     assert got.tobytes() == ref_dev.tobytes()
+    if kind != "f32":  # the same 16-bit arithmetic, result stored as f32
+        dy32 = sess.alloc(rows * cols * 4)
+        sess.run(B.expr("exact_f32_out", rows, cols, prog, bdt, out_dtype=B.F32, consts=(0.75, 0.0)), ptrs + [dy32])
+        assert sess.download(dy32, (rows, cols), np.float32).tobytes() == ref.tobytes()
 
 
 @pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
-def test_fused_chain_into_column_reduce(pkg, sess, kind):
+def test_fused_chain_into_column_reduce(pkg, sess, kind, expr_path):
     """|x0| + x1 summed over the rows, ascending, every step in the element type: the shape of
     benchmarks/kInputFusion/kInputFusion.mlir.in:6-41 with exact operations -> bit-exact;
     then the benchmark's own chain (with log) within a last-bit budget."""
@@ -774,7 +788,7 @@ def test_fused_chain_into_column_reduce(pkg, sess, kind):
     esz = x0_dev.dtype.itemsize
     dy = sess.alloc(cols * esz)
     sess.run(B.expr("input_fusion_exact", rows, cols, "in0 abs in1 add", bdt, reduce_leading=True), [d0, d1, dy])
-    assert sess.last_kernel() == "expr_reduce_leading"
+    assert sess.last_kernel() == "expr_reduce_leading" + expr_path
     got = sess.download(dy, (cols,), x0_dev.dtype)
     ref = oracle.reduce_leading_as(oracle.binary("addf", oracle.unary("absf", x0, odt), x1, odt), odt)
     ref_dev = ref if kind == "f32" else _NP16[kind][1](ref)
