@@ -640,6 +640,22 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
                   "four elementwise generics fused into one pass: two reads (x0 is read twice, the "
                   "second time from cache) and one write per element")
         del F0, F1, F2
+    # attention forward at the reference test's size: Z*H = 4 heads, 4096 keys, d 64, f16
+    heads, n_ctx = 4, 4096
+    Q = (torch.rand((heads * n_ctx, 64), device=dev) * 2 - 1).to(torch.float16)
+    Kt = (torch.rand((heads * n_ctx, 64), device=dev) * 2 - 1).to(torch.float16)
+    Vt = (torch.rand((heads * n_ctx, 64), device=dev) * 2 - 1).to(torch.float16)
+    Ot = torch.empty_like(Q)
+    ak = sess.kernel(B.attention_fwd("attention", heads, n_ctx, 64, B.F16, 0.5))
+    med, mn = timed(ak, [Q.data_ptr(), Kt.data_ptr(), Vt.data_ptr(), Ot.data_ptr()], cold=True)
+    aflops = 4.0 * heads * n_ctx * n_ctx * 64
+    out["attention_fwd_4x4096x64"] = {
+        "value": aflops / (med * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_cold_median": med, "ms_cold_min": mn,
+        "algorithmic_flops": aflops,
+        "roofline": {"bound": "tensor", "achieved": aflops / (med * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": aflops / (med * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None},
+        "note": "the reference's flash-attention test shape; 128 CTAs of 128 query rows, 17 GFLOP in all"}
+    del Q, Kt, Vt, Ot
     # config 3: GEMM 4096^3 + relu
     n = 4096
     A = (torch.rand((n, n), device=dev) * 2 - 1).to(torch.bfloat16)

@@ -65,6 +65,10 @@ extern "C" {
  *                   sum over rows, ascending, of the expression (the elementwise chain
  *                   feeding a column reduce, benchmarks/kInputFusion/kInputFusion.mlir.in:
  *                   6-41); otherwise Y[rows,cols] of out_dtype.
+ *   ATTENTION_FWD   Q, K, V, O: [heads * n_ctx, d_head] f16 or bf16, heads one after the
+ *                   other; dims = {heads, n_ctx, d_head}; fparams[0] = sm_scale;
+ *                   O = softmax(sm_scale * Q K^T) V per head, f32 accumulation
+ *                   (test/Integration/Dialect/XeGPU/WG/flash_attention_fwd.mlir:254-330)
  *   FILL_UNIFORM    Y[n]  dims = {n, seed, first}; fparams = {lo, hi}
  *   FILL_NORMAL     Y[n]  dims = {n, seed, first}; fparams = {mean, stddev}
  */
@@ -79,7 +83,8 @@ enum ImexOp {
   IMEX_OP_ELTWISE = 8,
   IMEX_OP_FILL_UNIFORM = 9,
   IMEX_OP_FILL_NORMAL = 10,
-  IMEX_OP_EXPR = 11
+  IMEX_OP_EXPR = 11,
+  IMEX_OP_ATTENTION_FWD = 12
 };
 
 /* Postfix code of IMEX_OP_EXPR.  Pushes take the element of input k at the current

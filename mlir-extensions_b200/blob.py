@@ -12,7 +12,7 @@ NAME_MAX = 64
 
 OP_GEMM, OP_SOFTMAX, OP_REDUCE_ROWS, OP_REDUCE_LEADING, OP_REDUCE_ALL = 1, 2, 3, 4, 5
 OP_TRANSPOSE2D, OP_TRANSPOSE3D, OP_ELTWISE, OP_FILL_UNIFORM, OP_FILL_NORMAL = 6, 7, 8, 9, 10
-OP_EXPR = 11
+OP_EXPR, OP_ATTENTION_FWD = 11, 12
 F32, BF16, F16, I32 = 1, 2, 3, 4
 EPI_NONE, EPI_RELU, EPI_SILU = 0, 1, 2
 FLAG_ACCUMULATE, FLAG_BIAS, FLAG_SOFTMAX_NEG_INF, FLAG_TRANS_A, FLAG_TRANS_B = 1, 2, 4, 8, 16
@@ -110,6 +110,12 @@ def expr(name, rows, cols, program, dtype=F32, out_dtype=None, reduce_leading=Fa
     flags = (FLAG_REDUCE_LEADING if reduce_leading else 0) | (FLAG_ACCUMULATE if accumulate else 0)
     return KernelDesc(name, OP_EXPR, dtype, dtype if out_dtype is None else out_dtype, 0, flags,
                       (rows, cols) + words, fparams=consts)
+
+
+def attention_fwd(name, heads, n_ctx, d_head=64, dtype=F16, sm_scale=0.5):
+    """Pointers Q, K, V, O: [heads * n_ctx, d_head] arrays of dtype, heads one after the other."""
+    return KernelDesc(name, OP_ATTENTION_FWD, dtype, dtype, 0, 0, (heads, n_ctx, d_head),
+                      fparams=(sm_scale, 0.0))
 
 
 def softmax(name, rows, cols, neg_inf_init=False):

@@ -34,6 +34,7 @@ RUNTIME_SOURCES = [
     "kernels/eltwise_fill.cu",
     "kernels/eltwise_expr.cu",
     "kernels/expr_jit.cu",
+    "kernels/flash_attention.cu",
     "kernels/wait_selftest.cu",
     "runtime/cuda_runtime_wrappers.cu",
     "runtime/stats.cpp",

@@ -61,6 +61,14 @@ size_t gemm_tcgen05_workspace_bytes();  // scratch the pair kernel can use for a
 cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &p, unsigned *status,
                                      cudaStream_t stream);
 
+// O = softmax(sm_scale * Q K^T) V per head; Q, K, V, O are [heads * n_ctx, 64] f16 or bf16
+// arrays, heads one after the other (tcgen05 for both products, one pass over K and V).
+bool flash_attention_supported(int64_t heads, int64_t n_ctx, int64_t d_head, int dtype, const void *q,
+                               const void *k, const void *v, const void *o);
+cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void *v, void *o, int64_t heads,
+                                       int64_t n_ctx, int64_t d_head, float sm_scale, int dtype,
+                                       unsigned *status, cudaStream_t stream);
+
 // One thread waits (bounded, ~1 ms) on a barrier nothing signals and reports
 // kStatusSelfTestTimeout: exercises wait expiry -> status word -> gpuWait error.
 cudaError_t launch_wait_selftest(unsigned *status, cudaStream_t stream);

@@ -95,6 +95,7 @@ const char *op_name(uint32_t op) {
   case IMEX_OP_FILL_UNIFORM: return "fill_uniform";
   case IMEX_OP_FILL_NORMAL: return "fill_normal";
   case IMEX_OP_EXPR: return "expr";
+  case IMEX_OP_ATTENTION_FWD: return "attention_fwd";
   }
   return nullptr;
 }
@@ -409,6 +410,16 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     }
     break;
   }
+  case IMEX_OP_ATTENTION_FWD:
+    need(4);
+    if (d.in_dtype != d.out_dtype) throw std::runtime_error("gpuLaunchKernel: attention keeps its element type");
+    if (!imex::flash_attention_supported(d.dims[0], d.dims[1], d.dims[2], static_cast<int>(d.in_dtype), ptrs[0],
+                                         ptrs[1], ptrs[2], ptrs[3]))
+      throw std::runtime_error("gpuLaunchKernel: attention needs f16/bf16, d_head 64 and 16-byte aligned arrays");
+    s->last_kernel = "flash_attention_fwd";
+    err = imex::launch_flash_attention_fwd(ptrs[0], ptrs[1], ptrs[2], ptrs[3], d.dims[0], d.dims[1], d.dims[2],
+                                           d.fparams[0], static_cast<int>(d.in_dtype), s->status_dev, s->stream);
+    break;
   case IMEX_OP_FILL_UNIFORM:
     need(1);
     s->last_kernel = "fill_uniform";

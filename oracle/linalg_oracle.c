@@ -257,9 +257,94 @@ void oracle_epilogue_f32(float *c, int64_t n, int epilogue) {
     oracle_silu_f32(c, c, n);
 }
 
+static inline float maximumf_(float a, float b);
+
+/* ------------------------------------------------------------------------
+ * attention forward, as the reference test's cpu_impl computes it */
+typedef struct {
+  const uint16_t *Q, *K, *V;
+  uint16_t *O;
+  int64_t r0, r1, n_ctx, d_head;
+  float sm_scale;
+  int is_bf16;
+} AttnJob;
+
+static void *attn_job_main(void *arg) {
+  AttnJob *a = (AttnJob *)arg;
+  const int64_t n = a->n_ctx, d = a->d_head;
+  const float log2e = 1.442695040888963f;
+  float *s = (float *)malloc(sizeof(float) * (size_t)n);
+  float *q = (float *)malloc(sizeof(float) * (size_t)d);
+  float *pv = (float *)malloc(sizeof(float) * (size_t)d);
+  for (int64_t row = a->r0; row < a->r1; ++row) {
+    const int64_t head = row / n, base = head * n;
+    for (int64_t k = 0; k < d; ++k)
+      q[k] = x16_to_f32(a->Q[row * d + k], a->is_bf16);
+    for (int64_t j = 0; j < n; ++j) {
+      float acc = 0.0f;
+      const uint16_t *kr = a->K + (base + j) * d;
+      for (int64_t k = 0; k < d; ++k) {
+        float t = q[k] * x16_to_f32(kr[k], a->is_bf16);
+        acc = acc + t;
+      }
+      s[j] = acc * a->sm_scale;
+    }
+    float mx = -INFINITY;
+    for (int64_t j = 0; j < n; ++j)
+      mx = maximumf_(mx, s[j]);
+    for (int64_t j = 0; j < n; ++j) {
+      float t = s[j] - mx;
+      float t1 = t * log2e;
+      s[j] = exp2f(t1);
+    }
+    float sum = 0.0f;
+    for (int64_t j = 0; j < n; ++j)
+      sum = sum + s[j];
+    for (int64_t j = 0; j < n; ++j)
+      s[j] = s[j] / sum;
+    for (int64_t c = 0; c < d; ++c)
+      pv[c] = 0.0f;
+    for (int64_t j = 0; j < n; ++j) { /* same per-(row, c) order as the k loop of the test */
+      const float p = a->is_bf16 ? oracle_bf16_to_f32(oracle_f32_to_bf16(s[j]))
+                                 : oracle_f16_to_f32(oracle_f32_to_f16(s[j]));
+      const uint16_t *vr = a->V + (base + j) * d;
+      for (int64_t c = 0; c < d; ++c) {
+        float t = p * x16_to_f32(vr[c], a->is_bf16);
+        pv[c] = t + pv[c];
+      }
+    }
+    for (int64_t c = 0; c < d; ++c)
+      a->O[row * d + c] = a->is_bf16 ? oracle_f32_to_bf16(pv[c]) : oracle_f32_to_f16(pv[c]);
+  }
+  free(s);
+  free(q);
+  free(pv);
+  return NULL;
+}
+
+void oracle_attention_fwd_x16(const uint16_t *Q, const uint16_t *K, const uint16_t *V, uint16_t *O,
+                              int64_t heads, int64_t n_ctx, int64_t d_head, float sm_scale,
+                              int is_bf16) {
+  const int64_t rows = heads * n_ctx;
+  int nt = oracle_threads();
+  if (nt > rows)
+    nt = rows > 0 ? (int)rows : 1;
+  pthread_t tid[64];
+  AttnJob job[64];
+  for (int t = 0; t < nt; ++t) {
+    job[t] = (AttnJob){Q, K, V, O, rows * t / nt, rows * (t + 1) / nt, n_ctx, d_head, sm_scale, is_bf16};
+    if (t == nt - 1 || pthread_create(&tid[t], NULL, attn_job_main, &job[t]) != 0) {
+      attn_job_main(&job[t]);
+      tid[t] = 0;
+    }
+  }
+  for (int t = 0; t < nt - 1; ++t)
+    if (tid[t])
+      pthread_join(tid[t], NULL);
+}
+
 /* ------------------------------------------------------------------------
  * single elementwise generics in the IR's element type */
-static inline float maximumf_(float a, float b);
 static inline float minimumf_(float a, float b) {
   if (a != a || b != b)
     return NAN;

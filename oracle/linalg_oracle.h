@@ -98,6 +98,19 @@ int oracle_binary(int op, int dtype, const float *a, const float *b, float *y, i
  * column reduce of kInputFusion.mlir.in:29-39 (maps (d0,d1)->(d1,d0), (d0,d1)->(d0)) */
 void oracle_reduce_leading_as(int dtype, const float *x, float *y, int64_t lead, int64_t inner);
 
+/* --- attention forward ----------------------------------------------------
+ * The CPU check of the reference's flash-attention test
+ * (test/Integration/Dialect/XeGPU/WG/flash_attention_fwd.mlir:334-432): Q, K, V
+ * and O are [heads * n_ctx, d_head] 16-bit arrays, heads laid out one after the
+ * other; per head S = sm_scale * (Q . K^T) in f32 (k ascending); row max with
+ * maximumf from -inf; exp2((s - max) * log2e); row sum (j ascending); p / sum;
+ * O = P . V with p truncated to the 16-bit type first, f32 accumulation (key
+ * ascending), result truncated to the 16-bit type.  Rows are independent and are
+ * spread over threads. */
+void oracle_attention_fwd_x16(const uint16_t *Q, const uint16_t *K, const uint16_t *V, uint16_t *O,
+                              int64_t heads, int64_t n_ctx, int64_t d_head, float sm_scale,
+                              int is_bf16);
+
 /* --- softmax over the last dim ------------------------------------------
  * BENCH  : fill -FLT_MAX; maximumf; x-max; exp; fill 0; sum (in+out); div
  *          (benchmarks/softmax/softmax_gpu.mlir.in:8-42)

@@ -68,6 +68,8 @@ def _load():
     lib.oracle_binary.restype = C.c_int
     lib.oracle_reduce_leading_as.argtypes = [C.c_int, _fp, _fp, _i64, _i64]
     lib.oracle_reduce_leading_as.restype = None
+    lib.oracle_attention_fwd_x16.argtypes = [_u16p, _u16p, _u16p, _u16p, _i64, _i64, _i64, C.c_float, C.c_int]
+    lib.oracle_attention_fwd_x16.restype = None
     lib.oracle_allclose_f32.argtypes = [_fp, _fp, _i64]
     lib.oracle_allclose_f32.restype = C.c_int
     lib.oracle_max_rel_err_f32.argtypes = [_fp, _fp, _i64, C.c_double]
@@ -245,6 +247,17 @@ def reduce_leading_as(x, dtype=DT_F32, init=None):
     y = np.zeros(x.shape[1:], np.float32) if init is None else f32c(init).copy()
     lib().oracle_reduce_leading_as(dtype, _f(x), _f(y), lead, inner)
     return y
+
+
+def attention_fwd(q_bits, k_bits, v_bits, heads, sm_scale, is_bf16=False):
+    """O bits [heads * n_ctx, d_head] of the reference test's CPU attention; inputs are
+    uint16 arrays of that shape."""
+    q, k, v = (np.ascontiguousarray(a, dtype=np.uint16) for a in (q_bits, k_bits, v_bits))
+    rows, d = q.shape
+    assert rows % heads == 0 and k.shape == q.shape == v.shape
+    o = np.empty_like(q)
+    lib().oracle_attention_fwd_x16(_h(q), _h(k), _h(v), _h(o), heads, rows // heads, d, sm_scale, int(is_bf16))
+    return o
 
 
 def softmax(x, flavour=SOFTMAX_BENCH):

@@ -818,3 +818,54 @@ def test_malformed_expression_programs_are_refused():
                    "s.run(B.expr('bad', 4, 4, bytes(%r)), [x, y])\nprint('not reached')\n" % (bad,))
         assert r.returncode < 0 and "malformed expression program" in r.stdout
         assert "not reached" not in r.stdout
+
+
+# ---------------------------------------------------------------- attention forward
+def _attention_inputs(heads, n_ctx, kind, seed):
+    conv = oracle.to_bf16_bits if kind == "bf16" else oracle.to_f16_bits
+    shape = (heads * n_ctx, 64)
+    # the reference test fills Q, K, V with uniform values in (-1, 1)
+    # (test/Integration/Dialect/XeGPU/WG/flash_attention_fwd.mlir:458-461,480-492)
+    return [conv(oracle.fill_uniform(shape, seed + i, -1.0, 1.0)) for i in range(3)]
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("heads,n_ctx", [(1, 128), (2, 256), (3, 384), (2, 200), (1, 72), (5, 1000)])
+def test_attention_forward_matches_the_reference_cpu_check(pkg, sess, kind, heads, n_ctx):
+    B = pkg.blob
+    q, k, v = _attention_inputs(heads, n_ctx, kind, 41)
+    dq, dk, dv = sess.upload(q), sess.upload(k), sess.upload(v)
+    poison = np.full(q.shape, 0x7E00 if kind == "f16" else 0x7FC0, np.uint16)  # NaN: must be overwritten
+    do = sess.upload(poison)
+    sess.run(B.attention_fwd("attn", heads, n_ctx, 64, B.BF16 if kind == "bf16" else B.F16, 0.5), [dq, dk, dv, do])
+    assert sess.last_kernel() == "flash_attention_fwd"
+    back = oracle.bf16_bits_to_f32 if kind == "bf16" else oracle.f16_bits_to_f32
+    got = back(sess.download(do, q.shape, np.uint16))
+    ref = back(oracle.attention_fwd(q, k, v, heads, 0.5, kind == "bf16"))
+    assert not np.isnan(got).any()
+    # The kernel rounds the un-normalised probabilities to 16 bits and divides by the row sum at
+    # the end; the reference check normalises first.  Both are equally far from the exact
+    # result (f16, 128 keys: 2.5e-4 against 3.0e-4 in the worst element), so they may differ from
+    # one another by a 16-bit ulp or two per element: relative Frobenius 1e-3 (f16) / 2^-8 (bf16),
+    # elementwise two ulps plus an absolute floor for outputs near zero.
+    frob_tol, rtol, atol = (2.0 ** -8, 2.0 ** -7, 2e-3) if kind == "bf16" else (1e-3, 2e-3, 2.5e-4)
+    assert oracle.rel_frobenius(got, ref) <= frob_tol
+    assert np.all(np.abs(got - ref) <= atol + rtol * np.abs(ref))
+
+
+def test_attention_forward_at_the_reference_size(pkg, sess):
+    """Z = 2, H = 2, N_CTX = 4096, D_HEAD = 64, sm_scale 0.5
+    (flash_attention_fwd.mlir:452-456): sampled heads' rows against the oracle, every row
+    against the softmax property that O lies inside the convex hull of V's rows."""
+    B = pkg.blob
+    heads, n_ctx = 4, 4096
+    q, k, v = _attention_inputs(heads, n_ctx, "f16", 51)
+    dq, dk, dv, do = sess.upload(q), sess.upload(k), sess.upload(v), sess.alloc(q.nbytes)
+    sess.run(B.attention_fwd("attn4k", heads, n_ctx, 64, B.F16, 0.5), [dq, dk, dv, do])
+    got = oracle.f16_bits_to_f32(sess.download(do, q.shape, np.uint16))
+    ref = oracle.f16_bits_to_f32(oracle.attention_fwd(q, k, v, heads, 0.5, False))
+    assert oracle.rel_frobenius(got, ref) <= 1e-3
+    assert oracle.allclose(got, ref)
+    vf = oracle.f16_bits_to_f32(v).reshape(heads, n_ctx, 64)
+    g = got.reshape(heads, n_ctx, 64)
+    assert np.all(g <= vf.max(axis=1, keepdims=True) + 1e-3) and np.all(g >= vf.min(axis=1, keepdims=True) - 1e-3)
