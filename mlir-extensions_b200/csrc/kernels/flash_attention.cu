@@ -12,12 +12,12 @@
 //               K-major) into one of two TMEM S buffers, one block ahead of the softmax;
 //               then PV_j = P_j V_j (M128 N64 K128; P K-major from shared memory, V
 //               MN-major exactly as it lies in its tile) into a third TMEM buffer.
-//   warps 2-5   one thread per query row: reads its row of S_j from TMEM (tcgen05.ld,
-//               32 columns at a time, twice: once for the maximum, once for the
-//               exponentials), keeps m and l, writes P_j as 16-bit values into shared
-//               memory in the swizzled K-major layout the MMA expects, and folds PV_{j-1}
-//               into its 64 f32 output registers while the tensor core works on PV_j's
-//               predecessor chain.  No shuffles: a row is one thread.
+//   warps 2-9   two threads per query row (64 keys and 32 output columns each): read the
+//               scores of S_j from TMEM once (tcgen05.ld), free the S buffer, exchange the
+//               two partial row maxima through shared memory, keep m and a partial l,
+//               write P_j as 16-bit values into shared memory in the swizzled K-major
+//               layout the MMA expects, and fold PV_{j-1} into 32 f32 output registers
+//               while the tensor core works on S_{j+1} and PV_j.  No shuffles.
 // Every wait is bounded; a wait that runs out records a status code, the roles leave
 // their loops, the CTA syncs and frees its TMEM.
 #include "kernels.h"
@@ -41,10 +41,11 @@ constexpr int DH = 64;         // head dimension
 constexpr int KV_STAGES = 3;  // 144 KB of shared memory: one CTA per SM, which owns all 512 TMEM columns
 constexpr int TILE_BYTES = 128 * DH * 2;        // 16 KB: any of the Q / K / V tiles
 constexpr int P_BYTES = BQ * BKV * 2;           // 32 KB: two 128 x 64-key boxes
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
 constexpr int TMEM_COLS = 512;                  // S0 [0,128) S1 [128,256) PV [256,320)
 constexpr int PV_COL = 256;
-constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 1024 + 256;
+constexpr int XCH_BYTES = 2 * 2 * BQ * 4;           // partial row maxima / sums of the two half-rows
+constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 1024 + 256 + XCH_BYTES;
 
 struct AttnParams {
   void *O;
@@ -62,13 +63,20 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// two f32 -> one 32-bit word of two 16-bit values (a in the low half), round to nearest even
 __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16) {
-  if (is_bf16) {
-    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a))) |
-           (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(b))) << 16);
-  }
-  return static_cast<uint32_t>(__half_as_ushort(__float2half_rn(a))) |
-         (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(b))) << 16);
+  uint32_t w;
+  if (is_bf16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));
+  return w;
+}
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ void st_shared_v4_u32(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -93,10 +101,12 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   const uint32_t p_full = bars + 8u * (5 + 2 * KV_STAGES);
   const uint32_t pv_full = bars + 8u * (6 + 2 * KV_STAGES);
   const uint32_t pv_empty = bars + 8u * (7 + 2 * KV_STAGES);
-  const uint32_t tmem_slot = bars + 8u * (8 + 2 * KV_STAGES);
+  const uint32_t xch_bar = bars + 8u * (8 + 2 * KV_STAGES);
+  const uint32_t tmem_slot = bars + 8u * (9 + 2 * KV_STAGES);
+  const uint32_t xch = bars + 256;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(
-      smem_aligned + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 8 * (8 + 2 * KV_STAGES));
+      smem_aligned + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 8 * (9 + 2 * KV_STAGES));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -113,11 +123,12 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full(b), 1);
-      mbar_init(s_empty(b), 4);   // lane 0 of each softmax warp
+      mbar_init(s_empty(b), 8);   // lane 0 of each softmax warp
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(pv_full, 1);
-    mbar_init(pv_empty, 4);
+    mbar_init(pv_empty, 8);
+    mbar_init(xch_bar, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -197,31 +208,47 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     }
   } else {
     // ------------------------------------------------------------ softmax + output
+    // Two threads per query row: warps 2-5 take keys 0-63 of every block and output
+    // columns 0-31, warps 6-9 keys 64-127 and columns 32-63 (a warp reaches the TMEM
+    // lanes 32 * (warp % 4) ..., so warps w and w + 4 see the same rows).  The two halves
+    // of a row exchange their partial maxima through shared memory once per block.
     const int lane_group = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = lane_group * 32 + lane;                       // row of the tile = TMEM lane
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
-    const uint32_t p_row = p_smem + r * 128;
+    const uint32_t p_row = p_smem + half * TILE_BYTES + r * 128; // box `half` holds this thread's keys
     const uint32_t swz = static_cast<uint32_t>(r & 7);
-    float o[DH];
+    constexpr int HC = BKV / 2;   // keys per thread and block
+    constexpr int HO = DH / 2;    // output columns per thread
+    float o[HO];
 #pragma unroll
-    for (int i = 0; i < DH; ++i) o[i] = 0.0f;
+    for (int i = 0; i < HO; ++i) o[i] = 0.0f;
     float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
     const float neg_inf = -INFINITY;
     bool ok = true;
+    // partial results of the two halves of a row meet here: xch[parity][half][row]
+    auto xch_addr = [&](int parity, int h) { return xch + static_cast<uint32_t>(((parity * 2 + h) * BQ + r) * 4); };
+    auto exchange = [&](int round, float mine, float &other) -> bool {
+      st_shared_f32(xch_addr(round & 1, half), mine);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xch_bar);
+      bool w = mbar_wait(xch_bar, round & 1);
+      w = __all_sync(0xffffffffu, w);
+      if (!w) return false;
+      other = ld_shared_f32(xch_addr(round & 1, half ^ 1));
+      return true;
+    };
     auto fold_pv = [&](int j, float alpha) -> bool {
-      // O = O * alpha + PV_j
+      // O = O * alpha + PV_j (this thread's 32 columns)
       bool w = mbar_wait(pv_full, j & 1);
       w = __all_sync(0xffffffffu, w);
       if (!w) return false;
       tcgen05_fence_after();
+      uint32_t v[32];
+      tmem_ld_32x32(t_row + PV_COL + half * HO, v);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c0 = 0; c0 < DH; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + PV_COL + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i]));
-      }
+      for (int i = 0; i < HO; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(v[i]));
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pv_empty);
@@ -233,69 +260,63 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       w = __all_sync(0xffffffffu, w);
       if (!w) { ok = false; break; }
       tcgen05_fence_after();
-      const int valid = p.n_ctx - j * BKV;  // keys of this block that exist (>= 128: all)
-      // pass 1: maximum of the scaled scores (in units of log2: s * sm_scale * log2 e)
-      float mx = neg_inf;
-#pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + b * BKV + c0, v);
+      // this thread's 64 scores, read once; the S buffer is free again right away
+      uint32_t sc[HC];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld_32x32(t_row + b * BKV + half * HC, lo);
+        tmem_ld_32x32(t_row + b * BKV + half * HC + 32, hi);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sv = __uint_as_float(v[i]) * p.scale_log2e;
-          mx = fmaxf(mx, (c0 + i < valid) ? sv : neg_inf);
-        }
+        for (int i = 0; i < 32; ++i) { sc[i] = lo[i]; sc[32 + i] = hi[i]; }
       }
-      const float m_new = fmaxf(m, mx);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty(b));
+      const int valid = p.n_ctx - j * BKV - half * HC;  // this thread's keys that exist (>= 64: all)
+      float mx = neg_inf;   // in units of log2: s * sm_scale * log2 e
+#pragma unroll
+      for (int i = 0; i < HC; ++i) mx = fmaxf(mx, (i < valid) ? __uint_as_float(sc[i]) * p.scale_log2e : neg_inf);
+      float other;
+      if (!exchange(j, mx, other)) { ok = false; break; }
+      const float m_new = fmaxf(m, fmaxf(mx, other));
       const float alpha = ex2(m - m_new);  // 0 on the first block (m = -inf)
       // the previous block's P.V: its completion also frees the P buffer
       if (j > 0) {
         if (!fold_pv(j - 1, alpha_prev)) { ok = false; break; }
       }
-      // pass 2: p = 2^(s' - m_new), rounded to 16 bits into the swizzled K-major P tile
+      // p = 2^(s' - m_new), rounded to 16 bits into the swizzled K-major P tile
       float rowsum = 0.0f;
 #pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + b * BKV + c0, v);
-        tmem_ld_wait();
-        float e[32];
+      for (int q = 0; q < HC / 8; ++q) {  // 16-byte chunks of 8 keys
+        float e[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pe = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new));
-          e[i] = (c0 + i < valid) ? pe : 0.0f;
+        for (int i = 0; i < 8; ++i) {
+          const float pe = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, -m_new));
+          e[i] = (8 * q + i < valid) ? pe : 0.0f;
           rowsum += e[i];
         }
-        const uint32_t box = p_row + (c0 >> 6) * TILE_BYTES;  // keys 0-63 | 64-127
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {  // four 16-byte chunks of 8 keys
-          const uint32_t chunk = static_cast<uint32_t>(((c0 & 63) >> 3) + q);
-          st_shared_v4_u32(box + ((chunk ^ swz) << 4), pack2(e[8 * q], e[8 * q + 1], p.is_bf16),
-                           pack2(e[8 * q + 2], e[8 * q + 3], p.is_bf16),
-                           pack2(e[8 * q + 4], e[8 * q + 5], p.is_bf16),
-                           pack2(e[8 * q + 6], e[8 * q + 7], p.is_bf16));
-        }
+        st_shared_v4_u32(p_row + ((static_cast<uint32_t>(q) ^ swz) << 4), pack2(e[0], e[1], p.is_bf16),
+                         pack2(e[2], e[3], p.is_bf16), pack2(e[4], e[5], p.is_bf16),
+                         pack2(e[6], e[7], p.is_bf16));
       }
       l = fmaf(l, alpha, rowsum);
       m = m_new;
       alpha_prev = alpha;
-      tcgen05_fence_before();
       fence_async_smem();  // P (generic-proxy stores) visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty(b));
-        mbar_arrive(p_full);
-      }
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && num_blocks > 0) ok = fold_pv(num_blocks - 1, alpha_prev);
+    float l_other = 0.0f;
+    if (ok) ok = exchange(num_blocks, l, l_other);
     if (!ok) {
       if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
     } else if (q0 + r < p.n_ctx) {
-      const float inv = 1.0f / l;
-      uint16_t *orow = static_cast<uint16_t *>(p.O) + static_cast<size_t>(head_row0 + q0 + r) * DH;
+      const float inv = 1.0f / (l + l_other);
+      uint16_t *orow = static_cast<uint16_t *>(p.O) + static_cast<size_t>(head_row0 + q0 + r) * DH + half * HO;
 #pragma unroll
-      for (int c = 0; c < DH; c += 8) {
+      for (int c = 0; c < HO; c += 8) {
         const uint4 out = make_uint4(pack2(o[c] * inv, o[c + 1] * inv, p.is_bf16),
                                      pack2(o[c + 2] * inv, o[c + 3] * inv, p.is_bf16),
                                      pack2(o[c + 4] * inv, o[c + 5] * inv, p.is_bf16),
