@@ -198,6 +198,8 @@ CASES = {
     "softmax_big": "softmax 65536x1024 (config-2 kernel on a 512 MiB problem, larger than L2)",
     "reduce": "row reduce 32768x8192 (config 4a)",
     "transpose": "transpose 8192x8192 (config 4b)",
+    "attention": "attention forward, 4 heads x 4096 keys x d 64, f16 (the reference test's shape)",
+    "loop_fusion": "fused elementwise chain (log, absf, addf, subf) on 8192x8192 f32",
 }
 
 
@@ -227,6 +229,20 @@ def run_case(name, iters):
         Y = torch.empty_like(X)
         k, ptrs = sess.kernel(B.softmax(name, rows, 1024)), [X.data_ptr(), Y.data_ptr()]
         work, unit = 2 * X.numel() * 4 / 1e9, "GB/s"
+    elif name == "attention":
+        heads, n_ctx = 4, 4096
+        Q, Kt, Vt = [(torch.rand((heads * n_ctx, 64), device=dev) * 2 - 1).to(torch.float16) for _ in range(3)]
+        Ot = torch.empty_like(Q)
+        k = sess.kernel(B.attention_fwd(name, heads, n_ctx, 64, B.F16, 0.5))
+        ptrs = [Q.data_ptr(), Kt.data_ptr(), Vt.data_ptr(), Ot.data_ptr()]
+        work, unit = 4.0 * heads * n_ctx * n_ctx * 64 / 1e12, "TFLOP/s"
+    elif name == "loop_fusion":
+        X = torch.empty((8192, 8192), dtype=torch.float32, device=dev).uniform_(0.5, 4.0)
+        X1 = torch.empty((8192, 8192), dtype=torch.float32, device=dev).uniform_(-2.0, 2.0)
+        Y = torch.empty_like(X)
+        k = sess.kernel(B.expr(name, 8192, 8192, "in0 log in1 abs add in0 sub", B.F32))
+        ptrs = [X.data_ptr(), X1.data_ptr(), Y.data_ptr()]
+        work, unit = 3 * X.numel() * 4 / 1e9, "GB/s"
     elif name == "reduce":
         X = torch.empty((32768, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
         Y = torch.empty(32768, dtype=torch.float32, device=dev)

@@ -12,12 +12,14 @@
 //               K-major) into one of two TMEM S buffers, one block ahead of the softmax;
 //               then PV_j = P_j V_j (M128 N64 K128; P K-major from shared memory, V
 //               MN-major exactly as it lies in its tile) into a third TMEM buffer.
-//   warps 2-9   two threads per query row (64 keys and 32 output columns each): read the
+//   warps 2-    SPLIT (4, or 2) threads per query row, each with its share of the block's keys
+//               and of the output columns: read the
 //               scores of S_j from TMEM once (tcgen05.ld), free the S buffer, exchange the
 //               two partial row maxima through shared memory, keep m and a partial l,
 //               write P_j as 16-bit values into shared memory in the swizzled K-major
-//               layout the MMA expects, and fold PV_{j-1} into 32 f32 output registers
-//               while the tensor core works on S_{j+1} and PV_j.  No shuffles.
+//               layout the MMA expects (two P buffers, two PV buffers in TMEM), then fold
+//               PV_{j-1} into their f32 output registers while the tensor core works on
+//               S_{j+1} and PV_j.  No shuffles.
 // Every wait is bounded; a wait that runs out records a status code, the roles leave
 // their loops, the CTA syncs and frees its TMEM.
 #include "kernels.h"
@@ -27,6 +29,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace imex {
@@ -40,14 +44,16 @@ constexpr int BKV = 128;       // keys per block
 constexpr int DH = 64;         // head dimension
 constexpr int KV_STAGES = 3;  // 144 KB of shared memory: one CTA per SM, which owns all 512 TMEM columns
 constexpr int TILE_BYTES = 128 * DH * 2;        // 16 KB: any of the Q / K / V tiles
-constexpr int P_BYTES = BQ * BKV * 2;           // 32 KB: two 128 x 64-key boxes
-constexpr int NUM_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
-constexpr int TMEM_COLS = 512;                  // S0 [0,128) S1 [128,256) PV [256,320)
+constexpr int P_BYTES = BQ * BKV * 2;           // 32 KB: two 128 x 64-key boxes; two such buffers
+// threads: producer warp, MMA warp, 4 * SPLIT softmax warps (SPLIT threads per query row)
+constexpr int num_threads(int split) { return 64 + 128 * split; }
+constexpr int TMEM_COLS = 512;                  // S0 [0,128) S1 [128,256) PV0 [256,320) PV1 [320,384)
 constexpr int PV_COL = 256;
-constexpr int XCH_BYTES = 2 * 2 * BQ * 4;           // partial row maxima / sums of the two half-rows
-constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 1024 + 256 + XCH_BYTES;
+constexpr int XCH_BYTES = 2 * 4 * BQ * 4;           // partial row maxima / sums of the threads of a row
+constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 1024 + 256 + XCH_BYTES;
 
 struct AttnParams {
+  long long *stats;   // optional cycle counters (nullptr = off), 8 per CTA
   void *O;
   unsigned *status;
   int n_ctx;
@@ -83,7 +89,22 @@ __device__ __forceinline__ void st_shared_v4_u32(uint32_t addr, uint32_t a, uint
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]);
+template <> __device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, uint32_t (&r)[32]) {
+  tmem_ld_32x32(taddr, r);
+}
+template <> __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int SPLIT, bool STATS>
+__global__ void __launch_bounds__(num_threads(SPLIT), 1)
 flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -91,22 +112,22 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   const uint32_t q_smem = smem_base;
   auto k_smem = [&](int s) { return smem_base + TILE_BYTES + s * 2 * TILE_BYTES; };
   auto v_smem = [&](int s) { return k_smem(s) + TILE_BYTES; };
-  const uint32_t p_smem = smem_base + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES;
-  const uint32_t bars = p_smem + P_BYTES;
+  auto p_smem = [&](int b) { return smem_base + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + b * P_BYTES; };
+  const uint32_t bars = p_smem(2);
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + KV_STAGES + s); };
   auto s_full = [&](int b) { return bars + 8u * (1 + 2 * KV_STAGES + b); };
   auto s_empty = [&](int b) { return bars + 8u * (3 + 2 * KV_STAGES + b); };
-  const uint32_t p_full = bars + 8u * (5 + 2 * KV_STAGES);
-  const uint32_t pv_full = bars + 8u * (6 + 2 * KV_STAGES);
-  const uint32_t pv_empty = bars + 8u * (7 + 2 * KV_STAGES);
-  const uint32_t xch_bar = bars + 8u * (8 + 2 * KV_STAGES);
-  const uint32_t tmem_slot = bars + 8u * (9 + 2 * KV_STAGES);
+  auto p_full = [&](int b) { return bars + 8u * (5 + 2 * KV_STAGES + b); };
+  auto pv_full = [&](int b) { return bars + 8u * (7 + 2 * KV_STAGES + b); };
+  auto pv_empty = [&](int b) { return bars + 8u * (9 + 2 * KV_STAGES + b); };
+  const uint32_t xch_bar = bars + 8u * (11 + 2 * KV_STAGES);
+  const uint32_t tmem_slot = bars + 8u * (12 + 2 * KV_STAGES);
   const uint32_t xch = bars + 256;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(
-      smem_aligned + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 8 * (9 + 2 * KV_STAGES));
+      smem_aligned + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 8 * (12 + 2 * KV_STAGES));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -123,12 +144,12 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full(b), 1);
-      mbar_init(s_empty(b), 8);   // lane 0 of each softmax warp
+      mbar_init(s_empty(b), 4 * SPLIT);   // lane 0 of each softmax warp
+      mbar_init(p_full(b), 4 * SPLIT);
+      mbar_init(pv_full(b), 1);
+      mbar_init(pv_empty(b), 4 * SPLIT);
     }
-    mbar_init(p_full, 8);
-    mbar_init(pv_full, 1);
-    mbar_init(pv_empty, 8);
-    mbar_init(xch_bar, 8);
+    mbar_init(xch_bar, 4 * SPLIT);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -171,12 +192,17 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      long long w_kv = 0, w_se = 0, w_pf = 0, w_pe = 0;
+      const long long t_begin = STATS ? clock64() : 0;
       bool ok = mbar_wait(q_full, 0);
       if (!ok) report(p.status, kStatusMmaWaitTimeout);
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES, b = j & 1;
+        long long t0 = STATS ? clock64() : 0;
         if (!mbar_wait(kv_full(s), (j / KV_STAGES) & 1)) return false;
+        if (STATS) { const long long t1 = clock64(); w_kv += t1 - t0; t0 = t1; }
         if (!mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1u)) return false;
+        if (STATS) w_se += clock64() - t0;
         tcgen05_fence_after();
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
@@ -186,16 +212,19 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         return true;
       };
       auto issue_pv = [&](int j) -> bool {
-        const int s = j % KV_STAGES;
-        if (!mbar_wait(p_full, j & 1)) return false;
-        if (!mbar_wait(pv_empty, (j & 1) ^ 1u)) return false;
+        const int s = j % KV_STAGES, b = j & 1;
+        long long t0 = STATS ? clock64() : 0;
+        if (!mbar_wait(p_full(b), (j >> 1) & 1)) return false;
+        if (STATS) { const long long t1 = clock64(); w_pf += t1 - t0; t0 = t1; }
+        if (!mbar_wait(pv_empty(b), ((j >> 1) & 1) ^ 1u)) return false;
+        if (STATS) w_pe += clock64() - t0;
         tcgen05_fence_after();
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
-          tcgen05_mma_f16(tmem_base + PV_COL,
-                          make_smem_desc(p_smem + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
+          tcgen05_mma_f16(tmem_base + PV_COL + b * DH,
+                          make_smem_desc(p_smem(b) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
                           make_smem_desc(v_smem(s) + k * 2048, TILE_BYTES, 1024), p.idesc_pv, k ? 1u : 0u);
-        tcgen05_commit(pv_full);      // PV_j is complete: P and this K/V stage are free again
+        tcgen05_commit(pv_full(b));   // PV_j is complete: P buffer b and this K/V stage are free again
         tcgen05_commit(kv_empty(s));
         return true;
       };
@@ -205,116 +234,162 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         if (ok) ok = issue_pv(j);
       }
       if (!ok) report(p.status, kStatusMmaWaitTimeout);
+      if (STATS && p.stats) {
+        long long *st = p.stats + 8 * (blockIdx.y * gridDim.x + blockIdx.x);
+        st[0] = clock64() - t_begin;  // MMA thread, total
+        st[1] = w_kv;                 // ... waiting for K/V tiles
+        st[2] = w_se;                 // ... for a free S buffer
+        st[3] = w_pf;                 // ... for P
+        st[4] = w_pe;                 // ... for a free PV buffer
+      }
     }
   } else {
     // ------------------------------------------------------------ softmax + output
-    // Two threads per query row: warps 2-5 take keys 0-63 of every block and output
-    // columns 0-31, warps 6-9 keys 64-127 and columns 32-63 (a warp reaches the TMEM
-    // lanes 32 * (warp % 4) ..., so warps w and w + 4 see the same rows).  The two halves
-    // of a row exchange their partial maxima through shared memory once per block.
+    // SPLIT threads per query row: warp w takes the TMEM lanes 32 * (w % 4) ... (a warp can
+    // reach no others), so warps w, w + 4, ... see the same rows; part = (w - 2) / 4 takes
+    // keys [part * 128 / SPLIT, ...) of every block and the same share of the output
+    // columns.  The parts of a row exchange their partial maxima through shared memory
+    // once per block.
     const int lane_group = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int r = lane_group * 32 + lane;                       // row of the tile = TMEM lane
+    constexpr int HC = BKV / SPLIT;   // keys per thread and block
+    constexpr int HO = DH / SPLIT;    // output columns per thread
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
-    const uint32_t p_row = p_smem + half * TILE_BYTES + r * 128; // box `half` holds this thread's keys
+    // this thread's keys lie in box (part * HC) / 64 of P, from 16-byte chunk ((part * HC) % 64) / 8 on
+    const uint32_t p_row_off = ((part * HC) >> 6) * TILE_BYTES + r * 128;
+    const uint32_t chunk0 = static_cast<uint32_t>(((part * HC) & 63) >> 3);
     const uint32_t swz = static_cast<uint32_t>(r & 7);
-    constexpr int HC = BKV / 2;   // keys per thread and block
-    constexpr int HO = DH / 2;    // output columns per thread
     float o[HO];
 #pragma unroll
     for (int i = 0; i < HO; ++i) o[i] = 0.0f;
     float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
     const float neg_inf = -INFINITY;
     bool ok = true;
-    // partial results of the two halves of a row meet here: xch[parity][half][row]
-    auto xch_addr = [&](int parity, int h) { return xch + static_cast<uint32_t>(((parity * 2 + h) * BQ + r) * 4); };
-    auto exchange = [&](int round, float mine, float &other) -> bool {
-      st_shared_f32(xch_addr(round & 1, half), mine);
+    // partial results of the threads of a row meet here: xch[parity][part][row]
+    auto xch_addr = [&](int parity, int h) { return xch + static_cast<uint32_t>(((parity * 4 + h) * BQ + r) * 4); };
+    // every thread of the row gets max (is_max) or sum of all parts' values
+    auto exchange = [&](int round, float mine, bool is_max, float &all) -> bool {
+      st_shared_f32(xch_addr(round & 1, part), mine);
       __syncwarp();
       if (lane == 0) mbar_arrive(xch_bar);
       bool w = mbar_wait(xch_bar, round & 1);
       w = __all_sync(0xffffffffu, w);
       if (!w) return false;
-      other = ld_shared_f32(xch_addr(round & 1, half ^ 1));
+      all = mine;
+#pragma unroll
+      for (int h = 1; h < SPLIT; ++h) {
+        const float other = ld_shared_f32(xch_addr(round & 1, (part + h) % SPLIT));
+        all = is_max ? fmaxf(all, other) : all + other;
+      }
       return true;
     };
     auto fold_pv = [&](int j, float alpha) -> bool {
-      // O = O * alpha + PV_j (this thread's 32 columns)
-      bool w = mbar_wait(pv_full, j & 1);
+      // O = O * alpha + PV_j (this thread's columns)
+      bool w = mbar_wait(pv_full(j & 1), (j >> 1) & 1);
       w = __all_sync(0xffffffffu, w);
       if (!w) return false;
       tcgen05_fence_after();
-      uint32_t v[32];
-      tmem_ld_32x32(t_row + PV_COL + half * HO, v);
+      uint32_t v[HO];
+      tmem_ld_cols<HO>(t_row + PV_COL + (j & 1) * DH + part * HO, v);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < HO; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(v[i]));
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pv_empty);
+      if (lane == 0) mbar_arrive(pv_empty(j & 1));
       return true;
     };
+    long long w_sf = 0;
+    const long long t_begin = STATS ? clock64() : 0;
     for (int j = 0; j < num_blocks; ++j) {
       const int b = j & 1;
+      const long long t0 = STATS ? clock64() : 0;
       bool w = mbar_wait(s_full(b), (j >> 1) & 1);
+      if (STATS) w_sf += clock64() - t0;
       w = __all_sync(0xffffffffu, w);
       if (!w) { ok = false; break; }
       tcgen05_fence_after();
-      // this thread's 64 scores, read once; the S buffer is free again right away
+      // this thread's scores, read once; the S buffer is free again right away
       uint32_t sc[HC];
-      {
+      if constexpr (HC == 64) {
         uint32_t lo[32], hi[32];
-        tmem_ld_32x32(t_row + b * BKV + half * HC, lo);
-        tmem_ld_32x32(t_row + b * BKV + half * HC + 32, hi);
+        tmem_ld_32x32(t_row + b * BKV + part * HC, lo);
+        tmem_ld_32x32(t_row + b * BKV + part * HC + 32, hi);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) { sc[i] = lo[i]; sc[32 + i] = hi[i]; }
+      } else {
+        tmem_ld_cols<HC>(t_row + b * BKV + part * HC, sc);
+        tmem_ld_wait();
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty(b));
-      const int valid = p.n_ctx - j * BKV - half * HC;  // this thread's keys that exist (>= 64: all)
+      const int valid = p.n_ctx - j * BKV - part * HC;  // this thread's keys that exist (>= HC: all)
+      // all keys present and a positive scale (every block but a ragged last one): the
+      // maximum is taken on the raw scores and scaled once, nothing is masked
+      const bool plain = valid >= HC && p.scale_log2e > 0.0f;
       float mx = neg_inf;   // in units of log2: s * sm_scale * log2 e
+      if (plain) {
 #pragma unroll
-      for (int i = 0; i < HC; ++i) mx = fmaxf(mx, (i < valid) ? __uint_as_float(sc[i]) * p.scale_log2e : neg_inf);
-      float other;
-      if (!exchange(j, mx, other)) { ok = false; break; }
-      const float m_new = fmaxf(m, fmaxf(mx, other));
-      const float alpha = ex2(m - m_new);  // 0 on the first block (m = -inf)
-      // the previous block's P.V: its completion also frees the P buffer
-      if (j > 0) {
-        if (!fold_pv(j - 1, alpha_prev)) { ok = false; break; }
+        for (int i = 0; i < HC; ++i) mx = fmaxf(mx, __uint_as_float(sc[i]));
+        mx *= p.scale_log2e;
+      } else {
+#pragma unroll
+        for (int i = 0; i < HC; ++i) mx = fmaxf(mx, (i < valid) ? __uint_as_float(sc[i]) * p.scale_log2e : neg_inf);
       }
-      // p = 2^(s' - m_new), rounded to 16 bits into the swizzled K-major P tile
+      float row_max;
+      if (!exchange(j, mx, true, row_max)) { ok = false; break; }
+      const float m_new = fmaxf(m, row_max);
+      const float alpha = ex2(m - m_new);  // 0 on the first block (m = -inf)
+      // p = 2^(s' - m_new), rounded to 16 bits into the swizzled K-major P tile; buffer b was
+      // last read by PV_{j-2}, whose completion this thread saw when it folded it in
+      const uint32_t p_row = p_smem(b) + p_row_off;
       float rowsum = 0.0f;
+      const float neg_m = -m_new;
 #pragma unroll
       for (int q = 0; q < HC / 8; ++q) {  // 16-byte chunks of 8 keys
         float e[8];
+        if (plain) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float pe = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, -m_new));
-          e[i] = (8 * q + i < valid) ? pe : 0.0f;
-          rowsum += e[i];
+          for (int i = 0; i < 8; ++i) e[i] = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, neg_m));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float pe = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, neg_m));
+            e[i] = (8 * q + i < valid) ? pe : 0.0f;
+          }
         }
-        st_shared_v4_u32(p_row + ((static_cast<uint32_t>(q) ^ swz) << 4), pack2(e[0], e[1], p.is_bf16),
+        rowsum += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+        st_shared_v4_u32(p_row + (((chunk0 + static_cast<uint32_t>(q)) ^ swz) << 4), pack2(e[0], e[1], p.is_bf16),
                          pack2(e[2], e[3], p.is_bf16), pack2(e[4], e[5], p.is_bf16),
                          pack2(e[6], e[7], p.is_bf16));
       }
-      l = fmaf(l, alpha, rowsum);
-      m = m_new;
-      alpha_prev = alpha;
       fence_async_smem();  // P (generic-proxy stores) visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full(b));
+      l = fmaf(l, alpha, rowsum);
+      m = m_new;
+      // the previous block's P.V, off the path that feeds the tensor core
+      if (j > 0) {
+        if (!fold_pv(j - 1, alpha_prev)) { ok = false; break; }
+      }
+      alpha_prev = alpha;
+    }
+    if (STATS && p.stats && warp == 2 && lane == 0) {
+      long long *st = p.stats + 8 * (blockIdx.y * gridDim.x + blockIdx.x);
+      st[5] = clock64() - t_begin;  // a softmax thread, all blocks
+      st[6] = w_sf;                 // ... waiting for S
     }
     if (ok && num_blocks > 0) ok = fold_pv(num_blocks - 1, alpha_prev);
-    float l_other = 0.0f;
-    if (ok) ok = exchange(num_blocks, l, l_other);
+    float l_row = 0.0f;
+    if (ok) ok = exchange(num_blocks, l, false, l_row);
     if (!ok) {
       if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
     } else if (q0 + r < p.n_ctx) {
-      const float inv = 1.0f / (l + l_other);
-      uint16_t *orow = static_cast<uint16_t *>(p.O) + static_cast<size_t>(head_row0 + q0 + r) * DH + half * HO;
+      const float inv = 1.0f / l_row;
+      uint16_t *orow = static_cast<uint16_t *>(p.O) + static_cast<size_t>(head_row0 + q0 + r) * DH + part * HO;
 #pragma unroll
       for (int c = 0; c < HO; c += 8) {
         const uint4 out = make_uint4(pack2(o[c] * inv, o[c + 1] * inv, p.is_bf16),
@@ -353,9 +428,18 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
   if (!flash_attention_supported(heads, n_ctx, d_head, dtype, q, k, v, o)) return cudaErrorNotSupported;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
+  static int split = 4;  // threads per query row (IMEX_ATTN_SPLIT=2 for the two-thread form)
+  static bool with_stats = false;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(flash_attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
+    if (const char *e = getenv("IMEX_ATTN_SPLIT")) split = atoi(e) == 2 ? 2 : 4;
+    with_stats = getenv("IMEX_ATTN_STATS") != nullptr;  // development aid: where the roles wait
+    cudaError_t e2 = cudaFuncSetAttribute(flash_attention_fwd_kernel<2, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e4 = cudaFuncSetAttribute(flash_attention_fwd_kernel<4, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e5 = cudaFuncSetAttribute(flash_attention_fwd_kernel<4, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    attr_err = e2 != cudaSuccess ? e2 : e4 != cudaSuccess ? e4 : e5;
   });
   if (attr_err != cudaSuccess) return attr_err;
   const int64_t rows = heads * n_ctx;
@@ -377,7 +461,30 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
   p.idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(DH >> 3) << 17) |
                (static_cast<uint32_t>(BQ >> 4) << 24);
   const dim3 grid(static_cast<unsigned>((n_ctx + BQ - 1) / BQ), static_cast<unsigned>(heads));
-  flash_attention_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  p.stats = nullptr;
+  static long long *stats_buf = nullptr;
+  const int ctas = static_cast<int>(grid.x * grid.y);
+  if (with_stats && ctas <= 4096) {
+    if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 4096 * sizeof(long long));
+    p.stats = stats_buf;
+  }
+  if (p.stats)
+    flash_attention_fwd_kernel<4, true><<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  else if (split == 2)
+    flash_attention_fwd_kernel<2, false><<<grid, num_threads(2), SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  else
+    flash_attention_fwd_kernel<4, false><<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  if (p.stats) {
+    cudaStreamSynchronize(stream);
+    double a[8] = {0};
+    for (int c = 0; c < ctas; ++c)
+      for (int i = 0; i < 8; ++i) a[i] += static_cast<double>(stats_buf[8 * c + i]);
+    fprintf(stderr,
+            "[attention stats, mean cycles per CTA, %d key blocks] mma total %.0f wait_kv %.0f wait_s_free %.0f "
+            "wait_p %.0f wait_pv_free %.0f | softmax total %.0f wait_s %.0f\n",
+            static_cast<int>((n_ctx + BKV - 1) / BKV), a[0] / ctas, a[1] / ctas, a[2] / ctas, a[3] / ctas,
+            a[4] / ctas, a[5] / ctas, a[6] / ctas);
+  }
   return cudaGetLastError();
 }
 
