@@ -462,7 +462,10 @@ def main():
             e2e_step()
         barrier()
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
-        assert torch.equal(hC[:4], Cm[:4].cpu()), "e2e result differs from the resident run"
+        # same products, but the two runs cut the work into different launches, and a k-split tile
+        # sums its parts in another order than a whole one: equal to the last bits, not bit for bit
+        assert torch.allclose(hC[:64], Cm[:64].cpu(), rtol=1e-4, atol=1e-6), \
+            "e2e result differs from the resident run"
         e2e = {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": int(hA.numel() * 2 + hB.numel() * 2),
                "d2h_bytes_per_step": int(hC.numel() * 4), "ms_per_step": e2e_ms,
