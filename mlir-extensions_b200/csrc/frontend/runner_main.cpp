@@ -372,9 +372,21 @@ private:
     int sp = 0, maxsp = 0;
     return emit(tree, p, sp, maxsp);
   }
-  static void shape2d(const Type &t, int64_t &rows, int64_t &cols) {
-    cols = t.shape.empty() ? 1 : t.shape.back();
-    rows = cols ? t.count() / cols : 0;
+  static bool hasVectorLeaf(const XNodeP &n) {
+    if (!n) return false;
+    if (n->kind == XNode::Leaf) return n->mode != 0;
+    return hasVectorLeaf(n->a) || hasVectorLeaf(n->b);
+  }
+  // Rows x columns the kernel walks: the tensor's own last dimension when a row or column
+  // vector is broadcast along it, otherwise one long row (any rank, best vector width).
+  static void shape2d(const Type &t, const XNodeP &tree, int64_t &rows, int64_t &cols) {
+    if (hasVectorLeaf(tree)) {
+      cols = t.shape.empty() ? 1 : t.shape.back();
+      rows = cols ? t.count() / cols : 0;
+    } else {
+      rows = 1;
+      cols = t.count();
+    }
   }
   ImexKernelDesc exprDesc(const ExprProgram &p, const Type &in, uint32_t outDtype, int64_t rows, int64_t cols) {
     ImexKernelDesc d = desc(IMEX_OP_EXPR, dtypeCode(in.elt), outDtype);
@@ -398,7 +410,7 @@ private:
     if (!compile(v.lazy, p)) die("internal: an elementwise chain outgrew the fused kernel");
     Value out = makeTensor(curStream, v.type);
     int64_t rows, cols;
-    shape2d(v.type, rows, cols);
+    shape2d(v.type, v.lazy, rows, cols);
     std::vector<void *> ptrs;
     for (auto &b : p.inputs) ptrs.push_back(b->ptr);
     ptrs.push_back(out.buf->ptr);
@@ -833,8 +845,13 @@ private:
     }
     case Kind::Relu:
     case Kind::Sigmoid: {
+      if (peek(fr, op.ins[0], op).type.elt != "f32" || peek(fr, op.ins[0], op).lazy) {
+        // f16 / bf16 (the benchmark grid's other dtypes) or part of an open chain: the fused
+        // elementwise kernel, which rounds every operation to the element type
+        elementwiseOp(op, b, fr, where);
+        break;
+      }
       Value &X = get(fr, op.ins[0], op);
-      if (X.type.elt != "f32") die(where + "elementwise ops are f32 only");
       uint32_t epi = IMEX_EPI_RELU;
       std::string finalRes = res;
       if (c.kind == Kind::Sigmoid) {
@@ -911,7 +928,7 @@ private:
     case Kind::ReduceLeading:
     case Kind::ReduceAll: {
       Value &maybeOpen = peek(fr, op.ins[0], op);
-      if (c.kind == Kind::ReduceLeading && maybeOpen.type.shape.size() == 2 &&
+      if (c.kind == Kind::ReduceLeading && maybeOpen.type.shape.size() >= 2 &&
           (maybeOpen.lazy || maybeOpen.type.elt != "f32")) {
         // an elementwise chain feeding the column sum (kInputFusion.mlir.in:6-41), or a
         // 16-bit input: one pass, every add rounded to the element type
@@ -922,7 +939,7 @@ private:
         if (!compile(tree, p)) die("internal: an elementwise chain outgrew the fused kernel");
         Value out = makeTensor(stream, outT);
         ImexKernelDesc d = exprDesc(p, maybeOpen.type, dtypeCode(outT.elt), maybeOpen.type.shape[0],
-                                    maybeOpen.type.shape[1]);
+                                    maybeOpen.type.count() / maybeOpen.type.shape[0]);
         d.flags |= IMEX_FLAG_REDUCE_LEADING;
         if (!(init.isFill && init.fillValue == 0.0)) {
           d.flags |= IMEX_FLAG_ACCUMULATE;

@@ -167,9 +167,17 @@ def test_f16_multiply_add_is_not_sent_to_the_tensor_cores():
      ["transpose2d dims=[1024,512"]),
     ("transpose/transpose3d_gpu", None, None),
     ("reduce/reduce_gpu", {}, ["reduce_leading dims=[32,4194304"]),
+    # the grid's 16-bit dtypes go through the fused elementwise kernel (per-operation rounding)
+    ("reduce/reduce_gpu", {"dtype": "bf16"}, ["expr[1 ops, 1 inputs] bf16 +reduce_leading dims=[32,4194304"]),
+    ("relu/relu_gpu", {"shape": "50x640x20x15", "affine_map": "d0, d1, d2, d3", "dtype": "f16",
+                       "iterator_types": '"parallel", "parallel", "parallel", "parallel"'},
+     ["expr[2 ops, 1 inputs] f16 dims=[1,9600000"]),
+    ("silu/silu_gpu", {"shape": "1x16x56x56", "affine_map": "d0, d1, d2, d3", "dtype": "bf16",
+                       "iterator_types": '"parallel", "parallel", "parallel", "parallel"'},
+     ["expr[9 ops, 1 inputs] bf16 dims=[1,50176"]),
     # four generics (log, absf, addf, subf) -> one launch; with the column reduce behind: still one
-    ("kLoopFusion/kLoopFusion", {}, ["expr[7 ops, 2 inputs] f32 dims=[512,1024"]),
-    ("kLoopFusion/kLoopFusion", {"dtype": "f16"}, ["expr[7 ops, 2 inputs] f16 dims=[512,1024"]),
+    ("kLoopFusion/kLoopFusion", {}, ["expr[7 ops, 2 inputs] f32 dims=[1,524288"]),  # walked as one long row
+    ("kLoopFusion/kLoopFusion", {"dtype": "f16"}, ["expr[7 ops, 2 inputs] f16 dims=[1,524288"]),
     ("kInputFusion/kInputFusion", {}, ["expr[5 ops, 2 inputs] f32 +reduce_leading dims=[512,1024"]),
     ("kInputFusion/kInputFusion", {"dtype": "bf16"}, ["expr[5 ops, 2 inputs] bf16 +reduce_leading dims=[512,1024"]),
 ])
