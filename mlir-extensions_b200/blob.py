@@ -118,8 +118,9 @@ def attention_fwd(name, heads, n_ctx, d_head=64, dtype=F16, sm_scale=0.5):
                       fparams=(sm_scale, 0.0))
 
 
-def softmax(name, rows, cols, neg_inf_init=False):
-    return KernelDesc(name, OP_SOFTMAX, F32, F32, 0, FLAG_SOFTMAX_NEG_INF if neg_inf_init else 0,
+def softmax(name, rows, cols, neg_inf_init=False, dtype=F32):
+    """dtype F16 / BF16: every operation of the chain rounds to the element type."""
+    return KernelDesc(name, OP_SOFTMAX, dtype, dtype, 0, FLAG_SOFTMAX_NEG_INF if neg_inf_init else 0,
                       (rows, cols))
 
 

@@ -895,7 +895,8 @@ private:
       if (!init.isFill) die(where + "softmax row max must start from a filled tensor");
       const bool negInf = std::isinf(init.fillValue) && init.fillValue < 0;
       if (!negInf && !(init.fillValue <= -3.4e38)) die(where + "softmax row max must start from -inf or -FLT_MAX");
-      if (X.type.elt != "f32" || X.type.shape.size() != 2) die(where + "softmax is f32, rank 2 only");
+      if ((X.type.elt != "f32" && X.type.elt != "f16" && X.type.elt != "bf16") || X.type.shape.size() != 2)
+        die(where + "softmax is f32 / f16 / bf16, rank 2 only");
       // The chain runs as one kernel when its LAST op (the divide) is reached: the row
       // sum's initial tensor may be defined between here and there.
       for (const Op *o : {sub, ex, sum}) absorbed.insert(o);
@@ -916,11 +917,11 @@ private:
       Value &sumInit = get(fr, plan.sum->outs[0], *plan.sum);
       if (!(sumInit.isFill && sumInit.fillValue == 0.0)) die(where + "softmax row sum must start from 0");
       Value out = makeTensor(stream, outT);
-      ImexKernelDesc d = desc(IMEX_OP_SOFTMAX, IMEX_F32, IMEX_F32);
+      ImexKernelDesc d = desc(IMEX_OP_SOFTMAX, dtypeCode(X.type.elt), dtypeCode(X.type.elt));
       if (plan.negInf) d.flags |= IMEX_FLAG_SOFTMAX_NEG_INF;
       d.dims[0] = X.type.shape[0];
       d.dims[1] = X.type.shape[1];
-      launch(stream, d, {X.buf->ptr, out.buf->ptr}, "softmax");
+      launch(stream, d, {X.buf->ptr, out.buf->ptr}, X.type.elt == "f32" ? "softmax" : "softmax " + X.type.elt);
       fr.vals[res] = out;
       break;
     }
@@ -989,15 +990,15 @@ private:
         d.dims[0] = sh[0];
         d.dims[1] = sh[1];
         launch(stream, d, {X.buf->ptr, out.buf->ptr}, "transpose2d");
-      } else if (sh.size() == 3 && eb == 4) {
-        ImexKernelDesc d = desc(IMEX_OP_TRANSPOSE3D, IMEX_F32, IMEX_F32);
+      } else if (sh.size() == 3 && (eb == 4 || eb == 2)) {
+        ImexKernelDesc d = desc(IMEX_OP_TRANSPOSE3D, eb == 4 ? IMEX_F32 : IMEX_BF16, eb == 4 ? IMEX_F32 : IMEX_BF16);
         for (int i = 0; i < 3; ++i) {
           d.dims[i] = sh[i];
           d.dims[3 + i] = c.perm[i];
         }
         launch(stream, d, {X.buf->ptr, out.buf->ptr}, "transpose3d");
       } else {
-        die(where + "only rank-2 and rank-3 (4-byte) permutations have kernels");
+        die(where + "only rank-2 and rank-3 permutations of 2- and 4-byte elements have kernels");
       }
       fr.vals[res] = out;
       break;

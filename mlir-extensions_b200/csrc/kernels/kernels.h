@@ -77,6 +77,11 @@ cudaError_t launch_wait_selftest(unsigned *status, cudaStream_t stream);
 cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols,
                                bool neg_inf_init, cudaStream_t stream);
 
+// The same chain on f16 / bf16 rows: every operation rounds to the element type and the row
+// sum is the sequential chain of rounded adds that the loop nest performs.  cols <= 12288.
+cudaError_t launch_softmax_x16(const void *x, void *y, int64_t rows, int64_t cols, bool neg_inf_init,
+                               bool is_bf16, cudaStream_t stream);
+
 // Y[r] = (acc ? Y[r] : 0) + sum_c X[r,c]
 cudaError_t launch_reduce_rows_f32(const float *x, float *y, int64_t rows, int64_t cols,
                                    bool accumulate, cudaStream_t stream);
@@ -92,9 +97,9 @@ cudaError_t launch_reduce_all_f32(const float *x, float *y, int64_t n, bool accu
 // Y[j,i] = X[i,j]; elem_bytes 4 or 2.
 cudaError_t launch_transpose2d(const void *x, void *y, int64_t rows, int64_t cols,
                                int elem_bytes, cudaStream_t stream);
-// rank-3 permutation of 4-byte elements: Y dims = X dims permuted by perm.
-cudaError_t launch_transpose3d_b32(const void *x, void *y, const int64_t dims[3],
-                                   const int perm[3], cudaStream_t stream);
+// rank-3 permutation of 4- or 2-byte elements: Y dims = X dims permuted by perm.
+cudaError_t launch_transpose3d(const void *x, void *y, const int64_t dims[3], const int perm[3],
+                               int elem_bytes, cudaStream_t stream);
 
 // Y[i] = epilogue(X[i]) (standalone relu / silu)
 cudaError_t launch_eltwise_f32(const float *x, float *y, int64_t n, int epilogue,

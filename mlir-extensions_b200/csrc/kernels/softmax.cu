@@ -12,6 +12,9 @@
 // `sum` differs from the sequential loop (per-lane partial sums + shuffle
 // tree), which is where the <= 1e-5 relative tolerance goes.
 #include "kernels.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cfloat>
 
 namespace imex {
@@ -178,7 +181,75 @@ cudaError_t launch_warp(const float *x, float *y, int64_t rows, int cols, float 
   return cudaGetLastError();
 }
 
+// 16-bit rows (the f16 / bf16 rows of the reference's benchmark grid,
+// benchmarks/softmax/softmax.dtypes.in): the chain's generics run in the element type, so
+// every operation rounds to it, and the row sum is a sequential chain of rounded adds whose
+// order decides the result.  One block per row: the row is staged in shared memory as f32,
+// max / subtract / exp / divide run on all threads, the sum on one thread in index order.
+template <bool BF16>
+__device__ __forceinline__ float round16(float v) {
+  if (BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return __half2float(__float2half_rn(v));
+}
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+softmax_rows_x16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ y, int64_t rows,
+                        int cols, float max_init) {
+  extern __shared__ float row[];
+  __shared__ float red[8];
+  __shared__ float total;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint16_t *xr = x + r * cols;
+    float mx = max_init;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float v = BF16 ? __uint_as_float(static_cast<uint32_t>(xr[i]) << 16)
+                           : __half2float(__ushort_as_half(xr[i]));
+      row[i] = v;
+      mx = fmaxf(mx, v);
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+    for (int i = threadIdx.x; i < cols; i += blockDim.x)
+      row[i] = round16<BF16>(expf(round16<BF16>(__fsub_rn(row[i], mx))));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float sum = 0.0f;
+      for (int i = 0; i < cols; ++i) sum = round16<BF16>(__fadd_rn(row[i], sum));
+      total = sum;
+    }
+    __syncthreads();
+    const float sum = total;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float q = __fdiv_rn(row[i], sum);
+      y[r * cols + i] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(q)) : __half_as_ushort(__float2half_rn(q));
+    }
+    __syncthreads();
+  }
+}
+
 } // namespace
+
+cudaError_t launch_softmax_x16(const void *x, void *y, int64_t rows, int64_t cols, bool neg_inf_init,
+                               bool is_bf16, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  if (cols > 12288) return cudaErrorNotSupported;  // the row is staged in 48 KB of shared memory
+  // -FLT_MAX is not a 16-bit value: the fill of the IR holds it rounded to the element type
+  const float max_init = neg_inf_init ? -INFINITY : (is_bf16 ? -3.3895313892515355e38f : -INFINITY);
+  const unsigned grid = static_cast<unsigned>(rows < 148 * 8 ? rows : 148 * 8);
+  const size_t smem = static_cast<size_t>(cols) * sizeof(float);
+  if (is_bf16)
+    softmax_rows_x16_kernel<true><<<grid, 256, smem, stream>>>(static_cast<const uint16_t *>(x),
+                                                               static_cast<uint16_t *>(y), rows,
+                                                               static_cast<int>(cols), max_init);
+  else
+    softmax_rows_x16_kernel<false><<<grid, 256, smem, stream>>>(static_cast<const uint16_t *>(x),
+                                                                static_cast<uint16_t *>(y), rows,
+                                                                static_cast<int>(cols), max_init);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols,
                                bool neg_inf_init, cudaStream_t stream) {

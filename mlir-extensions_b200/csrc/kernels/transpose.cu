@@ -78,8 +78,9 @@ transpose2d_generic_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t r
 }
 
 // Generic rank-3 permutation: one thread per OUTPUT element (coalesced writes).
+template <typename T>
 __global__ void __launch_bounds__(256)
-transpose3d_gather_kernel(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, int64_t d0,
+transpose3d_gather_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t d0,
                           int64_t d1, int64_t d2, int p0, int p1, int p2) {
   const int64_t dims[3] = {d0, d1, d2};
   const int64_t o1 = dims[p1], o2 = dims[p2];
@@ -119,24 +120,32 @@ cudaError_t launch_transpose2d(const void *x, void *y, int64_t rows, int64_t col
   return cudaGetLastError();
 }
 
-cudaError_t launch_transpose3d_b32(const void *x, void *y, const int64_t dims[3],
-                                   const int perm[3], cudaStream_t stream) {
+namespace {
+template <typename T>
+cudaError_t transpose3d_typed(const void *x, void *y, const int64_t dims[3], const int perm[3],
+                              cudaStream_t stream) {
   const int64_t total = dims[0] * dims[1] * dims[2];
-  if (total <= 0) return cudaSuccess;
   if (perm[0] == 0 && perm[1] == 2 && perm[2] == 1) {  // batched 2-D transpose
     int64_t tr = (dims[1] + 31) / 32, tc = (dims[2] + 31) / 32;
-    transpose2d_generic_kernel<uint32_t>
-        <<<static_cast<unsigned>(dims[0] * tr * tc), 256, 0, stream>>>(
-            static_cast<const uint32_t *>(x), static_cast<uint32_t *>(y), dims[1], dims[2], tc,
-            tr * tc);
+    transpose2d_generic_kernel<T><<<static_cast<unsigned>(dims[0] * tr * tc), 256, 0, stream>>>(
+        static_cast<const T *>(x), static_cast<T *>(y), dims[1], dims[2], tc, tr * tc);
     return cudaGetLastError();
   }
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 64) blocks = 148 * 64;
-  transpose3d_gather_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-      static_cast<const uint32_t *>(x), static_cast<uint32_t *>(y), dims[0], dims[1], dims[2],
-      perm[0], perm[1], perm[2]);
+  transpose3d_gather_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const T *>(x), static_cast<T *>(y), dims[0], dims[1], dims[2], perm[0], perm[1],
+      perm[2]);
   return cudaGetLastError();
+}
+} // namespace
+
+cudaError_t launch_transpose3d(const void *x, void *y, const int64_t dims[3], const int perm[3],
+                               int elem_bytes, cudaStream_t stream) {
+  if (dims[0] * dims[1] * dims[2] <= 0) return cudaSuccess;
+  if (elem_bytes == 4) return transpose3d_typed<uint32_t>(x, y, dims, perm, stream);
+  if (elem_bytes == 2) return transpose3d_typed<uint16_t>(x, y, dims, perm, stream);
+  return cudaErrorInvalidValue;
 }
 
 } // namespace imex

@@ -313,7 +313,16 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
   }
   case IMEX_OP_SOFTMAX:
     need(2);
-    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: softmax is f32 only");
+    if (d.in_dtype != d.out_dtype) throw std::runtime_error("gpuLaunchKernel: softmax keeps its element type");
+    if (d.in_dtype == IMEX_F16 || d.in_dtype == IMEX_BF16) {
+      s->last_kernel = "softmax_x16";
+      err = imex::launch_softmax_x16(ptrs[0], ptrs[1], d.dims[0], d.dims[1], d.flags & IMEX_FLAG_SOFTMAX_NEG_INF,
+                                     d.in_dtype == IMEX_BF16, s->stream);
+      if (err == cudaErrorNotSupported)
+        throw std::runtime_error("gpuLaunchKernel: 16-bit softmax rows hold at most 12288 values");
+      break;
+    }
+    if (d.in_dtype != IMEX_F32) throw std::runtime_error("gpuLaunchKernel: softmax is f32, f16 or bf16");
     s->last_kernel = "softmax";
     err = imex::launch_softmax_f32(static_cast<const float *>(ptrs[0]), static_cast<float *>(ptrs[1]),
                                    d.dims[0], d.dims[1], d.flags & IMEX_FLAG_SOFTMAX_NEG_INF,
@@ -354,8 +363,7 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     break;
   case IMEX_OP_TRANSPOSE3D: {
     need(2);
-    if (dtype_bytes(d.in_dtype) != 4)
-      throw std::runtime_error("gpuLaunchKernel: transpose3d takes 4-byte elements");
+    if (d.in_dtype != d.out_dtype) throw std::runtime_error("gpuLaunchKernel: a transpose keeps its element type");
     const int64_t dims[3] = {d.dims[0], d.dims[1], d.dims[2]};
     const int perm[3] = {static_cast<int>(d.dims[3]), static_cast<int>(d.dims[4]),
                          static_cast<int>(d.dims[5])};
@@ -366,7 +374,7 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     }
     if (seen != 7) throw std::runtime_error("gpuLaunchKernel: bad transpose3d permutation");
     s->last_kernel = "transpose3d";
-    err = imex::launch_transpose3d_b32(ptrs[0], ptrs[1], dims, perm, s->stream);
+    err = imex::launch_transpose3d(ptrs[0], ptrs[1], dims, perm, static_cast<int>(dtype_bytes(d.in_dtype)), s->stream);
     break;
   }
   case IMEX_OP_ELTWISE:

@@ -157,6 +157,8 @@ def test_f16_multiply_add_is_not_sent_to_the_tensor_cores():
 @needs_reference
 @pytest.mark.parametrize("name,subst,expect", [
     ("softmax/softmax_gpu", {"shape": "64x2000", "batch_size": "64"}, ["softmax dims=[64,2000"]),
+    ("softmax/softmax_gpu", {"shape": "1024x2000", "batch_size": "1024", "dtype": "f16"},
+     ["softmax f16 dims=[1024,2000"]),
     ("relu/relu_gpu", {"shape": "512x640x20x15", "affine_map": "d0, d1, d2, d3",
                        "iterator_types": '"parallel", "parallel", "parallel", "parallel"'},
      ["relu dims=[98304000"]),

@@ -604,6 +604,19 @@ def test_transpose3d(pkg, sess, dims, perm):
     assert np.array_equal(got, oracle.transpose3d(X, perm))
 
 
+@pytest.mark.parametrize("dims", [(16, 96, 96), (96, 7, 96), (3, 5, 7)])
+@pytest.mark.parametrize("perm", [(0, 2, 1), (2, 1, 0), (1, 2, 0)])
+def test_transpose3d_of_16bit_elements(pkg, sess, dims, perm):
+    """The f16 / bf16 rows of the reference's transpose grid (benchmarks/transpose/transpose.dtypes.in):
+    a bit copy, so the 32-bit oracle on the zero-extended values is the check."""
+    X = np.random.default_rng(sum(dims) + 1).integers(0, 65536, dims).astype(np.uint16)
+    dX, dY = sess.upload(X), sess.alloc(X.nbytes)
+    sess.run(pkg.blob.transpose3d("tr3h", dims, perm, pkg.blob.F16), [dX, dY])
+    got = sess.download(dY, tuple(dims[p] for p in perm), np.uint16)
+    ref = oracle.transpose3d(X.astype(np.uint32).view(np.float32), perm).view(np.uint32)
+    assert np.array_equal(got.astype(np.uint32), ref)
+
+
 # ---------------------------------------------------------------- eltwise / fill
 def test_eltwise_relu_silu(pkg, sess):
     X = np.random.default_rng(8).normal(0, 4, 100003).astype(np.float32)
@@ -869,3 +882,30 @@ def test_attention_forward_at_the_reference_size(pkg, sess):
     vf = oracle.f16_bits_to_f32(v).reshape(heads, n_ctx, 64)
     g = got.reshape(heads, n_ctx, 64)
     assert np.all(g <= vf.max(axis=1, keepdims=True) + 1e-3) and np.all(g >= vf.min(axis=1, keepdims=True) - 1e-3)
+
+
+# ---------------------------------------------------------------- softmax on 16-bit rows
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 2000), (16, 2000), (64, 2000), (5, 33), (300, 1024)])
+def test_softmax_on_16bit_rows_follows_the_element_type(pkg, sess, kind, shape):
+    """The f16 / bf16 rows of the reference's softmax grid (benchmarks/softmax/softmax.shapes.in,
+    softmax.dtypes.in): subtract, exp, add and divide round to the element type after every
+    operation and the row sum is the loop nest's sequential chain of rounded adds — the oracle
+    runs the chain's generics one at a time that way."""
+    B = pkg.blob
+    rows, cols = shape
+    bdt, odt, x_dev, x = _typed(pkg, kind, oracle.fill_uniform(shape, 61, -4.0, 4.0))
+    dx, dy = sess.upload(x_dev), sess.upload(np.full(shape, 0x7E00, np.uint16))
+    sess.run(B.softmax("softmax16", rows, cols, dtype=bdt), [dx, dy])
+    assert sess.last_kernel() == "softmax_x16"
+    got = _from_device(kind, sess.download(dy, shape, np.uint16))
+    mx = np.broadcast_to(x.max(axis=1, keepdims=True), shape).copy()
+    e = oracle.unary("exp", oracle.binary("subf", x, mx, odt), odt)
+    s = oracle.reduce_leading_as(np.ascontiguousarray(e.T), odt)          # row sums, index ascending
+    ref = oracle.binary("divf", e, np.broadcast_to(s[:, None], shape).copy(), odt)
+    assert not np.isnan(got).any()
+    # expf of the device and of glibc may differ in the last f32 bit, which now and then moves a
+    # 16-bit rounding, and through the row sum every element of that row by an ulp
+    ulp = 2.0 ** -10 if kind == "f16" else 2.0 ** -7
+    assert np.all(np.abs(got - ref) <= 2 * ulp * np.abs(ref) + 1e-7)
+    assert np.mean(got != ref) <= 0.05
