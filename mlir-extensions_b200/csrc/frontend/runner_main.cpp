@@ -467,10 +467,18 @@ private:
         Value &v = peek(fr, op.ins[i], op);
         if (v.kind != Value::Tensor) die(where + "elementwise operand that is not a tensor");
         if (v.type.elt != outT.elt) die(where + "elementwise op mixing " + v.type.elt + " and " + outT.elt);
-        if (v.lazy && inlineLazy && info.inputMode[i] == 0 && v.type.count() == outT.count())
+        int mode = info.inputMode[i];
+        if (mode == 0 && v.type.count() != outT.count()) {
+          // a row broadcast that was kept as its vector (see BroadcastRow) and is read here
+          if (!v.lazy && v.type.shape.size() == 1 && outT.shape.size() == 2 && v.type.shape[0] == outT.shape[1])
+            mode = 1;
+          else
+            die(where + "elementwise operand of another size than the result");
+        }
+        if (v.lazy && inlineLazy && mode == 0)
           operands.push_back(v.lazy);
         else
-          operands.push_back(leaf(get(fr, op.ins[i], op), info.inputMode[i]));
+          operands.push_back(leaf(get(fr, op.ins[i], op), mode));
       }
       return substitute(info.tree, operands);
     };
@@ -813,7 +821,10 @@ private:
         }
         feedsBias = feedsBias && okUser;
       }
-      if (!feedsBias) die(where + "row broadcast that is not the bias of a matmul; no CPU fallback");
+      if (!feedsBias) {  // a broadcast on its own: the fused elementwise kernel with a row-vector input
+        elementwiseOp(op, b, fr, where);
+        break;
+      }
       fr.vals[res] = get(fr, op.ins[0], op);
       break;
     }
