@@ -683,6 +683,7 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
     if (le != cudaSuccess) return le;
     gemm_splitk_fixup_kernel<<<p.split_tiles * (PAIR_M / 8), 256, 0, stream>>>(p);
   }
+  if (g.launched) *g.launched = p.split_tiles ? 2 : 1;
   if (want_stats && stats_buf) {
     cudaStreamSynchronize(stream);
     double a[8] = {0};

@@ -39,6 +39,7 @@ struct GemmProblem {
   int sm_margin = 0;  // SMs the persistent kernels leave unused
   void *workspace = nullptr;   // device scratch for a k-split tail (optional)
   size_t workspace_bytes = 0;
+  int *launched = nullptr;     // out (optional): kernels this call enqueued (2 with a k-split tail)
 };
 
 // f32 or 16-bit inputs, one thread per 4x4 outputs, k ascending with

@@ -284,6 +284,7 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     g.epilogue = static_cast<int>(d.epilogue);
     g.accumulate = acc;
     g.sm_margin = static_cast<int>(d.sm_margin);
+    g.launched = &launches;
     if (g.M < 0 || g.N < 0 || g.K < 0) throw std::runtime_error("gpuLaunchKernel: negative gemm dims");
     if ((g.lda && g.lda < (g.trans_a ? g.M : g.K)) || (g.ldb && g.ldb < (g.trans_b ? g.K : g.N)) ||
         (g.ldc && g.ldc < g.N))
