@@ -288,7 +288,7 @@ def main():
     ap.add_argument("--comm-ms", type=float, default=0.5,
                     help="N>1, --overlap calls: how long the first GEMM launch (NCCL beside it) should last")
     ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "calls"),
-                    choices=["slabs", "calls"],
+                    choices=["slabs", "calls", "prefetch"],
                     help="N>1: hide the replication of B inside a call (column slabs) or across calls")
     ap.add_argument("--case", default=None, choices=sorted(CASES),
                     help="run ONE small kernel case --iters times and exit (ncu captures)")
@@ -357,6 +357,8 @@ def main():
     def step():
         # world > 1: B lives on rank 0; its column slabs are NCCL-broadcast on a side
         # stream and land in local HBM, each slab's GEMM starts when its slab is in
+        if args.overlap == "prefetch":  # this step also starts the replication for the next one
+            return gemm(A, Bm, Cm, b_ready=True, prefetch_next=Bm)
         return gemm(A, Bm, Cm, b_ready=True)  # B is resident on rank 0 before the step
 
     sampler = ClockSampler(local_rank)
@@ -509,7 +511,9 @@ def main():
                                           "launch leaves %d SMs free" if gemm.overlap == "slabs" else
                                           "as one slab %s into one of two replica buffers, overlapped with "
                                           "the previous step's GEMM, whose first launch leaves %d SMs free "
-                                          "and whose second uses all SMs"))
+                                          "and whose second uses all SMs" if gemm.overlap == "calls" else
+                                          "as one slab %s started by the previous step, beside its main GEMM "
+                                          "launch; a helper launch takes over the %d SMs the broadcast held"))
                                       % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 else "none",
                        "gemm_launch_columns": [int(k_.dims[1]) for k_ in gemm.launch_descs],
                        "l2": "inputs (%d MiB A shard + 128 MiB B) and the %d MiB C shard exceed the 126 MB L2"

@@ -30,6 +30,12 @@ Two ways to hide the replication (`overlap=`):
              replica: the first leaves 32 SMs free and lasts about as long as
              the replication, the second uses the whole machine.  A lone call
              pays the whole replication up front.
+    "prefetch"  as "calls", but the caller names the NEXT call's B
+             (`prefetch_next=`) and the call itself starts that replication;
+             the GEMM is a main launch on all SMs but 32 and, on a second
+             stream, a helper launch on those 32 SMs that starts when the
+             replication has left them.  Written for 8 GPUs, where the first
+             launch of "calls" cannot be made short enough; not yet measured.
 """
 from . import blob as B
 from . import runtime as rt
@@ -131,6 +137,22 @@ def plan_two_parts(rows, n_cols, k, sm_count=148, comm_sms=32, comm_ms=0.5, tflo
     return w1, n_cols - w1
 
 
+def plan_main_helper(rows, n_cols, k, sm_count=148, comm_sms=32, comm_ms=0.4, tflops=1400.0):
+    """Column split (w_main, w_helper) for `overlap="prefetch"`: the main launch runs on
+    sm_count - comm_sms SMs for the whole call, the helper on comm_sms SMs once the
+    replication (comm_ms) has left them; widths in whole 256-column blocks, chosen so that
+    both finish together.  w_helper may be 0 (too few column blocks)."""
+    col_blocks = -(-n_cols // PAIR_TILE)
+    if col_blocks < 2:
+        return n_cols, 0
+    est_ms = 2.0 * rows * n_cols * k / (tflops * 1e9)            # on all SMs
+    total = (est_ms * sm_count + comm_sms * comm_ms) / sm_count   # helper's SMs idle for comm_ms
+    frac_main = min(1.0, (sm_count - comm_sms) * total / (est_ms * sm_count))
+    main_blocks = min(col_blocks - 1, max(1, round(frac_main * col_blocks)))
+    w_main = main_blocks * PAIR_TILE
+    return w_main, n_cols - w_main
+
+
 class RowShardedGemm:
     """C[rows of this rank, :] = epilogue(A[rows of this rank, :] . B), B replicated
     from rank `src` inside every call."""
@@ -145,14 +167,14 @@ class RowShardedGemm:
         self.sess, self.rank, self.world, self.src = session, rank, world, src
         self.m_total, self.n, self.k = m_total, n, k
         self.row0, self.rows = shard_rows(rank, world, m_total)
-        if overlap not in ("slabs", "calls"):
-            raise ValueError("overlap must be 'slabs' or 'calls'")
+        if overlap not in ("slabs", "calls", "prefetch"):
+            raise ValueError("overlap must be 'slabs', 'calls' or 'prefetch'")
         self.overlap = overlap
         if sm_margin is None:
-            sm_margin = 32 if overlap == "calls" else 8
+            sm_margin = 8 if overlap == "slabs" else 32
         self.margin = sm_margin if world > 1 else 0
         if slabs is None:
-            slabs = [(0, n)] if overlap == "calls" else plan_slabs(self.rows, n, world, sm_margin=sm_margin)
+            slabs = plan_slabs(self.rows, n, world, sm_margin=sm_margin) if overlap == "slabs" else [(0, n)]
         self.slabs = slabs
         self.device = device
         self.comm_stream = torch.cuda.Stream(device=device) if world > 1 else None
@@ -168,7 +190,26 @@ class RowShardedGemm:
             self.slab_bufs = self.slab_sets[0]
         # launches: (slab index, first column inside the slab, first column of C, kernel)
         self.launches, self.launch_descs = [], []
-        if world > 1 and overlap == "calls" and len(self.slabs) == 1:
+        self.helper = None        # overlap="prefetch": (first column, kernel of the helper session)
+        self._prefetched = None   # (replica index, work handle, tensor holding B on this rank)
+        self.slab_bufs = self.slab_sets[0] if self.slab_sets else None
+        if world > 1 and overlap == "prefetch" and len(self.slabs) == 1:
+            from .session import Session
+            w_main, w_help = plan_main_helper(self.rows, n, k, comm_sms=self.margin, comm_ms=comm_ms)
+            desc = B.gemm("row_sharded_gemm_main", self.rows, w_main, k, in_dtype, epilogue,
+                          ldb=n if w_main != n else 0, ldc=n if w_main != n else 0, sm_margin=self.margin)
+            self.launch_descs.append(desc)
+            self.launches.append((0, 0, 0, session.kernel(desc)))
+            if w_help:
+                # its own stream and session: own k-split workspace, own status word
+                self.helper_stream = torch.cuda.Stream(device=device)
+                dev_index = device.index if hasattr(device, "index") and device.index is not None else 0
+                self.helper_sess = Session(device=dev_index, adopt_stream=self.helper_stream.cuda_stream)
+                hdesc = B.gemm("row_sharded_gemm_helper", self.rows, w_help, k, in_dtype, epilogue,
+                               ldb=n, ldc=n, sm_margin=max(0, 148 - self.margin))
+                self.launch_descs.append(hdesc)
+                self.helper = (w_main, self.helper_sess.kernel(hdesc))
+        elif world > 1 and overlap == "calls" and len(self.slabs) == 1:
             w1, w2 = plan_two_parts(self.rows, n, k, comm_sms=self.margin, comm_ms=comm_ms)
             for j, (c0, w, margin) in enumerate([(0, w1, self.margin), (w1, w2, 0)]):
                 if w:
@@ -197,9 +238,75 @@ class RowShardedGemm:
                 waited.add(slab)
             self.sess.launch(kern, [a_shard.data_ptr(), bufs[slab].data_ptr() + self.elt_bytes * b_col,
                                     c_shard.data_ptr() + 4 * c_col], wait=False)
+        if self.helper is not None:  # the helper's columns, beside the main launch
+            torch = self.torch
+            cur = torch.cuda.current_stream()
+            col, kern = self.helper
+            self.helper_stream.wait_stream(cur)
+            self.helper_sess.launch(kern, [a_shard.data_ptr(), bufs[0].data_ptr() + self.elt_bytes * col,
+                                           c_shard.data_ptr() + 4 * col], wait=False)
+            joined = torch.cuda.Event()
+            joined.record(self.helper_stream)
+            cur.wait_event(joined)
+            return len(self.launches) + 1
         return len(self.launches)
 
-    def __call__(self, a_shard, b_full, c_shard, b_ready=None):
+    def _call_prefetch(self, a_shard, b_full, c_shard, b_ready, prefetch_next):
+        """overlap="prefetch": see the module text.  All of the call's work, the helper launch
+        included, is ordered before whatever the caller enqueues next on the current stream."""
+        torch = self.torch
+        import torch.distributed as dist
+        cur = torch.cuda.current_stream()
+        is_src = self.rank == self.src
+        if self._prefetched is not None:
+            which, work, b_here = self._prefetched
+            self._prefetched = None
+        else:  # nothing was prefetched for this call: replicate now
+            which = self.calls & 1
+            if b_ready is None:
+                self.comm_stream.wait_stream(cur)
+            elif b_ready is not True:
+                self.comm_stream.wait_event(b_ready)
+            if self.done_events[which] is not None:
+                self.comm_stream.wait_event(self.done_events[which])
+            b_here = b_full if is_src else self.slab_sets[which][0]
+            with torch.cuda.stream(self.comm_stream):
+                work = dist.broadcast(b_here, src=self.src, async_op=True)
+        self.calls += 1
+        self.slab_bufs = [b_here]
+        work_next = None
+        if prefetch_next is not None:  # resident on `src` already: starts at once
+            nb = which ^ 1
+            if self.done_events[nb] is not None:
+                self.comm_stream.wait_event(self.done_events[nb])
+            b_next = prefetch_next if is_src else self.slab_sets[nb][0]
+            with torch.cuda.stream(self.comm_stream):
+                work_next = dist.broadcast(b_next, src=self.src, async_op=True)
+            self._prefetched = (nb, work_next, b_next)
+        if self.helper is not None:
+            self.helper_stream.wait_stream(cur)       # A and whatever else precedes this call
+        work.wait()
+        self.sess.launch(self.launches[0][3], [a_shard.data_ptr(), b_here.data_ptr(), c_shard.data_ptr()],
+                         wait=False)
+        n_launch = 1
+        if self.helper is not None:
+            col, kern = self.helper
+            with torch.cuda.stream(self.helper_stream):
+                work.wait()
+                if work_next is not None:
+                    work_next.wait()                   # the SMs the replication held are free now
+                self.helper_sess.launch(kern, [a_shard.data_ptr(), b_here.data_ptr() + self.elt_bytes * col,
+                                               c_shard.data_ptr() + 4 * col], wait=False)
+            joined = torch.cuda.Event()
+            joined.record(self.helper_stream)
+            cur.wait_event(joined)
+            n_launch = 2
+        done = torch.cuda.Event()
+        done.record(cur)
+        self.done_events[which] = done
+        return n_launch
+
+    def __call__(self, a_shard, b_full, c_shard, b_ready=None, prefetch_next=None):
         """a_shard [rows,k], c_shard [rows,n] on this rank; b_full [k,n] valid on `src`
         (a scratch tensor of that shape elsewhere).  Enqueues on the current stream.
 
@@ -207,10 +314,14 @@ class RowShardedGemm:
                           current stream (b_full may be produced there); safe default;
                  True  -> b_full is already complete in memory (resident weights): the
                           broadcast starts at once and overlaps earlier GEMMs;
-                 event -> the broadcast waits for that CUDA event only."""
+                 event -> the broadcast waits for that CUDA event only.
+        prefetch_next (overlap="prefetch" only): the B of the NEXT call, already complete in
+        memory on `src`; its replication starts inside this call."""
         torch = self.torch
         if self.world == 1:
             return self.launch_gemms(a_shard, c_shard, bufs=[b_full])
+        if self.overlap == "prefetch":
+            return self._call_prefetch(a_shard, b_full, c_shard, b_ready, prefetch_next)
         cur = torch.cuda.current_stream()
         which = self.calls & 1
         self.calls += 1

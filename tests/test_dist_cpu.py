@@ -136,3 +136,19 @@ def test_two_part_plan_for_the_benchmark_gemm(world):
     # a GEMM shorter than the replication keeps one launch with the margin
     assert rows.plan_two_parts(1024, 8192, 1024) == (8192, 0)
     assert rows.plan_two_parts(4096, 512, 512) == (512, 0)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_main_and_helper_plan_for_the_benchmark_gemm(world):
+    """overlap="prefetch": the helper's columns are what 32 SMs can do in the time the main
+    launch needs on the other 116, less the time the replication holds them."""
+    from mlir_extensions_b200 import dist as rows
+    n = k = 8192
+    r = 65536 // world
+    w_main, w_help = rows.plan_main_helper(r, n, k)
+    assert w_main + w_help == n and w_main % 256 == 0 and w_help >= 256
+    est = 2.0 * r * n * k / 1.4e12                   # ms on 148 SMs
+    t_main = est * (w_main / n) * 148 / 116
+    t_help = 0.4 + est * (w_help / n) * 148 / 32
+    assert abs(t_main - t_help) <= 0.25 * max(t_main, t_help)
+    assert rows.plan_main_helper(1024, 256, 64) == (256, 0)   # one column block: nothing to hand over
