@@ -114,3 +114,36 @@ def test_statistics_definitions():
     assert rt.stat(5, v) == pytest.approx(2.0) and rt.stat(4, v) == pytest.approx(2.0 ** 0.5)
     assert rt.stat(6, v) == 5.0 and rt.stat(7, v) == 1.0 and rt.stat(8, v) == pytest.approx(3.0)
     assert rt.stat(3, [7.0]) == 7.0  # clamped where the reference would read past the end
+
+
+def test_expression_programs_assemble_and_pack():
+    """Postfix text -> ImexExprCode bytes -> the four program words of the descriptor."""
+    import struct
+    code = B.assemble_expr("in0 log in1 abs add in0 sub")
+    assert list(code) == [B.X_IN, B.X_UNARY["log"], B.X_IN + 1, B.X_UNARY["abs"], B.X_BINARY["add"],
+                          B.X_IN, B.X_BINARY["sub"]]
+    assert list(B.assemble_expr("row2 col3 mul c0 c1 max zero one min add")) == [
+        B.X_ROWV + 2, B.X_COLV + 3, B.X_BINARY["mul"], B.X_C0, B.X_C1, B.X_BINARY["max"], B.X_ZERO, B.X_ONE,
+        B.X_BINARY["min"], B.X_BINARY["add"]]
+    d = B.expr("chain", 512, 1024, "in0 log in1 abs add in0 sub", B.F16, reduce_leading=True, consts=(0.5, 2.0))
+    assert d.op == B.OP_EXPR and d.in_dtype == d.out_dtype == B.F16 and d.flags == B.FLAG_REDUCE_LEADING
+    assert d.dims[:2] == (512, 1024)
+    assert struct.pack("<4q", *d.dims[2:]).rstrip(b"\0") == code
+    assert d.fparams == (0.5, 2.0)
+    back = B.unpack_blob(B.pack_blob([d]))[1][0]
+    assert back.dims == d.dims and back.flags == d.flags
+    with pytest.raises(ValueError):
+        B.assemble_expr("in0 frobnicate")
+    with pytest.raises(ValueError):
+        B.assemble_expr("in4")
+    with pytest.raises(ValueError):
+        B.assemble_expr(" ".join(["in0"] * 33))
+
+
+def test_gemm_layout_and_attention_descriptors():
+    d = B.gemm("g", 64, 128, 256, B.F16, B.EPI_RELU, bias=True, trans_a=True, trans_b=True, out_dtype=B.BF16)
+    assert d.flags == B.FLAG_BIAS | B.FLAG_TRANS_A | B.FLAG_TRANS_B and d.out_dtype == B.BF16
+    a = B.attention_fwd("a", 4, 4096, 64, B.F16, 0.5)
+    assert a.op == B.OP_ATTENTION_FWD and a.dims[:3] == (4, 4096, 64) and a.fparams[0] == 0.5
+    s = B.softmax("s", 16, 2000, dtype=B.BF16)
+    assert s.in_dtype == s.out_dtype == B.BF16
