@@ -14,6 +14,9 @@
  * Parity pins: tests/golden/reference_vectors.json (values transcribed from
  * the CHECK lines of the reference's own tests) and oracle/_ref (the
  * reference's in-tree CPU GEMM compiled from its own source file).
+ * PARITY UNPINNED (no golden values exist in the reference): silu, the
+ * one-generic-at-a-time functions in 16-bit element types (oracle_unary /
+ * oracle_binary / oracle_reduce_leading_as) and oracle_attention_fwd_x16.
  *
  * Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may
  * load this library.  The product never does.
