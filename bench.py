@@ -285,6 +285,9 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=16, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--sm-margin", type=int, default=None,
                     help="SMs the GEMM leaves to the NCCL broadcast when N > 1")
+    ap.add_argument("--timeline", type=int, default=0,
+                    help="N>1: after the timed region run this many more steps with timing events around "
+                         "every broadcast and every step's GEMM launches and report the intervals")
     ap.add_argument("--comm-ms", type=float, default=0.5,
                     help="N>1, --overlap calls: how long the first GEMM launch (NCCL beside it) should last")
     ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "calls"),
@@ -403,6 +406,24 @@ def main():
         kernel_ms = max_over_ranks(ka.elapsed_time(kb))
     flops_job = 2.0 * M_total * N_DIM * K_DIM
     value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # optional: when does each broadcast run relative to the GEMMs (ms since the first event)
+    timeline = None
+    if world > 1 and args.timeline > 0 and args.overlap != "prefetch":
+        barrier()
+        base = torch.cuda.Event(enable_timing=True)
+        base.record()
+        gemm.trace = []
+        for _ in range(args.timeline):
+            step()
+        torch.cuda.synchronize()
+        mine = [{"step": i, "broadcast": [base.elapsed_time(e[0]), base.elapsed_time(e[1])],
+                 "gemm": [base.elapsed_time(e[2]), base.elapsed_time(e[3])]} for i, e in enumerate(gemm.trace)]
+        gemm.trace = None
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        timeline = {"rank0": gathered[0], "rank%d" % (world - 1): gathered[-1],
+                    "note": "each rank's own clock; broadcast[0] = the moment it may start"}
 
     # optional last step, outside the timed region and reported on its own: every rank
     # gets all rows of C (NCCL all-gather of the row shards)
@@ -530,7 +551,7 @@ def main():
                          "frac_of_nominal_2250": achieved / 2250.0},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "parity": {"rel_frobenius_sampled_rows": frob, "tolerance": 1e-3},
-            "cpu_baseline": cpu, "kernels": kernels, "sharded_rows": sharded, "all_gather_c": gather,
+            "cpu_baseline": cpu, "kernels": kernels, "sharded_rows": sharded, "all_gather_c": gather, "timeline": timeline,
         }
         print(json.dumps(line), flush=True)
     sess.close()

@@ -190,6 +190,7 @@ class RowShardedGemm:
             self.slab_bufs = self.slab_sets[0]
         # launches: (slab index, first column inside the slab, first column of C, kernel)
         self.launches, self.launch_descs = [], []
+        self.trace = None         # set to a list to collect four timing events per call (see __call__)
         self.helper = None        # overlap="prefetch": (first column, kernel of the helper session)
         self._prefetched = None   # (replica index, work handle, tensor holding B on this rank)
         self.slab_bufs = self.slab_sets[0] if self.slab_sets else None
@@ -227,7 +228,7 @@ class RowShardedGemm:
         self.kernels = [l[3] for l in self.launches]
         self.elt_bytes = 2
 
-    def launch_gemms(self, a_shard, c_shard, bufs=None, works=None):
+    def launch_gemms(self, a_shard, c_shard, bufs=None, works=None, on_first_wait=None):
         """Enqueue the GEMM launches of one call on the current stream; with `works`
         every launch first waits for the replication of its slab."""
         bufs = bufs if bufs is not None else self.slab_bufs
@@ -236,6 +237,8 @@ class RowShardedGemm:
             if works is not None and slab not in waited:
                 works[slab].wait()  # the current stream waits for this slab only
                 waited.add(slab)
+                if on_first_wait is not None and len(waited) == 1:
+                    on_first_wait()
             self.sess.launch(kern, [a_shard.data_ptr(), bufs[slab].data_ptr() + self.elt_bytes * b_col,
                                     c_shard.data_ptr() + 4 * c_col], wait=False)
         if self.helper is not None:  # the helper's columns, beside the main launch
@@ -333,6 +336,10 @@ class RowShardedGemm:
         # this set of slab buffers was last read by the GEMMs of two calls ago
         if self.done_events[which] is not None:
             self.comm_stream.wait_event(self.done_events[which])
+        ev = None
+        if self.trace is not None:  # (broadcast may start, broadcast done, GEMMs may start, GEMMs done)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record(self.comm_stream)
         if self.rank == self.src and len(self.slabs) == 1 and b_full.is_contiguous():
             # one full-width slab: the source sends B from where it lies and multiplies
             # with it in place (no packing copy competing with the GEMM for SMs)
@@ -345,7 +352,15 @@ class RowShardedGemm:
         else:
             works = replicate_slabs(b_full, bufs, self.slabs, self.src, self.rank == self.src,
                                     self.comm_stream)
-        n_launch = self.launch_gemms(a_shard, c_shard, bufs, works)
+        if ev is not None:
+            with torch.cuda.stream(self.comm_stream):
+                works[-1].wait()
+            ev[1].record(self.comm_stream)
+        n_launch = self.launch_gemms(a_shard, c_shard, bufs, works,
+                                     on_first_wait=(lambda: ev[2].record(cur)) if ev is not None else None)
+        if ev is not None:
+            ev[3].record(cur)
+            self.trace.append(ev)
         done = torch.cuda.Event()
         done.record(cur)
         self.done_events[which] = done
