@@ -212,3 +212,37 @@ def test_reference_gemm_reproduces_its_own_golden():
     assert oracle.ref_lib().ref_allclose_f32(
         got.ctypes.data_as(oracle._fp),
         np.array(case["expected"], np.float32).ctypes.data_as(oracle._fp), 9) == 1
+
+
+def test_one_pass_attention_recurrence_stays_within_the_budget_of_the_gpu_tests():
+    """The attention kernel's arithmetic, emulated in numpy (blocks of 128 keys, running maximum in
+    log2 units, un-normalised probabilities rounded to f16, division by the row sum at the end),
+    against the oracle (= the reference test's CPU check, which normalises before rounding): the
+    two formulations differ by 16-bit roundings only, inside the tolerances the GPU tests use, and
+    both are equally far from a float64 evaluation."""
+    heads, n, d, scale = 2, 384, 64, 0.5
+    q, k, v = (oracle.to_f16_bits(oracle.fill_uniform((heads * n, d), 41 + i, -1.0, 1.0)) for i in range(3))
+    ref = oracle.f16_bits_to_f32(oracle.attention_fwd(q, k, v, heads, scale, False))
+    qf, kf, vf = (oracle.f16_bits_to_f32(x).reshape(heads, n, d) for x in (q, k, v))
+    sl2 = np.float32(scale * 1.4426950408889634)
+    out = np.empty((heads, n, d), np.float32)
+    for h in range(heads):
+        m = np.full((n, 1), -np.inf, np.float32)
+        l = np.zeros((n, 1), np.float32)
+        o = np.zeros((n, d), np.float32)
+        for j0 in range(0, n, 128):
+            s = (qf[h] @ kf[h][j0:j0 + 128].T).astype(np.float32) * sl2
+            m_new = np.maximum(m, s.max(axis=1, keepdims=True))
+            alpha = np.exp2(m - m_new)
+            p = np.exp2(s - m_new).astype(np.float32)
+            l = l * alpha + p.sum(axis=1, keepdims=True)
+            o = o * alpha + p.astype(np.float16).astype(np.float32) @ vf[h][j0:j0 + 128]
+            m = m_new
+        out[h] = (o / l).astype(np.float16).astype(np.float32)
+    out = out.reshape(heads * n, d)
+    assert oracle.rel_frobenius(out, ref) <= 1e-3
+    assert np.all(np.abs(out - ref) <= 2.5e-4 + 2e-3 * np.abs(ref))
+    truth = np.concatenate([(lambda S: (np.exp(S - S.max(1, keepdims=True)) /
+                                        np.exp(S - S.max(1, keepdims=True)).sum(1, keepdims=True)) @ vf[h].astype(np.float64))(
+        (qf[h].astype(np.float64) @ kf[h].astype(np.float64).T) * scale) for h in range(heads)])
+    assert np.abs(out - truth).max() <= 1.5 * np.abs(ref - truth).max() + 1e-4
