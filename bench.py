@@ -55,17 +55,25 @@ def measured_peaks():
             "source": "fallback"}
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
-# captures summarised under profiles/; None where no capture has been taken.
-NCU_TRAFFIC = {
-    # profiles/gemm_tcgen05_2cta_8192_silu.md: 1.104 GB read + 0.2446 GB written on 8192 rows
-    "gemm_cfg5_per_8192_rows": 1.104139e9 + 244.613888e6,
-    "gemm_cfg3": None,
-    # profiles/memory_bound_kernels.md
-    "softmax": None,            # config 2 fits L2; the 65536-row capture moved 268.5 + 212.2 MB
-    "reduce_rows": 1073.754e6 + 3.6e6,
-    "transpose2d": 268.44e6 + 218.1e6,
-}
+def ncu_traffic():
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel, taken
+    from ncu captures: a text table `key bytes_read bytes_written` kept with the other profiler
+    summaries.  A key without a capture maps to None."""
+    table = {}
+    path = os.path.join(ROOT, "profiles", "ncu_dram_traffic.txt")
+    if os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                p = line.split("#")[0].split()
+                if len(p) >= 3:
+                    try:
+                        table[p[0]] = float(p[1]) + float(p[2])
+                    except ValueError:
+                        pass
+    return table
+
+
+NCU_TRAFFIC = ncu_traffic()
 
 
 class ClockSampler:
@@ -197,6 +205,7 @@ CASES = {
     "softmax": "softmax 4096x1024 (config 2)",
     "softmax_big": "softmax 65536x1024 (config-2 kernel on a 512 MiB problem, larger than L2)",
     "reduce": "row reduce 32768x8192 (config 4a)",
+    "reduce_shard8": "row reduce 4096x8192 (one rank's rows of config 4a at 8 GPUs)",
     "transpose": "transpose 8192x8192 (config 4b)",
     "attention": "attention forward, 4 heads x 4096 keys x d 64, f16 (the reference test's shape)",
     "loop_fusion": "fused elementwise chain (log, absf, addf, subf) on 8192x8192 f32",
@@ -243,10 +252,11 @@ def run_case(name, iters):
         k = sess.kernel(B.expr(name, 8192, 8192, "in0 log in1 abs add in0 sub", B.F32))
         ptrs = [X.data_ptr(), X1.data_ptr(), Y.data_ptr()]
         work, unit = 3 * X.numel() * 4 / 1e9, "GB/s"
-    elif name == "reduce":
-        X = torch.empty((32768, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
-        Y = torch.empty(32768, dtype=torch.float32, device=dev)
-        k, ptrs = sess.kernel(B.reduce_rows(name, 32768, 8192)), [X.data_ptr(), Y.data_ptr()]
+    elif name.startswith("reduce"):
+        nrows = 32768 if name == "reduce" else 4096
+        X = torch.empty((nrows, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
+        Y = torch.empty(nrows, dtype=torch.float32, device=dev)
+        k, ptrs = sess.kernel(B.reduce_rows(name, nrows, 8192)), [X.data_ptr(), Y.data_ptr()]
         work, unit = (X.numel() + Y.numel()) * 4 / 1e9, "GB/s"
     else:
         X = torch.empty((8192, 8192), dtype=torch.float32, device=dev).uniform_(-1.0, 1.0)
@@ -296,6 +306,8 @@ def main():
     ap.add_argument("--case", default=None, choices=sorted(CASES),
                     help="run ONE small kernel case --iters times and exit (ncu captures)")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="how many times the K-step region runs in all (the first one gives `value`)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -390,9 +402,22 @@ def main():
     sess.wait()
     launches = rt.imexLaunchCount() - launches0
     gemm_kernel_name = sess.last_kernel()
-    clocks = sampler.stop() if rank == 0 else None
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = total_ms / args.steps
+    # the same K-step region again, a few times: how much one region's figure moves (short
+    # regions do not reach the power cap, long ones do); `value` stays the first region's
+    region_ms = [ms_per_step]
+    for _ in range(max(0, args.repeats - 1)):
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(args.steps):
+            step()
+        r1.record()
+        barrier()
+        region_ms.append(max_over_ranks(r0.elapsed_time(r1)) / args.steps)
+    sess.wait()
+    clocks = sampler.stop() if rank == 0 else None
     if world == 1:
         kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_events]))
     else:
@@ -448,16 +473,43 @@ def main():
                   "own_block_intact": same, "note": "NCCL all-gather of the f32 row shards of C, not in ms_per_step"}
         del c_full
 
-    # parity guard: sampled rows of this rank's shard against the CPU oracle
+    # parity guard (enforced): rows of this rank's shard against the CPU oracle: the first
+    # and the last row, one row of the last 256-row block (where a k-split tail lands) and
+    # random ones; at N > 1 the whole shard against ONE plain launch over the same rows
     from oracle import oracle
-    sample_rows = np.sort(np.random.default_rng(rank).choice(rows, size=min(8, rows), replace=False))
+    rng = np.random.default_rng(rank)
+    fixed = {0, rows - 1, max(0, rows - 1 - int(rng.integers(0, min(256, rows))))}
+    extra = rng.choice(rows, size=min(8, rows), replace=False)
+    sample_rows = np.array(sorted(fixed | set(int(r) for r in extra)))
     a_bits = A[torch.as_tensor(sample_rows, device=dev)].view(torch.int16).cpu().numpy().view(np.uint16)
     if world > 1:
         dist.broadcast(Bm, src=0)  # only for this check: non-root ranks hold B as slabs
     b_bits = Bm.view(torch.int16).cpu().numpy().view(np.uint16)
     got = Cm[torch.as_tensor(sample_rows, device=dev)].cpu().numpy()
     ref = oracle.silu(oracle.matmul_x16_f32(a_bits, b_bits, True))
-    frob = max_over_ranks(oracle.rel_frobenius(got, ref))
+    frob_local = oracle.rel_frobenius(got, ref)
+    frob = max_over_ranks(frob_local if np.isfinite(frob_local) else 1e30)
+    shard_check = None
+    if world > 1:
+        plain = sess.kernel(B.gemm("whole_shard_one_launch", rows, N_DIM, K_DIM, B.BF16, epi))
+        C_one = torch.empty_like(Cm)
+        sess.launch(plain, [A.data_ptr(), Bm.data_ptr(), C_one.data_ptr()])
+        diff = (Cm - C_one).abs().max().item()
+        scale = C_one.abs().max().item()
+        shard_check = {"max_abs_diff_vs_one_launch": max_over_ranks(diff), "max_abs": max_over_ranks(scale),
+                       "bitwise_equal": bool(max_over_ranks(0.0 if torch.equal(Cm, C_one) else 1.0) == 0.0),
+                       "tolerance": "max abs diff <= 1e-5 x max abs (k-split tails sum in another order)"}
+        del C_one
+        if not (shard_check["max_abs_diff_vs_one_launch"] <= 1e-5 * shard_check["max_abs"]):
+            frob = 1e30  # every rank holds the same maxima, so every rank takes this branch
+    if not (frob <= 1e-3):
+        print("bench.py: PARITY FAILURE on rank %d: rel. Frobenius of sampled rows %.3e (this rank), "
+              "worst rank %.3e, shard check %s; tolerance 1e-3" % (rank, frob_local, frob, shard_check),
+              file=sys.stderr, flush=True)
+        sess.close()
+        if world > 1:
+            dist.destroy_process_group()
+        sys.exit(3)
 
     # ---- end to end through the C ABI with host buffers ----------------------
     e2e = None
@@ -541,7 +593,8 @@ def main():
                              % (rows * K_DIM * 2 >> 20, rows * N_DIM * 4 >> 20)},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC["gemm_cfg5_per_8192_rows"] * rows / 8192.0,
+                         "traffic": (NCU_TRAFFIC["gemm_cfg5_per_8192_rows"] * rows / 8192.0
+                                     if NCU_TRAFFIC.get("gemm_cfg5_per_8192_rows") else None),
                          "traffic_note": "ncu capture on 8192 rows scaled by rows/8192",
                          "kernel": gemm_kernel_name, "kernel_ms": kernel_ms,
                          "launches_per_step": len(gemm.launches),
@@ -550,9 +603,23 @@ def main():
                          if peaks.get("bf16_tflops_sustained") else None,
                          "frac_of_nominal_2250": achieved / 2250.0},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "parity": {"rel_frobenius_sampled_rows": frob, "tolerance": 1e-3},
-            "cpu_baseline": cpu, "kernels": kernels, "sharded_rows": sharded, "all_gather_c": gather, "timeline": timeline,
+            "parity": {"rel_frobenius_sampled_rows": frob, "tolerance": 1e-3, "enforced": True,
+                       "rows_checked_per_rank": int(len(sample_rows)), "whole_shard_vs_one_launch": shard_check},
+            "cpu_baseline": cpu, "sharded_rows": sharded, "all_gather_c": gather, "timeline": timeline,
+            "repeats": {"regions": len(region_ms), "tflops": [flops_job / (m * 1e-3) / 1e12 for m in region_ms],
+                        "median": flops_job / (float(np.median(region_ms)) * 1e-3) / 1e12,
+                        "min": flops_job / (max(region_ms) * 1e-3) / 1e12,
+                        "max": flops_job / (min(region_ms) * 1e-3) / 1e12,
+                        "ms_per_step_x_sm_mhz": (ms_per_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None},
+            "kernels_detail": kernels,
         }
+        # last, and short, so that a reader who keeps only the end of the line still has every
+        # kernel's roofline: name -> [achieved, unit, fraction of the measured peak, ms]
+        if kernels:
+            line["kernels"] = {k: {"achieved": round(v["roofline"]["achieved"], 1), "unit": v["roofline"]["unit"],
+                                   "frac": round(v["roofline"]["frac"], 3), "ms": round(v["roofline_ms"], 5),
+                                   "bound": v["roofline"]["bound"], "traffic": v["roofline"].get("traffic")}
+                               for k, v in kernels.items()}
         print(json.dumps(line), flush=True)
     sess.close()
     if world > 1:
@@ -637,7 +704,23 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
                 ms.append(a.elapsed_time(b))
         return float(np.median(ms))
 
-    def hbm_entry(name, key, nbytes, kernel, ptrs, note):
+    def back_to_back(kernel, ptr_sets, rounds=7):
+        """ms per launch when the launches follow each other on the stream, each on its own
+        buffers (ptr_sets together exceed L2, so every launch still reads cold data): one
+        event pair around len(ptr_sets) launches, median over `rounds`."""
+        per = []
+        for i in range(rounds + 2):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for ptrs in ptr_sets:
+                sess.launch(kernel, ptrs, wait=False)
+            b.record()
+            b.synchronize()
+            if i >= 2:
+                per.append(a.elapsed_time(b) / len(ptr_sets))
+        return float(np.median(per))
+
+    def hbm_entry(name, key, nbytes, kernel, ptrs, note, ptr_sets=None):
         med, mn = timed(kernel, ptrs, cold=True)
         wmed, _ = timed(kernel, ptrs, cold=False)
         ach = nbytes / (med * 1e-3) / 1e9
@@ -646,17 +729,32 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
                      "ms_warm_median": wmed, "algorithmic_bytes": nbytes,
                      "ms_copy_of_same_bytes": floor, "speed_vs_copy_of_same_bytes": floor / med,
                      "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm, "unit": "GB/s",
-                                  "frac": ach / hbm, "traffic": NCU_TRAFFIC[key],
+                                  "frac": ach / hbm, "traffic": NCU_TRAFFIC.get(key),
                                   "peak_source": peaks["source"] + " (copy)",
                                   "frac_of_nominal_8000": ach / 8000.0},
-                     "note": note}
+                     "roofline_ms": med, "note": note}
+        if ptr_sets:
+            # a problem this small is timed mostly by the event pair around ONE launch; the
+            # launch duration proper shows when launches follow each other
+            b2b = back_to_back(kernel, ptr_sets)
+            ach2 = nbytes / (b2b * 1e-3) / 1e9
+            out[name].update(ms_back_to_back=b2b, gbs_flushed_single_launch=ach, roofline_ms=b2b)
+            out[name]["roofline"].update(achieved=ach2, frac=ach2 / hbm, frac_of_nominal_8000=ach2 / 8000.0,
+                                         timing="%d launches back to back on %d distinct buffer pairs (%d MiB in all, "
+                                                "larger than L2), one event pair around them; the flushed "
+                                                "single-launch figure is gbs_flushed_single_launch"
+                                                % (len(ptr_sets), len(ptr_sets), len(ptr_sets) * nbytes >> 20))
+            out[name]["value"] = ach2
 
     # config 2: softmax 4096 x 1024
     X = torch.empty((4096, 1024), dtype=torch.float32, device=dev).normal_(0.0, 3.0)
     Y = torch.empty_like(X)
+    pairs = [(torch.empty_like(X).normal_(0.0, 3.0), torch.empty_like(X)) for _ in range(16)]
     hbm_entry("softmax_4096x1024", "softmax", 2 * X.numel() * 4,
               sess.kernel(B.softmax("softmax", 4096, 1024)), [X.data_ptr(), Y.data_ptr()],
-              "config 2; 32 MiB moved, fits L2: cold = flushed before each launch")
+              "config 2; 32 MiB moved, fits L2: cold = flushed before each launch",
+              ptr_sets=[[a.data_ptr(), b.data_ptr()] for a, b in pairs])
+    del pairs
     # config 4a: row reduce 32768 x 8192
     R = torch.empty((32768, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
     S = torch.empty(32768, dtype=torch.float32, device=dev)
@@ -673,11 +771,11 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
     del T, U
     # the reference's fusion benchmark chain (log, absf, addf, subf: kLoopFusion), scaled up to
     # 8192 x 8192 so that it streams from HBM; its own 512 x 1024 shape moves 6 MiB
-    for tag, tdt, bdt, esz in (("f32", torch.float32, B.F32, 4), ("f16", torch.float16, B.F16, 2)):
+    for tag, tdt, bdt, esz in (("f32", torch.float32, B.F32, 4), ("f16", torch.float16, B.F16, 2),
+                               ("bf16", torch.bfloat16, B.BF16, 2)):
         F0 = torch.empty((8192, 8192), dtype=tdt, device=dev).uniform_(0.5, 4.0)
         F1 = torch.empty((8192, 8192), dtype=tdt, device=dev).uniform_(-2.0, 2.0)
         F2 = torch.empty_like(F0)
-        NCU_TRAFFIC.setdefault("expr_" + tag, None)
         hbm_entry("loop_fusion_8192x8192_" + tag, "expr_" + tag, 3 * F0.numel() * esz,
                   sess.kernel(B.expr("loop_fusion", 8192, 8192, "in0 log in1 abs add in0 sub", bdt)),
                   [F0.data_ptr(), F1.data_ptr(), F2.data_ptr()],
@@ -695,15 +793,17 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
     aflops = 4.0 * heads * n_ctx * n_ctx * 64
     out["attention_fwd_4x4096x64"] = {
         "value": aflops / (med * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_cold_median": med, "ms_cold_min": mn,
-        "algorithmic_flops": aflops,
+        "algorithmic_flops": aflops, "roofline_ms": med,
         "roofline": {"bound": "tensor", "achieved": aflops / (med * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": aflops / (med * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None},
         "note": "the reference's flash-attention test shape; 128 CTAs of 128 query rows, 17 GFLOP in all"}
     del Q, Kt, Vt, Ot
     # config 3: GEMM 4096^3 + relu
     n = 4096
-    A = (torch.rand((n, n), device=dev) * 2 - 1).to(torch.bfloat16)
-    Bm = (torch.rand((n, n), device=dev) * 2 - 1).to(torch.bfloat16)
+    A = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
+    Bm = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
+    sess.run(B.fill_uniform("cfg3_a", n * n, B.BF16, 3, -1.0, 1.0), [A.data_ptr()])   # seeds 3, 4: the inputs of
+    sess.run(B.fill_uniform("cfg3_b", n * n, B.BF16, 4, -1.0, 1.0), [Bm.data_ptr()])  # the config-3 parity test
     Cm = torch.empty((n, n), dtype=torch.float32, device=dev)
     k = sess.kernel(B.gemm("gemm_relu", n, n, n, B.BF16, B.EPI_RELU))
     med, mn = timed(k, [A.data_ptr(), Bm.data_ptr(), Cm.data_ptr()], cold=True)
@@ -712,10 +812,10 @@ def bench_kernels(torch, pkg, sess, dev, peaks, iters=30):
     ach = fl / (med * 1e-3) / 1e12
     out["gemm_4096_relu"] = {
         "value": ach, "unit": "TFLOP/s", "ms_cold_median": med, "ms_cold_min": mn,
-        "ms_warm_median": wmed, "algorithmic_flops": fl,
+        "ms_warm_median": wmed, "algorithmic_flops": fl, "roofline_ms": med,
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                     "traffic": NCU_TRAFFIC["gemm_cfg3"],
+                     "traffic": NCU_TRAFFIC.get("gemm_cfg3"),
                      "peak_source": peaks["source"] + " (cuBLAS bf16 burst)",
                      "frac_of_nominal_2250": ach / 2250.0},
         "note": "config 3"}

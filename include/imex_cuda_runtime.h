@@ -62,14 +62,19 @@ void gpuMemcpy(void *stream, void *dst, void *src, size_t size); /* alias */
  * descriptor blob (imex_b200_blob.h); the parsed module is cached by blob
  * address and lives until process exit. */
 void *gpuModuleLoad(void *stream, const void *data, size_t dataSize);
-/* LevelZeroRuntimeWrappers.cpp:649-652 */
+/* LevelZeroRuntimeWrappers.cpp:649-652.  The handle belongs to the module:
+ * asking for the same name again returns the same handle. */
 void *gpuKernelGet(void *stream, void *module, const char *name);
 /* LevelZeroRuntimeWrappers.cpp:654-664, 507-603.  grid/block sizes describe
  * the reference's one-work-item-per-element launch and are NOT used: each
  * recognised op launches its own sm_100a geometry.  sharedMemBytes != 0
  * means the last param is the local-memory placeholder and is dropped
- * (LevelZeroRuntimeWrappers.cpp:462-475).  Returns an event that later
- * launches may list in depEvents.  With IMEX_ENABLE_PROFILING set the launch
+ * (LevelZeroRuntimeWrappers.cpp:462-475).  8-byte params whose value is not
+ * device-accessible memory (index scalars of loop bounds) are not operands
+ * and are skipped wherever they stand.  Returns an event that later
+ * launches may list in depEvents; events come from a ring of 256 per stream
+ * (the reference's fixed pool, LevelZeroRuntimeWrappers.cpp:155-168), so a
+ * handle is valid for the next 255 launches on that stream.  With IMEX_ENABLE_PROFILING set the launch
  * is repeated and timed first (IMEX_PROFILING_RUNS, IMEX_PROFILING_WARMUPS,
  * IMEX_ENABLE_CACHE_FLUSHING; LevelZeroRuntimeWrappers.cpp:521-597). */
 void *gpuLaunchKernel(void *stream, void *kernel, size_t gridX, size_t gridY,
@@ -113,7 +118,8 @@ uint64_t imexLaunchCount(void);
 const char *imexLastKernelName(void *stream);
 /* Block partition of `extent` over `numShards` (the reference's sharding rule,
  * lib/Dialect/NDArray/Extensions/MeshShardingExtensions.cpp:74-100: the LAST
- * extent%numShards shards get one extra element). */
+ * extent%numShards shards get one extra element).  Both return -1 for
+ * numShards <= 0, a shard outside [0, numShards) or a negative extent. */
 int64_t imexShardSize(int64_t shard, int64_t numShards, int64_t extent);
 int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent);
 /* Timing statistics of the profiling loop

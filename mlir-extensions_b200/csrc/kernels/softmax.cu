@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cfloat>
+#include <cstdlib>
 
 namespace imex {
 namespace {
@@ -107,6 +108,83 @@ softmax_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t 
   }
 }
 
+// The same row-in-registers scheme for problems of only a few rows per SM (config 2 of the
+// benchmark set: 4096 x 1024, i.e. 27.7 rows per SM).  With CTAs of eight rows the rows
+// land unevenly (four CTAs on some SMs, three on others) and the last CTA to be scheduled
+// sets the time.  Here the grid is one CTA per SM and each CTA has as many warps as its
+// share of the rows (up to MAXW), so every SM issues all of its loads in the first
+// microsecond and owns the same number of rows to within one; with more rows than
+// SMs x MAXW a warp walks several rows.  Row r goes to CTA r % gridDim.x.
+// The division is by one correctly rounded reciprocal per row and one residual step per
+// element (q = e * rc; q += (e - q * s) * rc): the correctly rounded quotient e / s for
+// every normal result (Markstein), at 3 instructions per element instead of the ~10 of a
+// full IEEE division sequence.
+__device__ __forceinline__ float4 ldg_stream4(const float4 *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float div_by(float e, float s, float rc) {
+  const float q = __fmul_rn(e, rc);
+  return __fmaf_rn(__fmaf_rn(-q, s, e), rc, q);
+}
+
+template <int V, int MAXW>
+__global__ void __launch_bounds__(32 * MAXW)
+softmax_warp_balanced_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int cols,
+                             float max_init) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int nvec = cols >> 2;
+  for (int64_t row = blockIdx.x + static_cast<int64_t>(gridDim.x) * warp; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * nwarps) {
+    const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols);
+    float4 *yr = reinterpret_cast<float4 *>(y + row * cols);
+    float4 v[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int idx = lane + 32 * i;
+      v[i] = (idx < nvec) ? ldg_stream4(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    float m = max_init;
+#pragma unroll
+    for (int i = 0; i < V; ++i) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    m = warp_max(m);
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      if (lane + 32 * i < nvec) {
+        v[i].x = exp_neg(v[i].x - m);
+        v[i].y = exp_neg(v[i].y - m);
+        v[i].z = exp_neg(v[i].z - m);
+        v[i].w = exp_neg(v[i].w - m);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
+    }
+    s = warp_sum(s);
+    const float rc = __frcp_rn(s);
+    // a sum that is not a finite normal number (NaN row, overflow) takes the full division
+    const bool plain = !(s >= 1.0f && s < 3.0e38f);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < nvec) {
+        float4 o;
+        if (plain) {
+          o.x = __fdiv_rn(v[i].x, s); o.y = __fdiv_rn(v[i].y, s);
+          o.z = __fdiv_rn(v[i].z, s); o.w = __fdiv_rn(v[i].w, s);
+        } else {
+          o.x = div_by(v[i].x, s, rc); o.y = div_by(v[i].y, s, rc);
+          o.z = div_by(v[i].z, s, rc); o.w = div_by(v[i].w, s, rc);
+        }
+        yr[idx] = o;
+      }
+    }
+  }
+}
+
 // Any cols: one block per row, three sweeps over the row (the 2nd and 3rd hit
 // L1/L2).  Used for ragged or very long rows.
 __global__ void __launch_bounds__(256)
@@ -172,9 +250,29 @@ softmax_tiny_rows_kernel(const float *__restrict__ x, float *__restrict__ y, int
   for (int c = 0; c < cols; ++c) yr[c] = __fdiv_rn(e[c], s);
 }
 
+// How many rows per SM the balanced kernel takes before the plain grid of 8-row CTAs
+// (which refills SMs as CTAs finish) streams as well.
+constexpr int64_t kBalancedMaxRowsPerSm = 128;
+
 template <int V>
 cudaError_t launch_warp(const float *x, float *y, int64_t rows, int cols, float max_init,
                         cudaStream_t stream) {
+  static const int sms = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  static const int variant = getenv("IMEX_SOFTMAX_VARIANT") ? atoi(getenv("IMEX_SOFTMAX_VARIANT")) : 1;
+  if (variant == 1 && rows <= kBalancedMaxRowsPerSm * sms) {
+    constexpr int MAXW = V <= 8 ? 32 : 16;
+    const int64_t per_sm = (rows + sms - 1) / sms;            // rows of the fullest SM
+    const int64_t rounds = (per_sm + MAXW - 1) / MAXW;        // rows a warp walks
+    const int warps_cta = static_cast<int>((per_sm + rounds - 1) / rounds);
+    const unsigned grid = static_cast<unsigned>(rows < sms ? rows : sms);
+    softmax_warp_balanced_kernel<V, MAXW><<<grid, 32 * warps_cta, 0, stream>>>(x, y, rows, cols, max_init);
+    return cudaGetLastError();
+  }
   const int warps = 8;
   unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
   softmax_warp_kernel<V><<<grid, warps * 32, 0, stream>>>(x, y, rows, cols, max_init);

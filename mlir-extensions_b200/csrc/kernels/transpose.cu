@@ -21,10 +21,13 @@ transpose2d_b32_vec_kernel(const uint32_t *__restrict__ x, uint32_t *__restrict_
   const int64_t tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
   const int64_t r0 = tr * TILE, c0 = tc * TILE;
   const int tid = threadIdx.x;
-  // load: 64 rows x 16 float4; thread -> (row = tid/16 + 16*p, vec = tid%16)
+  // load: 64 rows x 16 float4.  A warp takes 4 rows x 8 float4 (128 contiguous bytes per
+  // row): with the 65-word row pitch its 32 scalar stores of one component fall into 32
+  // different banks (bank = row + 4 * vec + k), and so do the transposed reads below.
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    int r = (tid >> 4) + 16 * p, v = tid & 15;
+    const int slot = tid + 256 * p;
+    int r = ((slot >> 3) & 3) + 4 * (slot >> 6), v = (slot & 7) + 8 * ((slot >> 5) & 1);
     int64_t gr = r0 + r, gc = c0 + 4 * v;
     if (gr < rows && gc < cols) {
       uint4 q = *reinterpret_cast<const uint4 *>(x + gr * cols + gc);
@@ -38,7 +41,8 @@ transpose2d_b32_vec_kernel(const uint32_t *__restrict__ x, uint32_t *__restrict_
   // store: output row = c0 + c, output cols r0 .. r0+63 as 16 float4
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    int c = (tid >> 4) + 16 * p, v = tid & 15;
+    const int slot = tid + 256 * p;
+    int c = ((slot >> 3) & 3) + 4 * (slot >> 6), v = (slot & 7) + 8 * ((slot >> 5) & 1);
     int64_t gc = c0 + c, gr = r0 + 4 * v;
     if (gc < cols && gr < rows) {
       uint4 q;

@@ -23,6 +23,7 @@
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 namespace {
@@ -54,6 +55,16 @@ struct Allocation {
   int device;
 };
 
+struct Event {
+  cudaEvent_t ev = nullptr;
+};
+
+// Launch-completion events come from a ring of kEventSlots per stream, created on first
+// use and re-recorded when the ring wraps: the reference hands out events from one fixed
+// pool of 256 slots as well (LevelZeroRuntimeWrappers.cpp:155-168) and nobody ever releases
+// them.  A handle therefore stays meaningful for the next 255 launches on its stream.
+constexpr size_t kEventSlots = 256;
+
 struct Stream {
   int device = 0;
   cudaStream_t stream = nullptr;
@@ -63,18 +74,18 @@ struct Stream {
   float *scratch = nullptr;  // reduce-all partials
   size_t scratch_bytes = 0;
   const char *last_kernel = "";
-};
-
-struct Module {
-  std::vector<ImexKernelDesc> kernels;
+  Event events[kEventSlots];
+  size_t next_event = 0;
+  std::unordered_set<const void *> device_ptrs;  // parameter values already seen to be device memory
 };
 
 struct Kernel {
   ImexKernelDesc desc;
 };
 
-struct Event {
-  cudaEvent_t ev = nullptr;
+struct Module {
+  std::vector<ImexKernelDesc> kernels;
+  std::vector<std::unique_ptr<Kernel>> handles;  // one per table row, made on first gpuKernelGet
 };
 
 std::mutex g_mutex;
@@ -132,6 +143,8 @@ Stream *make_stream(const int32_t *device, cudaStream_t adopt) {
 void destroy_stream(Stream *s) {
   if (!s) return;
   if (s->scratch) cudaFree(s->scratch);
+  for (auto &e : s->events)
+    if (e.ev) cudaEventDestroy(e.ev);
   if (s->status_host) cudaFreeHost(s->status_host);
   if (s->owned && s->stream) CHECK_CUDA(cudaStreamDestroy(s->stream));
   delete s;
@@ -203,11 +216,16 @@ Module *load_module(const void *data, size_t size) {
 
 Kernel *get_kernel(Module *m, const char *name) {
   if (!m || !name) throw std::runtime_error("gpuKernelGet: null module or name");
-  for (auto &k : m->kernels)
-    if (strncmp(k.name, name, IMEX_KERNEL_NAME_MAX) == 0) {
-      auto *out = new Kernel;  // never released, like the reference's kernel handles
-      out->desc = k;
-      return out;
+  for (size_t i = 0; i < m->kernels.size(); ++i)
+    if (strncmp(m->kernels[i].name, name, IMEX_KERNEL_NAME_MAX) == 0) {
+      // the handle belongs to the module (which lives to exit): asking twice gives the same one
+      std::lock_guard<std::mutex> lock(g_mutex);
+      if (m->handles.size() < m->kernels.size()) m->handles.resize(m->kernels.size());
+      if (!m->handles[i]) {
+        m->handles[i] = std::make_unique<Kernel>();
+        m->handles[i]->desc = m->kernels[i];
+      }
+      return m->handles[i].get();
     }
   throw std::runtime_error(std::string("gpuKernelGet: no kernel named '") + name + "' in module");
 }
@@ -509,6 +527,32 @@ void profile(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
   fflush(stdout);
 }
 
+// Is this 8-byte parameter value the address of memory a kernel can read?  Allocations of
+// this library are known; anything else is asked of the driver once and remembered.
+bool is_device_pointer(Stream *s, void *v) {
+  if (!v) return false;
+  if (s->device_ptrs.count(v)) return true;
+  bool yes = false;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    yes = g_allocs.count(v) != 0;
+  }
+  if (!yes) {
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, v) != cudaSuccess) {
+      cudaGetLastError();  // an ordinary integer: not an error of the launch
+      return false;
+    }
+    yes = a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged ||
+          (a.type == cudaMemoryTypeHost && a.devicePointer != nullptr);
+  }
+  if (yes) {
+    if (s->device_ptrs.size() > 4096) s->device_ptrs.clear();
+    s->device_ptrs.insert(v);
+  }
+  return yes;
+}
+
 Event *launch(Stream *s, Kernel *k, size_t sharedMemBytes, ImexParamDesc *params,
               ImexEventDesc *deps) {
   if (!s || !k) throw std::runtime_error("gpuLaunchKernel: null stream or kernel");
@@ -518,24 +562,26 @@ Event *launch(Stream *s, Kernel *k, size_t sharedMemBytes, ImexParamDesc *params
     while (!(params[nparams].data == nullptr && params[nparams].size == 0)) ++nparams;
   // the caller passes an i32; the last param is the local-memory placeholder then
   if ((sharedMemBytes & 0xFFFFFFFFu) != 0 && nparams > 0) --nparams;
+  // The lowering passes memrefs as bare pointers and index scalars (loop bounds) by value,
+  // both 8 bytes wide (GPUXToLLVMPass.cpp:571-584).  Only values that ARE device-accessible
+  // memory count as the op's operands; an index that sits between two memrefs is skipped
+  // instead of shifting the operands behind it.
   std::vector<void *> ptrs;
   for (size_t i = 0; i < nparams; ++i) {
     if (params[i].size == sizeof(void *) && params[i].data) {
       void *v;
       memcpy(&v, params[i].data, sizeof v);
-      ptrs.push_back(v);
+      if (is_device_pointer(s, v)) ptrs.push_back(v);
     }
   }
-  // Pointer arguments come first in every op; the scalars the lowering appends
-  // for loop bounds have pointer size too, so only the leading ones are used.
   if (deps)
     for (size_t i = 0; deps[i].event; ++i)
       CHECK_CUDA(cudaStreamWaitEvent(s->stream, static_cast<Event *>(deps[i].event)->ev, 0));
   for (void *p : ptrs) prefetch_managed(s, p);
   if (getenv("IMEX_ENABLE_PROFILING")) profile(s, k->desc, ptrs.data(), ptrs.size());
   enqueue(s, k->desc, ptrs.data(), ptrs.size());
-  auto *ev = new Event;  // never released by the caller, as in the reference
-  CHECK_CUDA(cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming));
+  Event *ev = &s->events[s->next_event++ % kEventSlots];
+  if (!ev->ev) CHECK_CUDA(cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming));
   CHECK_CUDA(cudaEventRecord(ev->ev, s->stream));
   return ev;
 }
@@ -687,10 +733,12 @@ const char *imexLastKernelName(void *stream) {
 }
 
 int64_t imexShardSize(int64_t shard, int64_t numShards, int64_t extent) {
+  if (numShards <= 0 || shard < 0 || shard >= numShards || extent < 0) return -1;
   return extent / numShards + (shard >= numShards - (extent % numShards) ? 1 : 0);
 }
 
 int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent) {
+  if (numShards <= 0 || shard < 0 || shard >= numShards || extent < 0) return -1;
   int64_t extra = shard - (numShards - (extent % numShards));
   return shard * (extent / numShards) + (extra > 0 ? extra : 0);
 }

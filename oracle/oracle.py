@@ -25,10 +25,21 @@ _u16p = C.POINTER(C.c_uint16)
 _u32p = C.POINTER(C.c_uint32)
 
 
-def build(reference="/root/reference"):
-    """Compile the oracle; also oracle/_ref when the reference checkout exists."""
+def reference_dir():
+    """The reference checkout: $IMEX_REFERENCE_DIR, else a directory `reference` beside the
+    repository; None when neither exists."""
+    for cand in (os.environ.get("IMEX_REFERENCE_DIR"),
+                 os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "lib", "ExecutionEngine")):
+            return os.path.abspath(cand)
+    return None
+
+
+def build(reference=None):
+    """Compile the oracle; also oracle/_ref when a reference checkout is found."""
     subprocess.check_call(["make", "-C", HERE, "all"], stdout=subprocess.DEVNULL)
-    if os.path.isdir(reference):
+    reference = reference or reference_dir()
+    if reference and os.path.isdir(reference):
         subprocess.check_call(["make", "-C", HERE, "ref", f"REFERENCE={reference}"],
                               stdout=subprocess.DEVNULL)
 

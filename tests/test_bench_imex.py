@@ -9,7 +9,7 @@ import pytest
 from __graft_entry__ import ROOT
 
 SCRIPT = os.path.join(ROOT, "mlir-extensions_b200", "bench_imex.py")
-REFERENCE_BENCHMARKS = "/root/reference/benchmarks"
+import reference_files  # noqa: E402  (tests/reference_files.py: checkout or staged copies)
 
 
 def _run(*args, cwd=None):
@@ -80,12 +80,12 @@ def test_dry_run_of_a_single_file_writes_the_report(tmp_path):
     assert len(kernels) == 3 and "+reduce_leading" in kernels[2]
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_BENCHMARKS), reason="no reference checkout")
 def test_the_whole_reference_grid_becomes_kernels(tmp_path):
     """Every instance of the reference's benchmark grid (7 benchmarks x shapes x f32 / f16 / bf16)
     is recognised: one launch each."""
     report = tmp_path / "report.txt"
-    r = _run("-b", "--emit-plan", "--benchmarks", REFERENCE_BENCHMARKS, "--out", str(tmp_path / "gen"),
+    benchmarks = os.path.dirname(os.path.dirname(reference_files.need("benchmarks/relu/relu.shapes.in")))
+    r = _run("-b", "--emit-plan", "--benchmarks", benchmarks, "--out", str(tmp_path / "gen"),
              "--report", str(report))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     lines = [l for l in report.read_text().splitlines() if ": kernel " in l]

@@ -19,10 +19,7 @@ from mlir_extensions_b200 import filecheck, imex_runner  # noqa: E402
 
 RUNNER = os.path.join(ROOT, "mlir-extensions_b200", "bin", "imex-b200-runner")
 MLIR = os.path.join(ROOT, "tests", "mlir")
-REFERENCE = "/root/reference"
-# a copy of a few reference test files staged under the git-ignored baseline/_ref/ (so that
-# they travel to a GPU box that has no reference checkout)
-STAGED = os.path.join(ROOT, "baseline", "_ref", "reference_tests")
+import reference_files  # noqa: E402  (tests/reference_files.py: checkout or staged copies)
 
 
 def plan(path, *extra):
@@ -125,10 +122,6 @@ def test_imex_runner_command_line(tmp_path, capsys):
     assert rc == 0 and "gpuLaunchKernel" in (tmp_path / "plan.txt").read_text()
 
 
-needs_reference = pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="no reference checkout")
-
-
-@needs_reference
 @pytest.mark.parametrize("rel,expect", [
     ("test/PlaidML/OpTest.Matmul.mlir", ["gemm"]),
     ("test/PlaidML/OpTest.GEMM_FLOAT32.mlir", ["gemm"] * 100),
@@ -141,20 +134,18 @@ needs_reference = pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="no re
     ("test/Jax/qoc/jit_swapaxes.304_linalg.mlir", ["transpose2d"]),
 ])
 def test_reference_tests_are_recognised(rel, expect):
-    rc, out, err = plan(os.path.join(REFERENCE, rel))
+    rc, out, err = plan(reference_files.need(rel))
     assert rc == 0, err
     assert [k.split()[0] for k in kernels(out)] == expect
 
 
-@needs_reference
 def test_f16_multiply_add_is_not_sent_to_the_tensor_cores():
     # test/PlaidML/CppEdsl.DotF16.mlir multiplies and adds in f16: rounding at every
     # step, which an f32-accumulating GEMM would not reproduce
-    rc, out, err = plan(os.path.join(REFERENCE, "test/PlaidML/CppEdsl.DotF16.mlir"))
+    rc, out, err = plan(reference_files.need("test/PlaidML/CppEdsl.DotF16.mlir"))
     assert rc == 1 and "f32 accumulate only" in err
 
 
-@needs_reference
 @pytest.mark.parametrize("name,subst,expect", [
     ("softmax/softmax_gpu", {"shape": "64x2000", "batch_size": "64"}, ["softmax dims=[64,2000"]),
     ("softmax/softmax_gpu", {"shape": "1024x2000", "batch_size": "1024", "dtype": "f16"},
@@ -184,7 +175,7 @@ def test_f16_multiply_add_is_not_sent_to_the_tensor_cores():
     ("kInputFusion/kInputFusion", {"dtype": "bf16"}, ["expr[5 ops, 2 inputs] bf16 +reduce_leading dims=[512,1024"]),
 ])
 def test_reference_benchmark_templates_are_recognised(tmp_path, name, subst, expect):
-    src = open(os.path.join(REFERENCE, "benchmarks", name + ".mlir.in")).read()
+    src = open(reference_files.need("benchmarks/" + name + ".mlir.in")).read()
     if subst is None:  # 3-D transpose: fill the template from the file's own placeholders
         subst = {"in_shape": "16x96x96", "out_shape": "96x16x96", "affine_map_in": "d0, d1, d2",
                  "affine_map_out": "d1, d0, d2", "perm": "1, 0, 2"}
@@ -228,15 +219,11 @@ def test_trace_shows_the_reference_call_sequence_on_the_device():
 
 
 @pytest.mark.gpu
-@pytest.mark.skipif(not (os.path.isdir(REFERENCE) or os.path.isdir(STAGED)),
-                    reason="no reference checkout or staged copy")
 @pytest.mark.parametrize("rel", ["test/PlaidML/OpTest.Matmul.mlir", "test/PlaidML/OpTest.Softmax.mlir",
                                  "test/PlaidML/OpTest.Sum.mlir", "test/PlaidML/OpTest.Transpose.mlir",
                                  "test/PlaidML/CppEdsl.Dot.mlir", "test/PlaidML/CppEdsl.DotF16_AccF32.mlir"])
 def test_reference_tests_pass_their_own_check_lines(rel):
-    path = os.path.join(REFERENCE, rel)
-    if not os.path.exists(path):
-        path = os.path.join(STAGED, os.path.basename(rel))
+    path = reference_files.need(rel)
     r = subprocess.run([sys.executable, os.path.join(ROOT, "mlir-extensions_b200", "imex_runner.py"),
                         "-i", path, "-e", "main", "--entry-point-result=void",
                         "--filecheck"], capture_output=True, text=True)
