@@ -12,7 +12,8 @@
  * `test_kernel_0`, ...): gpuKernelGet only uses it to pick the table row.
  *
  * Layout (little endian, no padding beyond what the structs show):
- *   ImexBlobHeader, then num_kernels * ImexKernelDesc.
+ *   ImexBlobHeader, then num_kernels * ImexKernelDesc, then an optional payload
+ *   (kernel text of IMEX_OP_LOOPNEST descriptors, addressed by offset).
  * The magic can never be mistaken for SPIR-V (0x07230203); a blob without it
  * is rejected through the library's error convention.
  */
@@ -69,6 +70,16 @@ extern "C" {
  *                   other; dims = {heads, n_ctx, d_head}; fparams[0] = sm_scale;
  *                   O = softmax(sm_scale * Q K^T) V per head, f32 accumulation
  *                   (test/Integration/Dialect/XeGPU/WG/flash_attention_fwd.mlir:254-330)
+ *   LOOPNEST        any other linalg.generic, lowered the way the reference's pipeline lowers
+ *                   every linalg op (benchmarks/pipelines/linalg-to-gpu.pp:3-47): a loop nest
+ *                   whose parallel loops are mapped to threads and whose reduction loops run
+ *                   serially per thread.  The kernel is CUDA C++ text in the blob's payload
+ *                   (one `extern "C" __global__ void imex_loopnest(...)`, see
+ *                   csrc/frontend/loopnest.h), compiled for sm_100a at first launch, as the
+ *                   reference's runtime compiles SPIR-V when a module is loaded.
+ *                   dims = {threads, payload offset from the start of the blob, payload
+ *                   bytes (text without NUL), number of pointer arguments}; pointers = the
+ *                   tensor inputs in order, then the outputs.
  *   FILL_UNIFORM    Y[n]  dims = {n, seed, first}; fparams = {lo, hi}
  *   FILL_NORMAL     Y[n]  dims = {n, seed, first}; fparams = {mean, stddev}
  */
@@ -84,7 +95,8 @@ enum ImexOp {
   IMEX_OP_FILL_UNIFORM = 9,
   IMEX_OP_FILL_NORMAL = 10,
   IMEX_OP_EXPR = 11,
-  IMEX_OP_ATTENTION_FWD = 12
+  IMEX_OP_ATTENTION_FWD = 12,
+  IMEX_OP_LOOPNEST = 13
 };
 
 /* Postfix code of IMEX_OP_EXPR.  Pushes take the element of input k at the current

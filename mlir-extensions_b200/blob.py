@@ -12,7 +12,7 @@ NAME_MAX = 64
 
 OP_GEMM, OP_SOFTMAX, OP_REDUCE_ROWS, OP_REDUCE_LEADING, OP_REDUCE_ALL = 1, 2, 3, 4, 5
 OP_TRANSPOSE2D, OP_TRANSPOSE3D, OP_ELTWISE, OP_FILL_UNIFORM, OP_FILL_NORMAL = 6, 7, 8, 9, 10
-OP_EXPR, OP_ATTENTION_FWD = 11, 12
+OP_EXPR, OP_ATTENTION_FWD, OP_LOOPNEST = 11, 12, 13
 F32, BF16, F16, I32 = 1, 2, 3, 4
 EPI_NONE, EPI_RELU, EPI_SILU = 0, 1, 2
 FLAG_ACCUMULATE, FLAG_BIAS, FLAG_SOFTMAX_NEG_INF, FLAG_TRANS_A, FLAG_TRANS_B = 1, 2, 4, 8, 16
@@ -37,6 +37,7 @@ class KernelDesc:
         self.sm_margin = int(sm_margin)
         self.dims = tuple(int(d) for d in dims) + (0,) * (6 - len(dims))
         self.fparams = tuple(float(f) for f in fparams)
+        self.payload = b""  # OP_LOOPNEST: the kernel's text; placed behind the table by pack_blob
 
     def pack(self):
         return _DESC.pack(self.name.encode(), self.op, self.in_dtype, self.out_dtype,
@@ -44,8 +45,16 @@ class KernelDesc:
 
 
 def pack_blob(descs):
-    """bytes of a blob holding `descs` (list of KernelDesc)."""
-    return _HEADER.pack(MAGIC, VERSION, len(descs)) + b"".join(d.pack() for d in descs)
+    """bytes of a blob holding `descs` (list of KernelDesc): header, descriptor table, then
+    the payloads (kernel text of OP_LOOPNEST descriptors, addressed by offset and length
+    in dims[1], dims[2])."""
+    table_end = _HEADER.size + len(descs) * _DESC.size
+    payload = b""
+    for d in descs:
+        if d.payload:
+            d.dims = (d.dims[0], table_end + len(payload), len(d.payload)) + tuple(d.dims[3:])
+            payload += d.payload
+    return _HEADER.pack(MAGIC, VERSION, len(descs)) + b"".join(d.pack() for d in descs) + payload
 
 
 def unpack_blob(data):
@@ -110,6 +119,16 @@ def expr(name, rows, cols, program, dtype=F32, out_dtype=None, reduce_leading=Fa
     flags = (FLAG_REDUCE_LEADING if reduce_leading else 0) | (FLAG_ACCUMULATE if accumulate else 0)
     return KernelDesc(name, OP_EXPR, dtype, dtype if out_dtype is None else out_dtype, 0, flags,
                       (rows, cols) + words, fparams=consts)
+
+
+def loopnest(name, source, threads, n_pointers):
+    """A loop-nest kernel given as CUDA C++ text: one `extern "C" __global__ void
+    imex_loopnest(pointers...)` written against the runtime's loop-nest prelude (element-type
+    helpers, IMX_THREAD_INDEX); compiled for sm_100a at first launch and run over `threads`
+    points.  Pointers = the kernel's arguments in order."""
+    d = KernelDesc(name, OP_LOOPNEST, 0, 0, 0, 0, (threads, 0, 0, n_pointers))
+    d.payload = source.encode() if isinstance(source, str) else bytes(source)
+    return d
 
 
 def attention_fwd(name, heads, n_ctx, d_head=64, dtype=F16, sm_scale=0.5):

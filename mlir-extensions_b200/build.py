@@ -34,13 +34,15 @@ RUNTIME_SOURCES = [
     "kernels/eltwise_fill.cu",
     "kernels/eltwise_expr.cu",
     "kernels/expr_jit.cu",
+    "kernels/loopnest_jit.cu",
     "kernels/flash_attention.cu",
     "kernels/wait_selftest.cu",
     "runtime/cuda_runtime_wrappers.cu",
     "runtime/stats.cpp",
 ]
 UTILS_SOURCES = ["utils/runner_utils.cpp"]
-FRONTEND_SOURCES = ["frontend/mlir_text.cpp", "frontend/recognise.cpp", "frontend/runner_main.cpp"]
+FRONTEND_SOURCES = ["frontend/mlir_text.cpp", "frontend/recognise.cpp", "frontend/loopnest.cpp",
+                    "frontend/runner_main.cpp"]
 BIN = os.path.join(PKG, "bin")
 
 

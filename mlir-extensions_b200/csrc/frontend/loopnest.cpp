@@ -1,0 +1,536 @@
+// CUDA C++ text of a linalg.generic as a loop nest; see loopnest.h.
+#include "loopnest.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <set>
+#include <sstream>
+
+namespace imex {
+namespace fe {
+namespace {
+
+bool isFloat(const std::string &e) { return e == "f32" || e == "f64" || e == "f16" || e == "bf16"; }
+bool isInt(const std::string &e) {
+  return e == "i1" || e == "i8" || e == "i16" || e == "i32" || e == "i64" || e == "index";
+}
+
+// type a value of this element type is computed in
+const char *computeType(const std::string &e) {
+  if (e == "f32" || e == "f16" || e == "bf16") return "float";
+  if (e == "f64") return "double";
+  if (e == "i1") return "bool";
+  if (e == "i8") return "signed char";
+  if (e == "i16") return "short";
+  if (e == "i32") return "int";
+  if (e == "i64" || e == "index") return "i64";
+  return nullptr;
+}
+const char *unsignedType(const std::string &e) {
+  if (e == "i8") return "unsigned char";
+  if (e == "i16") return "unsigned short";
+  if (e == "i32") return "unsigned";
+  if (e == "i64" || e == "index") return "u64";
+  return nullptr;
+}
+// type of the array elements in memory
+const char *storageType(const std::string &e) {
+  if (e == "f16" || e == "bf16") return "u16";
+  if (e == "i1") return "u8";
+  return computeType(e);
+}
+std::string loadExpr(const std::string &e, const std::string &ref) {
+  if (e == "f16") return "imx_f16_to_f32(" + ref + ")";
+  if (e == "bf16") return "imx_bf16_to_f32(" + ref + ")";
+  if (e == "i1") return "(" + ref + " != 0)";
+  return ref;
+}
+std::string storeExpr(const std::string &e, const std::string &v) {
+  if (e == "f16") return "imx_f32_to_f16(" + v + ")";
+  if (e == "bf16") return "imx_f32_to_bf16(" + v + ")";
+  if (e == "i1") return "(u8)(" + v + " ? 1 : 0)";
+  return v;
+}
+// a float result rounded to the element type it belongs to
+std::string rounded(const std::string &e, const std::string &v) {
+  if (e == "f16") return "imx_rf16(" + v + ")";
+  if (e == "bf16") return "imx_rbf16(" + v + ")";
+  return v;
+}
+
+std::string literal(const std::string &e, double v) {
+  char buf[64];
+  if (isFloat(e)) {
+    const bool dbl = e == "f64";
+    std::string s;
+    if (std::isnan(v)) s = dbl ? "imx_nan64()" : "imx_nan32()";
+    else if (std::isinf(v)) s = std::string(v < 0 ? "(-" : "(") + (dbl ? "imx_inf64()" : "imx_inf32()") + ")";
+    else {
+      if (dbl) std::snprintf(buf, sizeof buf, "(%a)", v);
+      else std::snprintf(buf, sizeof buf, "(%af)", static_cast<double>(static_cast<float>(v)));
+      s = buf;
+    }
+    return rounded(e, s);
+  }
+  if (e == "i1") return v != 0 ? "true" : "false";
+  std::snprintf(buf, sizeof buf, "((%s)%lldLL)", computeType(e), static_cast<long long>(v));
+  return buf;
+}
+
+struct Val {
+  std::string expr;  // C expression (a variable name or a literal)
+  std::string elt;
+};
+
+class BodyWriter {
+public:
+  BodyWriter(const ConstantTable &c, std::ostringstream &o, const std::string &ind) : constants(c), os(o), indent(ind) {}
+  std::map<std::string, Val> env;
+  std::string why;
+
+  Val use(const std::string &name, const std::string &eltHint) {
+    auto it = env.find(name);
+    if (it != env.end()) return it->second;
+    auto c = constants.find(name);
+    if (c != constants.end()) {
+      if (!computeType(eltHint)) {
+        why = "constant " + name + " of type " + eltHint;
+        return Val{"0", eltHint};
+      }
+      return Val{literal(eltHint, c->second), eltHint};
+    }
+    why = "body uses value " + name + " that is neither a block argument nor a known constant";
+    return Val{"0", eltHint};
+  }
+
+  std::string define(const std::string &name, const std::string &elt, const std::string &rhs) {
+    const std::string var = "v" + std::to_string(counter++);
+    os << indent << "const " << computeType(elt) << " " << var << " = " << rhs << ";\n";
+    env[name] = Val{var, elt};
+    return var;
+  }
+
+  // one operation of the region; false when it has no C counterpart
+  bool emit(const Op &o) {
+    const std::string &n = o.name;
+    const std::string fn = n.substr(n.find('.') + 1);
+    const std::string resElt = o.resultTypes.empty() ? "" : o.resultTypes[0].elt;
+    const std::string opElt = o.operandTypes.empty() ? resElt : o.operandTypes[0].elt;
+    if (!o.results.empty() && !computeType(resElt)) {
+      why = "element type " + resElt + " in " + n;
+      return false;
+    }
+    auto in = [&](size_t i, const std::string &e) { return use(o.operands[i], e).expr; };
+    const bool dbl = opElt == "f64";
+    auto mathName = [&](const std::string &base) { return dbl ? base : base + "f"; };
+
+    if (n == "arith.constant") {
+      double v = o.numbers.empty() ? 0.0 : o.numbers[0];
+      if (!o.isRaw.empty() && o.isRaw[0]) {  // hex literal: the bits of the value
+        if (resElt == "f32") {
+          uint32_t u = static_cast<uint32_t>(o.rawBits[0]);
+          float f;
+          std::memcpy(&f, &u, 4);
+          v = f;
+        } else if (resElt == "f64") {
+          std::memcpy(&v, &o.rawBits[0], 8);
+        } else if (isFloat(resElt)) {
+          why = "hex literal of type " + resElt;
+          return false;
+        } else {
+          v = static_cast<double>(static_cast<int64_t>(o.rawBits[0]));
+        }
+      }
+      define(o.results[0], resElt, literal(resElt, v));
+      return true;
+    }
+    if (n == "linalg.index") {
+      define(o.results[0], "index", "(i64)d" + std::to_string(o.intAttr));
+      return true;
+    }
+    if (n == "arith.cmpf") {
+      const std::string a = in(0, opElt), b = in(1, opElt), &p = o.predicate;
+      std::string e;
+      if (p == "oeq") e = a + " == " + b;
+      else if (p == "ogt") e = a + " > " + b;
+      else if (p == "oge") e = a + " >= " + b;
+      else if (p == "olt") e = a + " < " + b;
+      else if (p == "ole") e = a + " <= " + b;
+      else if (p == "one") e = "(" + a + " < " + b + ") || (" + a + " > " + b + ")";
+      else if (p == "ord") e = "(" + a + " == " + a + ") && (" + b + " == " + b + ")";
+      else if (p == "ueq") e = "!((" + a + " < " + b + ") || (" + a + " > " + b + "))";
+      else if (p == "ugt") e = "!(" + a + " <= " + b + ")";
+      else if (p == "uge") e = "!(" + a + " < " + b + ")";
+      else if (p == "ult") e = "!(" + a + " >= " + b + ")";
+      else if (p == "ule") e = "!(" + a + " > " + b + ")";
+      else if (p == "une") e = a + " != " + b;
+      else if (p == "uno") e = "(" + a + " != " + a + ") || (" + b + " != " + b + ")";
+      else if (p == "false" || p == "true") e = p;
+      else { why = "cmpf predicate " + p; return false; }
+      define(o.results[0], "i1", "(" + e + ")");
+      return true;
+    }
+    if (n == "arith.cmpi") {
+      std::string a = in(0, opElt), b = in(1, opElt);
+      const std::string &p = o.predicate;
+      if (p[0] == 'u' && opElt != "i1") {
+        const char *ut = unsignedType(opElt);
+        if (!ut) { why = "cmpi on " + opElt; return false; }
+        a = "(" + std::string(ut) + ")" + a;
+        b = "(" + std::string(ut) + ")" + b;
+      }
+      const char *c = p == "eq" ? "==" : p == "ne" ? "!=" : (p == "slt" || p == "ult") ? "<"
+                    : (p == "sle" || p == "ule") ? "<=" : (p == "sgt" || p == "ugt") ? ">"
+                    : (p == "sge" || p == "uge") ? ">=" : nullptr;
+      if (!c) { why = "cmpi predicate " + p; return false; }
+      define(o.results[0], "i1", "(" + a + " " + c + " " + b + ")");
+      return true;
+    }
+    if (n == "arith.select") {
+      define(o.results[0], resElt, "(" + in(0, "i1") + " ? " + in(1, resElt) + " : " + in(2, resElt) + ")");
+      return true;
+    }
+    // ---- conversions ------------------------------------------------------------
+    if (n == "arith.extf" || n == "arith.truncf") {
+      const std::string a = in(0, opElt);
+      if (resElt == "f64") define(o.results[0], resElt, "(double)" + a);
+      else define(o.results[0], resElt, rounded(resElt, "(float)" + a));
+      return true;
+    }
+    if (n == "arith.sitofp" || n == "arith.uitofp") {
+      std::string a = in(0, opElt);
+      if (opElt == "i1") a = n == "arith.sitofp" ? "(" + a + " ? -1 : 0)" : "(" + a + " ? 1 : 0)";
+      else if (n == "arith.uitofp") a = "(" + std::string(unsignedType(opElt)) + ")" + a;
+      define(o.results[0], resElt, rounded(resElt, "(" + std::string(computeType(resElt)) + ")" + a));
+      return true;
+    }
+    if (n == "arith.fptosi" || n == "arith.fptoui") {
+      const std::string a = in(0, opElt);
+      if (resElt == "i1") define(o.results[0], resElt, "(((int)" + a + ") & 1) != 0");
+      else if (n == "arith.fptoui")
+        define(o.results[0], resElt, "(" + std::string(computeType(resElt)) + ")(" + unsignedType(resElt) + ")" + a);
+      else define(o.results[0], resElt, "(" + std::string(computeType(resElt)) + ")" + a);
+      return true;
+    }
+    if (n == "arith.extsi" || n == "arith.extui" || n == "arith.trunci" || n == "arith.index_cast" ||
+        n == "arith.index_castui") {
+      std::string a = in(0, opElt);
+      if (opElt == "i1") a = n == "arith.extsi" ? "(" + a + " ? -1 : 0)" : "(" + a + " ? 1 : 0)";
+      else if (n == "arith.extui" || n == "arith.index_castui") a = "(" + std::string(unsignedType(opElt)) + ")" + a;
+      if (resElt == "i1") define(o.results[0], resElt, "((" + a + " & 1) != 0)");
+      else define(o.results[0], resElt, "(" + std::string(computeType(resElt)) + ")" + a);
+      return true;
+    }
+    if (n == "arith.bitcast") {
+      const std::string a = in(0, opElt);
+      if (opElt == "f32" && resElt == "i32") define(o.results[0], resElt, "imx_f32_bits(" + a + ")");
+      else if (opElt == "i32" && resElt == "f32") define(o.results[0], resElt, "imx_bits_f32(" + a + ")");
+      else { why = "bitcast " + opElt + " to " + resElt; return false; }
+      return true;
+    }
+    // ---- float arithmetic ------------------------------------------------------------
+    if (isFloat(resElt) && !o.operands.empty()) {
+      static const std::map<std::string, const char *> infix = {
+          {"addf", "+"}, {"subf", "-"}, {"mulf", "*"}, {"divf", "/"}};
+      auto ix = infix.find(fn);
+      if (n.rfind("arith.", 0) == 0 && ix != infix.end() && o.operands.size() == 2) {
+        define(o.results[0], resElt, rounded(resElt, "(" + in(0, resElt) + " " + ix->second + " " + in(1, resElt) + ")"));
+        return true;
+      }
+      if (n == "arith.negf") {
+        define(o.results[0], resElt, "(-" + in(0, resElt) + ")");
+        return true;
+      }
+      if (n == "arith.remf") {
+        define(o.results[0], resElt, rounded(resElt, mathName("fmod") + "(" + in(0, resElt) + ", " + in(1, resElt) + ")"));
+        return true;
+      }
+      static const std::map<std::string, const char *> minmax = {
+          {"maximumf", "imx_maximum"}, {"maxf", "imx_maximum"}, {"minimumf", "imx_minimum"},
+          {"minf", "imx_minimum"}, {"maxnumf", "imx_maxnum"}, {"minnumf", "imx_minnum"}};
+      auto mm = minmax.find(fn);
+      if (n.rfind("arith.", 0) == 0 && mm != minmax.end()) {
+        define(o.results[0], resElt, std::string(mm->second) + "(" + in(0, resElt) + ", " + in(1, resElt) + ")");
+        return true;
+      }
+      if (n.rfind("math.", 0) == 0) {
+        static const std::map<std::string, const char *> unary = {
+            {"exp", "exp"}, {"exp2", "exp2"}, {"expm1", "expm1"}, {"log", "log"}, {"log2", "log2"},
+            {"log10", "log10"}, {"log1p", "log1p"}, {"sqrt", "sqrt"}, {"cbrt", "cbrt"}, {"tanh", "tanh"},
+            {"sin", "sin"}, {"cos", "cos"}, {"tan", "tan"}, {"atan", "atan"}, {"asin", "asin"},
+            {"acos", "acos"}, {"sinh", "sinh"}, {"cosh", "cosh"}, {"asinh", "asinh"}, {"acosh", "acosh"},
+            {"atanh", "atanh"}, {"erf", "erf"}, {"floor", "floor"}, {"ceil", "ceil"}, {"absf", "fabs"},
+            {"round", "round"}, {"roundeven", "rint"}, {"trunc", "trunc"}};
+        static const std::map<std::string, const char *> binary = {
+            {"powf", "pow"}, {"atan2", "atan2"}, {"copysign", "copysign"}};
+        auto u = unary.find(fn);
+        if (u != unary.end() && o.operands.size() == 1) {
+          define(o.results[0], resElt, rounded(resElt, mathName(u->second) + "(" + in(0, resElt) + ")"));
+          return true;
+        }
+        auto b = binary.find(fn);
+        if (b != binary.end() && o.operands.size() == 2) {
+          define(o.results[0], resElt,
+                 rounded(resElt, mathName(b->second) + "(" + in(0, resElt) + ", " + in(1, resElt) + ")"));
+          return true;
+        }
+        if (fn == "rsqrt") {  // expanded to 1 / sqrt(x) by the CPU pipeline
+          define(o.results[0], resElt, rounded(resElt, "(" + std::string(dbl ? "1.0" : "1.0f") + " / " +
+                                                           mathName("sqrt") + "(" + in(0, resElt) + "))"));
+          return true;
+        }
+        if (fn == "fma" && o.operands.size() == 3) {
+          define(o.results[0], resElt, rounded(resElt, mathName("fma") + "(" + in(0, resElt) + ", " + in(1, resElt) +
+                                                           ", " + in(2, resElt) + ")"));
+          return true;
+        }
+      }
+    }
+    // ---- integer arithmetic (wrapping) -----------------------------------------------
+    if (isInt(resElt) && o.operands.size() == 2 && n.rfind("arith.", 0) == 0) {
+      const std::string a = in(0, resElt), b = in(1, resElt);
+      if (resElt == "i1") {
+        const char *c = (fn == "andi" || fn == "muli") ? "&&" : fn == "ori" ? "||" : (fn == "xori" || fn == "addi" || fn == "subi") ? "!=" : nullptr;
+        if (!c) { why = n + " on i1"; return false; }
+        define(o.results[0], resElt, "(" + a + " " + c + " " + b + ")");
+        return true;
+      }
+      const std::string T = computeType(resElt), U = unsignedType(resElt);
+      auto wrap = [&](const char *c) { return "(" + T + ")((" + U + ")" + a + " " + c + " (" + U + ")" + b + ")"; };
+      std::string e;
+      if (fn == "addi") e = wrap("+");
+      else if (fn == "subi") e = wrap("-");
+      else if (fn == "muli") e = wrap("*");
+      else if (fn == "andi") e = wrap("&");
+      else if (fn == "ori") e = wrap("|");
+      else if (fn == "xori") e = wrap("^");
+      else if (fn == "shli") e = wrap("<<");
+      else if (fn == "shrui") e = wrap(">>");
+      else if (fn == "divui") e = wrap("/");
+      else if (fn == "remui") e = wrap("%");
+      else if (fn == "shrsi") e = "(" + T + ")(" + a + " >> " + b + ")";
+      else if (fn == "divsi") e = "(" + T + ")(" + a + " / " + b + ")";
+      else if (fn == "remsi") e = "(" + T + ")(" + a + " % " + b + ")";
+      else if (fn == "maxsi") e = "(" + a + " > " + b + " ? " + a + " : " + b + ")";
+      else if (fn == "minsi") e = "(" + a + " < " + b + " ? " + a + " : " + b + ")";
+      else if (fn == "maxui") e = "((" + U + ")" + a + " > (" + U + ")" + b + " ? " + a + " : " + b + ")";
+      else if (fn == "minui") e = "((" + U + ")" + a + " < (" + U + ")" + b + " ? " + a + " : " + b + ")";
+      else { why = "integer operation " + n; return false; }
+      define(o.results[0], resElt, e);
+      return true;
+    }
+    if (n == "math.absi" && o.operands.size() == 1) {
+      const std::string a = in(0, resElt);
+      define(o.results[0], resElt, "(" + a + " < 0 ? (" + computeType(resElt) + ")(-" + a + ") : " + a + ")");
+      return true;
+    }
+    why = "operation " + n + " has no loop-nest translation";
+    return false;
+  }
+
+private:
+  const ConstantTable &constants;
+  std::ostringstream &os;
+  std::string indent;
+  int counter = 0;
+};
+
+} // namespace
+
+bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why) {
+  if (op.name != "linalg.generic" || !op.body) {
+    why = "not a linalg.generic";
+    return false;
+  }
+  const size_t nIn = op.ins.size(), nOut = op.outs.size();
+  if (nOut == 0 || op.maps.size() != nIn + nOut || op.body->args.size() != nIn + nOut) {
+    why = "operand, map and block-argument counts disagree";
+    return false;
+  }
+  const int nd = op.maps[0].numDims;
+  if (static_cast<int>(op.iterators.size()) != nd) {
+    why = "iterator_types do not match the maps";
+    return false;
+  }
+  for (auto &m : op.maps)
+    if (m.numDims != nd) {
+      why = "indexing maps over different iteration spaces";
+      return false;
+    }
+  auto typeOf = [&](size_t k) -> const Type & { return k < nIn ? op.insTypes[k] : op.outsTypes[k - nIn]; };
+  for (size_t k = 0; k < nIn + nOut; ++k) {
+    const Type &t = typeOf(k);
+    if (!computeType(t.elt)) {
+      why = "element type " + t.elt;
+      return false;
+    }
+    if (t.isShaped()) {
+      if (t.unranked) { why = "unranked operand"; return false; }
+      for (auto d : t.shape)
+        if (d < 0) { why = "dynamic shape"; return false; }
+      if (t.shape.size() != op.maps[k].results.size()) { why = "map rank differs from operand rank"; return false; }
+    } else if (k >= nIn) {
+      why = "scalar output";
+      return false;
+    }
+  }
+  // extents of the iteration dimensions, from the operands they index directly
+  std::vector<int64_t> extent(nd, -1);
+  for (size_t k = 0; k < nIn + nOut; ++k) {
+    const Type &t = typeOf(k);
+    if (!t.isShaped()) continue;
+    for (size_t r = 0; r < op.maps[k].results.size(); ++r) {
+      const MapResult &mr = op.maps[k].results[r];
+      if (!mr.simple || mr.isConst) continue;
+      if (extent[mr.value] >= 0 && extent[mr.value] != t.shape[r]) {
+        why = "operands disagree on the extent of d" + std::to_string(mr.value);
+        return false;
+      }
+      extent[mr.value] = t.shape[r];
+    }
+  }
+  for (int d = 0; d < nd; ++d)
+    if (extent[d] < 0) {
+      why = "extent of d" + std::to_string(d) + " cannot be inferred";
+      return false;
+    }
+  std::vector<int> par, red;
+  for (int d = 0; d < nd; ++d) (op.iterators[d] == "reduction" ? red : par).push_back(d);
+  // outputs: indexed by parallel dimensions only, and by all of them
+  for (size_t k = nIn; k < nIn + nOut; ++k) {
+    std::set<int> used;
+    for (auto &mr : op.maps[k].results) {
+      if (!mr.simple) { why = "output indexed by a compound expression"; return false; }
+      if (!mr.isConst) used.insert(static_cast<int>(mr.value));
+    }
+    for (int d : red)
+      if (used.count(d)) { why = "output indexed by a reduction dimension"; return false; }
+    for (int d : par)
+      if (!used.count(d) && extent[d] > 1) { why = "parallel dimension missing from an output map"; return false; }
+  }
+
+  auto linearIndex = [&](size_t k) {
+    const Type &t = typeOf(k);
+    std::string e;
+    int64_t stride = 1;
+    for (int r = static_cast<int>(t.shape.size()) - 1; r >= 0; --r) {
+      std::string term = "(i64)(" + op.maps[k].results[r].expr + ")";
+      if (stride != 1) term += " * " + std::to_string(stride) + "LL";
+      e = e.empty() ? term : term + " + " + e;
+      stride *= t.shape[r];
+    }
+    return e.empty() ? std::string("0") : e;
+  };
+
+  out.threads = 1;
+  for (int d : par) out.threads *= extent[d];
+  if (out.threads < 0 || out.threads > (int64_t(1) << 40)) { why = "iteration space too large"; return false; }
+  for (int64_t e : extent)
+    if (e == 0) out.threads = 0;
+
+  // does the region read an output's block argument?
+  std::set<std::string> usedNames;
+  for (auto &o : op.body->ops)
+    for (auto &v : o->operands) usedNames.insert(v);
+  out.readsInit.assign(nOut, false);
+  for (size_t k = 0; k < nOut; ++k) out.readsInit[k] = !red.empty() || usedNames.count(op.body->args[nIn + k]) != 0;
+
+  std::ostringstream os;
+  os << "extern \"C\" __global__ void imex_loopnest(";
+  out.pointerInputs.clear();
+  bool first = true;
+  for (size_t k = 0; k < nIn; ++k) {
+    if (!typeOf(k).isShaped()) continue;
+    out.pointerInputs.push_back(static_cast<int>(k));
+    os << (first ? "" : ", ") << "const " << storageType(typeOf(k).elt) << " *__restrict__ in" << k;
+    first = false;
+  }
+  for (size_t k = 0; k < nOut; ++k) {
+    os << (first ? "" : ", ") << storageType(typeOf(nIn + k).elt) << " *__restrict__ out" << k;
+    first = false;
+  }
+  os << ") {\n"
+     << "  const i64 p = IMX_THREAD_INDEX;\n"
+     << "  if (p >= " << out.threads << "LL) return;\n"
+     << "  i64 q = p;\n";
+  for (int i = static_cast<int>(par.size()) - 1; i >= 0; --i) {
+    const int d = par[i];
+    if (i == 0) os << "  const i64 d" << d << " = q;\n";
+    else os << "  const i64 d" << d << " = q % " << extent[d] << "LL; q /= " << extent[d] << "LL;\n";
+  }
+  os << "  (void)q;\n";
+  for (size_t k = 0; k < nOut; ++k) {
+    const std::string &e = typeOf(nIn + k).elt;
+    os << "  const i64 o" << k << " = " << linearIndex(nIn + k) << ";\n";
+    os << "  " << computeType(e) << " acc" << k << " = ";
+    if (out.readsInit[k]) os << loadExpr(e, "out" + std::to_string(k) + "[o" + std::to_string(k) + "]") << ";\n";
+    else os << literal(e, 0.0) << ";\n";
+  }
+  std::string indent = "  ";
+  for (int d : red) {
+    os << indent << "for (i64 d" << d << " = 0; d" << d << " < " << extent[d] << "LL; ++d" << d << ") {\n";
+    indent += "  ";
+  }
+  BodyWriter body(constants, os, indent);
+  for (size_t k = 0; k < nIn; ++k) {
+    const Type &t = typeOf(k);
+    const std::string &arg = op.body->args[k];
+    if (!t.isShaped()) {  // a scalar operand: its value is known when the kernel is written
+      auto c = constants.find(op.ins[k]);
+      if (c == constants.end()) { why = "scalar operand " + op.ins[k] + " is not a known constant"; return false; }
+      body.env[arg] = Val{literal(t.elt, c->second), t.elt};
+      continue;
+    }
+    if (!usedNames.count(arg)) {
+      bool yielded = false;
+      for (auto &o : op.body->ops)
+        if (o->name == "linalg.yield")
+          for (auto &v : o->operands) yielded = yielded || v == arg;
+      if (!yielded) continue;  // never read: no load
+    }
+    os << indent << "const " << computeType(t.elt) << " a" << k << " = "
+       << loadExpr(t.elt, "in" + std::to_string(k) + "[" + linearIndex(k) + "]") << ";\n";
+    body.env[arg] = Val{"a" + std::to_string(k), t.elt};
+  }
+  for (size_t k = 0; k < nOut; ++k)
+    body.env[op.body->args[nIn + k]] = Val{"acc" + std::to_string(k), typeOf(nIn + k).elt};
+  bool yielded = false;
+  for (auto &o : op.body->ops) {
+    if (o->name == "linalg.yield") {
+      if (o->operands.size() != nOut) { why = "yield count differs from the outputs"; return false; }
+      // all yielded values are read before any accumulator is overwritten
+      std::vector<std::string> vals;
+      for (size_t k = 0; k < nOut; ++k) vals.push_back(body.use(o->operands[k], typeOf(nIn + k).elt).expr);
+      if (nOut > 1)
+        for (size_t k = 0; k < nOut; ++k)
+          os << indent << "const " << computeType(typeOf(nIn + k).elt) << " y" << k << " = " << vals[k] << ";\n";
+      for (size_t k = 0; k < nOut; ++k)
+        os << indent << "acc" << k << " = " << (nOut > 1 ? "y" + std::to_string(k) : vals[k]) << ";\n";
+      yielded = true;
+      continue;
+    }
+    if (!body.emit(*o)) {
+      why = body.why;
+      return false;
+    }
+  }
+  if (!body.why.empty()) { why = body.why; return false; }
+  if (!yielded) { why = "region without linalg.yield"; return false; }
+  for (size_t i = 0; i < red.size(); ++i) {
+    indent.resize(indent.size() - 2);
+    os << indent << "}\n";
+  }
+  for (size_t k = 0; k < nOut; ++k)
+    os << "  out" << k << "[o" << k << "] = " << storeExpr(typeOf(nIn + k).elt, "acc" + std::to_string(k)) << ";\n";
+  os << "}\n";
+  out.source = os.str();
+  std::ostringstream sum;
+  sum << "loopnest[" << par.size() << " parallel, " << red.size() << " reduction dims, " << out.threads << " threads]";
+  out.summary = sum.str();
+  return true;
+}
+
+} // namespace fe
+} // namespace imex

@@ -1,0 +1,41 @@
+// Loop-nest kernels: any linalg.generic that is none of the recognised hot-path ops.
+//
+// The reference's GPU pipeline turns every linalg op into a loop nest, maps the parallel
+// loops to work-items and outlines one kernel per nest, each work-item running the
+// reduction loops serially (benchmarks/pipelines/linalg-to-gpu.pp:3-47; the result for a
+// matmul is test/SPIRV/OpTest.GEMM_BF16_ACC_F32.mlir:129-140).  This is the same lowering
+// written out as CUDA C++ text: one thread per point of the parallel iteration space, the
+// reduction dimensions as ascending serial loops around the region's body, every body
+// operation evaluated in the IR's element type (f16 / bf16: operate in f32, round after
+// every operation; integers wrap).  Per output element the sequence of operations is
+// exactly that of linalg-to-loops on the CPU, so exactly-rounded bodies give bit-identical
+// results.  The text travels in the kernel blob (IMEX_OP_LOOPNEST) and the runtime
+// compiles it for sm_100a when the module is first launched, as the reference's runtime
+// compiles SPIR-V at gpuModuleLoad.
+#pragma once
+
+#include "mlir_text.h"
+#include "recognise.h"
+
+#include <string>
+#include <vector>
+
+namespace imex {
+namespace fe {
+
+struct LoopNestKernel {
+  std::string source;               // one `extern "C" __global__ void imex_loopnest(...)`
+  std::vector<int> pointerInputs;   // indices into op.ins passed as pointers, in argument order
+                                    // (scalar ins are written into the text as literals)
+  std::vector<bool> readsInit;      // per output: the kernel reads the output's initial contents
+  int64_t threads = 1;              // points of the parallel iteration space
+  std::string summary;              // for plans and diagnostics
+};
+
+// False (with `why`) when the op cannot be written as a loop nest: dynamic shapes, an
+// operation or element type without a C counterpart, an output indexed by a reduction
+// dimension, or a parallel dimension missing from an output's map.
+bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why);
+
+} // namespace fe
+} // namespace imex

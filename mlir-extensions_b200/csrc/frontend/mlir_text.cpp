@@ -186,7 +186,10 @@ private:
       ++pos;
       return s.substr(b, pos - b);
     }
-    while (!eof() && identChar(s[pos])) ++pos;
+    while (!eof() && (identChar(s[pos]) ||
+                      // value names may hold '-' (%c-1_i8), never directly before '>'
+                      (s[b] == '%' && s[pos] == '-' && pos + 1 < s.size() && identChar(s[pos + 1]))))
+      ++pos;
     if (s[b] == '%' && peek() == '#') {  // result index
       ++pos;
       while (!eof() && std::isdigit(static_cast<unsigned char>(s[pos]))) ++pos;
@@ -386,27 +389,101 @@ private:
     skip();
     if (peek() != ')') {
       do {
-        skip();
+        AffineTerm t = affineSum(dims);
         MapResult r;
-        if (std::isdigit(static_cast<unsigned char>(peek())) || peek() == '-') {
+        r.expr = t.text;
+        if (t.kind == AffineTerm::Const) {
           r.isConst = true;
-          r.value = static_cast<int64_t>(number().value);
+          r.value = t.value;
+        } else if (t.kind == AffineTerm::Dim) {
+          r.value = t.value;
         } else {
-          std::string d = ident();
-          int idx = -1;
-          for (size_t i = 0; i < dims.size(); ++i)
-            if (dims[i] == d) idx = static_cast<int>(i);
-          if (idx < 0) fail("unknown dimension '" + d + "' in affine map");
-          r.value = idx;
+          r.simple = false;
+          r.value = -1;
         }
-        skip();
-        if (peek() == '+' || peek() == '*' || peek() == '-')
-          fail("affine map results other than a dimension or a constant are not supported");
         m.results.push_back(r);
       } while (accept(','));
     }
     expect(')');
     return m;
+  }
+  // affine expressions: sums of products of dimensions and constants, floordiv / ceildiv /
+  // mod by constants, parentheses.  Dimensions are non-negative, so C's `/` and `%` agree
+  // with floordiv and mod for the positive divisors the syntax allows.
+  struct AffineTerm {
+    enum { Const, Dim, Other } kind = Other;
+    int64_t value = 0;
+    std::string text;
+  };
+  AffineTerm affineAtom(const std::vector<std::string> &dims) {
+    skip();
+    AffineTerm t;
+    if (peek() == '(') {
+      ++pos;
+      t = affineSum(dims);
+      expect(')');
+      if (t.kind == AffineTerm::Other) t.text = "(" + t.text + ")";
+      return t;
+    }
+    if (peek() == '-') {
+      ++pos;
+      AffineTerm a = affineAtom(dims);
+      if (a.kind == AffineTerm::Const) {
+        a.value = -a.value;
+        a.text = std::to_string(a.value);
+        return a;
+      }
+      t.text = "(-" + a.text + ")";
+      return t;
+    }
+    if (std::isdigit(static_cast<unsigned char>(peek()))) {
+      t.kind = AffineTerm::Const;
+      t.value = static_cast<int64_t>(number().value);
+      t.text = std::to_string(t.value);
+      return t;
+    }
+    std::string d = ident();
+    int idx = -1;
+    for (size_t i = 0; i < dims.size(); ++i)
+      if (dims[i] == d) idx = static_cast<int>(i);
+    if (idx < 0) fail("unknown dimension '" + d + "' in affine map");
+    t.kind = AffineTerm::Dim;
+    t.value = idx;
+    t.text = "d" + std::to_string(idx);
+    return t;
+  }
+  AffineTerm affineProduct(const std::vector<std::string> &dims) {
+    AffineTerm a = affineAtom(dims);
+    for (;;) {
+      skip();
+      const char *op = nullptr;
+      if (peek() == '*') { ++pos; op = "*"; }
+      else if (acceptWord("floordiv")) op = "/";
+      else if (acceptWord("ceildiv")) op = "ceil";
+      else if (acceptWord("mod")) op = "%";
+      else break;
+      AffineTerm b = affineAtom(dims);
+      AffineTerm r;
+      if (std::string(op) == "ceil") r.text = "((" + a.text + " + " + b.text + " - 1) / " + b.text + ")";
+      else r.text = "(" + a.text + " " + op + " " + b.text + ")";
+      a = r;
+    }
+    return a;
+  }
+  AffineTerm affineSum(const std::vector<std::string> &dims) {
+    AffineTerm a = affineProduct(dims);
+    for (;;) {
+      skip();
+      char op = peek();
+      if (op != '+' && op != '-') break;
+      if (op == '-' && pos + 1 < s.size() && s[pos + 1] == '>') break;  // the map's arrow
+      ++pos;
+      AffineTerm b = affineProduct(dims);
+      AffineTerm r;
+      r.text = "(" + a.text + " " + op + " " + b.text + ")";
+      a = r;
+    }
+    return a;
   }
   AffineMap mapRefOrInline() {
     skip();
@@ -792,15 +869,22 @@ private:
       expect('{');
       block(*op->body, /*allowLabel=*/false);
     } else if (n.rfind("arith.", 0) == 0 || n.rfind("math.", 0) == 0) {
-      // unary / binary scalar ops: "%r = arith.addf %a, %b [fastmath<..>] : f32"
+      // unary / binary scalar ops: "%r = arith.addf %a, %b [fastmath<..>] : f32", and the
+      // conversions written "%r = arith.extui %a : i8 to i32"
       operandList(op->operands);
       skip();
       if (startsWith("fastmath")) {
         pos += 8;
         skipBalanced('<', '>');
       }
+      skip();
+      if (peek() == '{') skipBalanced('{', '}');  // e.g. {overflowFlags = ...}
       expect(':');
-      op->resultTypes.push_back(type());
+      Type from = type();
+      Type to = from;
+      if (acceptWord("to")) to = type();
+      op->operandTypes.push_back(from);
+      op->resultTypes.push_back(to);
     } else {
       fail("operation '" + n + "' is outside the supported subset");
     }

@@ -35,10 +35,15 @@ struct Type {
   std::string str() const;
 };
 
-// One result of an affine map: a loop dimension or a constant.
+// One result of an affine map.  The hot-path kernels only take a loop dimension or a
+// constant (`simple`); anything else (d1 + d3, d1 floordiv 3, 2 * d0 ...) keeps its text as
+// a C expression over d0, d1, ... for the loop-nest kernels and matches no recognised op
+// (value = -1).
 struct MapResult {
   bool isConst = false;
-  int64_t value = 0;  // dimension index or the constant
+  int64_t value = 0;     // dimension index or the constant; -1 when not simple
+  bool simple = true;
+  std::string expr;      // C expression over d0.. (always set)
 };
 struct AffineMap {
   int numDims = 0;
@@ -77,6 +82,7 @@ struct Op {
   std::string callee;                  // "@printMemrefF32"
   std::string predicate;               // cmpf / cmpi predicate
   int64_t intAttr = 0;                 // linalg.index dimension
+  std::vector<Type> bodyOperandTypes;  // per operand of a scalar op, when the syntax gives them
   std::vector<std::vector<int64_t>> reassociation;  // expand/collapse_shape
   std::vector<std::string> iterArgs, iterInits;     // scf.for iter_args
 };

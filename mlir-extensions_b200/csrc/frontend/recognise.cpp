@@ -235,18 +235,23 @@ Classified classify(const Op &op, const ConstantTable &constants) {
         static_cast<int>(inMap.results.size()) == nd) {
       // position of loop dim d in the input / output
       std::vector<int> inPos(nd, -1), outPos(nd, -1);
+      bool permutation = true;
       for (int i = 0; i < nd; ++i) {
-        if (inMap.results[i].isConst || outMap.results[i].isConst) {
-          c.why = "broadcasting copy";
-          return c;
+        const MapResult &ri = inMap.results[i], &ro = outMap.results[i];
+        if (ri.isConst || ro.isConst || !ri.simple || !ro.simple) {
+          permutation = false;
+          break;
         }
-        inPos[inMap.results[i].value] = i;
-        outPos[outMap.results[i].value] = i;
+        if (inPos[ri.value] >= 0 || outPos[ro.value] >= 0) permutation = false;  // a dim used twice
+        inPos[ri.value] = i;
+        outPos[ro.value] = i;
       }
-      c.perm.assign(nd, 0);
-      for (int d = 0; d < nd; ++d) c.perm[outPos[d]] = inPos[d];
-      c.kind = Kind::Transpose;
-      return c;
+      if (permutation) {
+        c.perm.assign(nd, 0);
+        for (int d = 0; d < nd; ++d) c.perm[outPos[d]] = inPos[d];
+        c.kind = Kind::Transpose;
+        return c;
+      }
     }
   }
   bool identityAll = true;

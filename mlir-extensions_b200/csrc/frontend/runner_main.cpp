@@ -16,12 +16,13 @@
 // IR that matches nothing is an error (exit 1): there is no CPU fallback.
 //
 //   imex-b200-runner FILE.mlir [-e main] [--entry-point-result=void]
-//                    [--shared-libs=...] [--emit-plan] [--trace]
+//                    [--shared-libs=...] [--emit-plan] [--trace] [--all-loopnests]
 // --emit-plan: recognise and print the kernels and ABI calls without touching
 //              a GPU.   --trace (or IMEX_B200_TRACE=1): log ABI calls to stderr.
 #include "../../../include/imex_b200_blob.h"
 #include "../../../include/imex_cuda_runtime.h"
 #include "../../../include/imex_runner_utils.h"
+#include "loopnest.h"
 #include "mlir_text.h"
 #include "recognise.h"
 
@@ -42,6 +43,10 @@ namespace {
 
 bool g_plan = false;   // --emit-plan: no GPU calls
 bool g_trace = false;  // log ABI calls
+// --all-loopnests: recognise nothing; every linalg op becomes the loop nest that the
+// reference's linalg-to-loops lowering makes of it (a self-check of the hot-path kernels
+// against the plain lowering, and the mode the CPU checker under oracle/ runs in)
+bool g_allLoopNests = false;
 
 [[noreturn]] void die(const std::string &msg) {
   std::cout.flush();
@@ -102,6 +107,23 @@ uint16_t f32ToF16(float v) {
   uint32_t r = base + q;
   if (r > 0x7c00u) r = 0x7c00u;
   return sign | static_cast<uint16_t>(r);
+}
+
+float f16BitsToF32(uint16_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+  uint32_t u;
+  if (exp == 0x1f) u = sign | 0x7f800000u | (man << 13);
+  else if (exp != 0) u = sign | ((exp + 112u) << 23) | (man << 13);
+  else if (man == 0) u = sign;
+  else {  // subnormal: normalise
+    int e = -1;
+    uint32_t m = man;
+    do { ++e; m <<= 1; } while (!(m & 0x400u));
+    u = sign | ((112u - e) << 23) | ((m & 0x3ffu) << 13);
+  }
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
 }
 
 // ---- runtime values ---------------------------------------------------------
@@ -166,6 +188,7 @@ private:
   std::map<const Op *, SoftmaxPlan> pendingSoftmax;  // keyed by the chain's final divide
   int kernelCounter = 0;
   void *curStream = nullptr;  // stream of the function being interpreted
+  const std::map<std::string, int> *curUses = nullptr;  // use counts of that function (nested bodies included)
   std::vector<std::unique_ptr<std::vector<char>>> blobs;  // modules are cached by blob address
 
   // ---- device helpers ---------------------------------------------------
@@ -231,10 +254,16 @@ private:
   }
 
   // One kernel: module with one descriptor, loaded, looked up, launched, waited for.
-  void launch(void *stream, ImexKernelDesc d, const std::vector<void *> &ptrs, const std::string &what) {
+  void launch(void *stream, ImexKernelDesc d, const std::vector<void *> &ptrs, const std::string &what,
+              const std::string &payload = std::string()) {
     std::snprintf(d.name, sizeof d.name, "imex_b200_kernel_%d", kernelCounter++);
-    auto blob = std::make_unique<std::vector<char>>(sizeof(ImexBlobHeader) + sizeof(ImexKernelDesc));
+    auto blob = std::make_unique<std::vector<char>>(sizeof(ImexBlobHeader) + sizeof(ImexKernelDesc) + payload.size());
     ImexBlobHeader h{IMEX_BLOB_MAGIC, IMEX_BLOB_VERSION, 1};
+    if (!payload.empty()) {  // kernel text behind the descriptor table
+      d.dims[1] = static_cast<int64_t>(sizeof h + sizeof d);
+      d.dims[2] = static_cast<int64_t>(payload.size());
+      std::memcpy(blob->data() + sizeof h + sizeof d, payload.data(), payload.size());
+    }
     std::memcpy(blob->data(), &h, sizeof h);
     std::memcpy(blob->data() + sizeof h, &d, sizeof d);
     std::ostringstream os;
@@ -279,9 +308,12 @@ private:
     std::map<std::string, int> uses;
     index(f.body, defs, uses);
     void *outerStream = curStream;
+    const std::map<std::string, int> *outerUses = curUses;
     curStream = stream;
+    curUses = &uses;
     std::vector<Value> results = runBlock(f.body, fr, stream, absorbed, defs, uses);
     curStream = outerStream;
+    curUses = outerUses;
     fr.vals.clear();  // frees this function's buffers (results hold their own references)
     if (!g_plan) {
       // results must outlive the stream handle they were allocated with
@@ -299,6 +331,7 @@ private:
       for (auto &v : o->operands) uses[v]++;
       for (auto &v : o->ins) uses[v]++;
       for (auto &v : o->outs) uses[v]++;
+      for (auto &v : o->iterInits) uses[v]++;
       if (o->body && o->name == "scf.for") index(*o->body, defs, uses);
     }
   }
@@ -454,13 +487,20 @@ private:
   // it at the loop point, or the column reduce of kInputFusion.mlir.in:29-39).
   void elementwiseOp(const Op &op, const Block &b, Frame &fr, const std::string &where) {
     ElementwiseInfo info;
-    if (!classifyElementwise(op, fr.constants, info))
-      die(where + op.name + " is not a recognised hot-path op; no CPU fallback");
     const Type outT = op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0];
-    if (outT.elt != "f32" && outT.elt != "f16" && outT.elt != "bf16") die(where + "elementwise ops on " + outT.elt);
+    bool fusable = classifyElementwise(op, fr.constants, info) &&
+                   (outT.elt == "f32" || outT.elt == "f16" || outT.elt == "bf16");
     bool broadcast = false;
     for (int m : info.inputMode) broadcast = broadcast || m != 0;
-    if (broadcast && outT.shape.size() != 2) die(where + "broadcasting elementwise ops are rank 2 only");
+    fusable = fusable && !(broadcast && outT.shape.size() != 2);
+    for (size_t i = 0; fusable && i < op.ins.size(); ++i) {
+      Value &v = peek(fr, op.ins[i], op);
+      fusable = v.kind == Value::Tensor && v.type.elt == outT.elt;
+    }
+    if (!fusable) {  // outside what the fused elementwise kernel takes: a loop nest of its own
+      loopNestOp(op, fr, curStream, where, "an elementwise body, operand type or broadcast the fused kernel lacks");
+      return;
+    }
     auto build = [&](bool inlineLazy) {
       std::vector<XNodeP> operands;
       for (size_t i = 0; i < op.ins.size(); ++i) {
@@ -494,7 +534,7 @@ private:
     out.type = outT;
     out.lazy = tree;
     const std::string res = op.results.empty() ? "" : op.results[0];
-    bool defer = !res.empty();
+    bool defer = !res.empty() && (!curUses || allUsesVisible(res, b, *curUses));
     auto us = usersOf(res, b);
     defer = defer && !us.empty();
     for (auto *u : us) {
@@ -514,6 +554,166 @@ private:
     if (!defer) materialise(out);
     else trace("deferred: " + info.expr + "  // joins the next elementwise kernel");
     fr.vals[res] = out;
+  }
+
+  // linalg.matmul / matmul_transpose_a / _b / transpose written out as the linalg.generic they
+  // stand for (multiply, then add to the output element; operands of another element type
+  // are converted to the output's first, as the named ops define).
+  std::unique_ptr<Op> namedOpAsGeneric(const Op &op, const std::string &where) {
+    auto g = std::make_unique<Op>();
+    g->name = "linalg.generic";
+    g->line = op.line;
+    g->results = op.results;
+    g->resultTypes = op.resultTypes;
+    g->ins = op.ins;
+    g->insTypes = op.insTypes;
+    g->outs = op.outs;
+    g->outsTypes = op.outsTypes;
+    g->body = std::make_unique<Block>();
+    auto dimMap = [](int nd, std::vector<int> dims) {
+      AffineMap m;
+      m.numDims = nd;
+      for (int d : dims) {
+        MapResult r;
+        r.value = d;
+        r.expr = "d" + std::to_string(d);
+        m.results.push_back(r);
+      }
+      return m;
+    };
+    auto scalarOp = [&](const std::string &name, const std::string &res, std::vector<std::string> operands,
+                        const std::string &elt, const std::string &fromElt = "") {
+      auto o = std::make_unique<Op>();
+      o->name = name;
+      o->results = {res};
+      o->operands = std::move(operands);
+      Type t;
+      t.kind = Type::Scalar;
+      t.elt = elt;
+      o->resultTypes = {t};
+      Type f = t;
+      if (!fromElt.empty()) f.elt = fromElt;
+      o->operandTypes = {f};
+      g->body->ops.push_back(std::move(o));
+    };
+    auto yield = [&](const std::string &v) {
+      auto o = std::make_unique<Op>();
+      o->name = "linalg.yield";
+      o->operands = {v};
+      g->body->ops.push_back(std::move(o));
+    };
+    if (op.name == "linalg.matmul" || op.name == "linalg.matmul_transpose_a" || op.name == "linalg.matmul_transpose_b") {
+      if (op.ins.size() != 2 || op.outs.size() != 1) die(where + "malformed " + op.name);
+      const bool ta = op.name == "linalg.matmul_transpose_a", tb = op.name == "linalg.matmul_transpose_b";
+      g->maps = {dimMap(3, ta ? std::vector<int>{2, 0} : std::vector<int>{0, 2}),
+                 dimMap(3, tb ? std::vector<int>{1, 2} : std::vector<int>{2, 1}), dimMap(3, {0, 1})};
+      g->iterators = {"parallel", "parallel", "reduction"};
+      g->body->args = {"%a", "%b", "%c"};
+      const std::string e = op.outsTypes[0].elt;
+      const bool fl = e[0] == 'f' || e[0] == 'b';
+      std::string a = "%a", bv = "%b";
+      auto convert = [&](const std::string &v, const std::string &from) {
+        if (from == e) return v;
+        const bool ffrom = from[0] == 'f' || from[0] == 'b';
+        const std::string name = ffrom && fl ? "arith.extf" : !ffrom && fl ? "arith.sitofp" : !ffrom ? "arith.extsi" : "";
+        if (name.empty()) die(where + op.name + " converting " + from + " to " + e);
+        scalarOp(name, v + "x", {v}, e, from);
+        return v + "x";
+      };
+      a = convert(a, op.insTypes[0].elt);
+      bv = convert(bv, op.insTypes[1].elt);
+      scalarOp(fl ? "arith.mulf" : "arith.muli", "%m", {a, bv}, e);
+      scalarOp(fl ? "arith.addf" : "arith.addi", "%s", {"%c", "%m"}, e);
+      yield("%s");
+    } else if (op.name == "linalg.transpose") {
+      const int nd = static_cast<int>(op.reassociation.size());
+      std::vector<int> ident, outDims(nd);
+      for (int i = 0; i < nd; ++i) ident.push_back(i);
+      // result dim i = input dim perm[i]: iterate over the input's dims, the output is indexed by them permuted
+      std::vector<int> perm;
+      for (auto &grp : op.reassociation) perm.push_back(static_cast<int>(grp[0]));
+      g->maps = {dimMap(nd, ident), dimMap(nd, perm)};
+      g->iterators.assign(nd, "parallel");
+      g->body->args = {"%a", "%c"};
+      yield("%a");
+    } else if (op.name == "linalg.copy") {
+      const int nd = static_cast<int>(op.outsTypes[0].shape.size());
+      std::vector<int> ident;
+      for (int i = 0; i < nd; ++i) ident.push_back(i);
+      g->maps = {dimMap(nd, ident), dimMap(nd, ident)};
+      g->iterators.assign(nd, "parallel");
+      g->body->args = {"%a", "%c"};
+      yield("%a");
+    } else {
+      die(where + op.name + " has no loop-nest form here");
+    }
+    return g;
+  }
+
+  // Any linalg.generic that is none of the recognised ops: the reference pipeline's own
+  // lowering, a loop nest with its parallel loops on threads (loopnest.h).
+  void loopNestOp(const Op &op, Frame &fr, void *stream, const std::string &where, const std::string &because) {
+    LoopNestKernel k;
+    std::string why;
+    if (op.results.empty())
+      die(where + "linalg ops on buffers (no results) are not supported: the runner works on tensors");
+    if (!buildLoopNest(op, fr.constants, k, why))
+      die(where + op.name + " is not a recognised hot-path op (" + because + ") and cannot be written as a loop nest (" +
+          why + "); no CPU fallback");
+    std::vector<void *> ptrs;
+    for (int i : k.pointerInputs) ptrs.push_back(get(fr, op.ins[i], op).buf->ptr);
+    std::vector<Value> outs;
+    for (size_t r = 0; r < op.outs.size(); ++r) {
+      const Type t = r < op.resultTypes.size() ? op.resultTypes[r] : op.outsTypes[r];
+      Value out = makeTensor(stream, t);
+      if (k.readsInit[r]) {
+        Value &init = get(fr, op.outs[r], op);
+        trace("gpuMemCopy(device -> device, " + std::to_string(out.buf->bytes) + " bytes)  // initial value of the result");
+        if (!g_plan && out.buf->bytes) gpuMemCopy(stream, out.buf->ptr, init.buf->ptr, out.buf->bytes);
+      }
+      ptrs.push_back(out.buf->ptr);
+      outs.push_back(out);
+    }
+    ImexKernelDesc d = desc(IMEX_OP_LOOPNEST, 0, 0);
+    d.dims[0] = k.threads;
+    d.dims[3] = static_cast<int64_t>(ptrs.size());
+    launch(stream, d, ptrs, k.summary, k.source);
+    for (size_t r = 0; r < op.results.size() && r < outs.size(); ++r) fr.vals[op.results[r]] = outs[r];
+  }
+
+  // How often `v` is used by the top-level ops of `b`; fusions that make `v` disappear are
+  // only sound when these are ALL its uses (none hidden inside a nested loop body).
+  static int visibleUses(const std::string &v, const Block &b) {
+    int n = 0;
+    for (auto &o : b.ops) {
+      for (auto &x : o->ins) n += x == v;
+      for (auto &x : o->outs) n += x == v;
+      for (auto &x : o->operands) n += x == v;
+      for (auto &x : o->iterInits) n += x == v;
+    }
+    return n;
+  }
+  static bool allUsesVisible(const std::string &v, const Block &b, const std::map<std::string, int> &uses) {
+    auto it = uses.find(v);
+    return it == uses.end() || it->second == visibleUses(v, b);
+  }
+
+  // Makes `name` available now when it is defined LATER in the block by a chain of view ops
+  // (expand / collapse / cast) over values that already exist: a fusion looking ahead (the
+  // bias of a matmul, test/Jax/janet/jit__net_loss.91_linalg.mlir:25-39) may need it early.
+  bool forceViewChain(const std::string &name, Frame &fr, std::map<std::string, const Op *> &defs, int depth = 0) {
+    if (fr.vals.count(name)) return true;
+    auto it = defs.find(name);
+    if (it == defs.end() || depth > 8) return false;
+    const Op &o = *it->second;
+    const std::string &n = o.name;
+    if (n != "tensor.expand_shape" && n != "tensor.collapse_shape" && n != "tensor.cast") return false;
+    if (o.operands.empty() || !forceViewChain(o.operands[0], fr, defs, depth + 1)) return false;
+    Value v = fr.vals[o.operands[0]];
+    if (v.lazy) return false;
+    if (!o.resultTypes[0].unranked) v.type = o.resultTypes[0];
+    fr.vals[o.results[0]] = v;
+    return true;
   }
 
   std::vector<Value> runBlock(const Block &b, Frame &fr, void *stream, std::set<const Op *> &absorbed,
@@ -540,11 +740,27 @@ private:
         } else {
           v.kind = Value::Scalar;
           v.scalar = op.numbers[0];
-          if (op.isRaw[0] && v.type.elt == "f32") {
-            uint32_t u = static_cast<uint32_t>(op.rawBits[0]);
-            float f;
-            std::memcpy(&f, &u, 4);
-            v.scalar = f;
+          if (op.isRaw[0]) {  // a hex literal holds the bits of the value
+            const uint64_t bits = op.rawBits[0];
+            if (v.type.elt == "f32") {
+              uint32_t u = static_cast<uint32_t>(bits);
+              float f;
+              std::memcpy(&f, &u, 4);
+              v.scalar = f;
+            } else if (v.type.elt == "f64") {
+              double d;
+              std::memcpy(&d, &bits, 8);
+              v.scalar = d;
+            } else if (v.type.elt == "bf16") {
+              uint32_t u = static_cast<uint32_t>(bits) << 16;
+              float f;
+              std::memcpy(&f, &u, 4);
+              v.scalar = f;
+            } else if (v.type.elt == "f16") {
+              v.scalar = f16BitsToF32(static_cast<uint16_t>(bits));
+            } else {
+              v.scalar = static_cast<double>(static_cast<int64_t>(bits));
+            }
           }
           fr.constants[op.results[0]] = v.scalar;
         }
@@ -649,6 +865,47 @@ private:
     if (c == "@printF64") { if (!g_plan) printF64(get(fr, op.operands[0], op).scalar); return; }
     if (c == "@printF32") { if (!g_plan) printF32(static_cast<float>(get(fr, op.operands[0], op).scalar)); return; }
     if (c == "@printNewline") { if (!g_plan) printNewline(); return; }
+    if (c.rfind("@printAllclose", 0) == 0 || c.rfind("@printMaxError", 0) == 0) {
+      // the reference's result checks (lib/ExecutionEngine/ImexRunnerUtils.cpp:185-255): both
+      // tensors come back to the host and go to the runner-utils function of that name
+      if (op.operands.size() != 2) die("line " + std::to_string(op.line) + ": " + c + " takes two tensors");
+      Value &t = get(fr, op.operands[0], op), &r = get(fr, op.operands[1], op);
+      trace("gpuMemCopy(device -> host, " + std::to_string(t.buf ? t.buf->bytes : 0) + " bytes)  // " + c);
+      trace("gpuMemCopy(device -> host, " + std::to_string(r.buf ? r.buf->bytes : 0) + " bytes)  // " + c);
+      if (g_plan) return;
+      struct HostCopy {
+        std::vector<char> data;
+        std::vector<int64_t> words;
+        ImexUnrankedMemRef u;
+      };
+      auto fetch = [&](Value &v, HostCopy &h) {
+        h.data.resize(v.buf->bytes ? v.buf->bytes : 1);
+        if (v.buf->bytes) gpuMemCopy(stream, h.data.data(), v.buf->ptr, v.buf->bytes);
+        const int64_t rank = static_cast<int64_t>(v.type.shape.size());
+        h.words.assign(3 + 2 * rank, 0);
+        void *base = h.data.data();
+        std::memcpy(&h.words[0], &base, 8);
+        std::memcpy(&h.words[1], &base, 8);
+        int64_t stride = 1;
+        for (int64_t d = rank - 1; d >= 0; --d) {
+          h.words[3 + d] = v.type.shape[d];
+          h.words[3 + rank + d] = stride;
+          stride *= v.type.shape[d];
+        }
+        h.u = ImexUnrankedMemRef{rank, h.words.data()};
+      };
+      HostCopy a, b;
+      fetch(t, a);
+      fetch(r, b);
+      const std::string &e = t.type.elt;
+      const bool close = c.rfind("@printAllclose", 0) == 0;
+      if (r.type.elt != "f32") die("line " + std::to_string(op.line) + ": the reference tensor of " + c + " is f32");
+      if (e == "f32") close ? _mlir_ciface_printAllcloseF32(&a.u, &b.u) : _mlir_ciface_printMaxErrorF32(&a.u, &b.u);
+      else if (e == "f16") close ? _mlir_ciface_printAllcloseF16(&a.u, &b.u) : _mlir_ciface_printMaxErrorF16(&a.u, &b.u);
+      else if (e == "bf16") close ? _mlir_ciface_printAllcloseBF16(&a.u, &b.u) : _mlir_ciface_printMaxErrorBF16(&a.u, &b.u);
+      else die(c + " of element type " + e);
+      return;
+    }
     if (c.rfind("@printMemref", 0) == 0) {
       Value &t = get(fr, op.operands[0], op);
       trace("gpuMemCopy(device -> host, " + std::to_string(t.buf ? t.buf->bytes : 0) + " bytes)  // " + c);
@@ -716,8 +973,21 @@ private:
                 std::map<std::string, const Op *> &defs, std::map<std::string, int> &uses) {
     Classified c = classify(op, fr.constants);
     auto where = "line " + std::to_string(op.line) + ": ";
-    if (c.kind == Kind::Unknown)
-      die(where + op.name + " is not a recognised hot-path op (" + c.why + "); no CPU fallback");
+    if (op.results.empty())
+      die(where + "linalg ops on buffers (no results) are not supported: the runner works on tensors");
+    if (g_allLoopNests) {
+      if (op.name == "linalg.generic") {
+        loopNestOp(op, fr, stream, where, "every op is lowered to its loop nest in this mode");
+      } else {
+        std::unique_ptr<Op> g = namedOpAsGeneric(op, where);
+        loopNestOp(*g, fr, stream, where, "every op is lowered to its loop nest in this mode");
+      }
+      return;
+    }
+    if (c.kind == Kind::Unknown) {
+      loopNestOp(op, fr, stream, where, c.why);
+      return;
+    }
     const std::string res = op.results.empty() ? "" : op.results[0];
     const Type outT = op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0];
 
@@ -735,7 +1005,15 @@ private:
       }
       Value &A = get(fr, aName, op), &Bv = get(fr, bName, op);
       if (A.type.elt != Bv.type.elt) die(where + "matmul operands of different element types");
-      if (outT.elt != "f32") die(where + "matmul accumulating in " + outT.elt + " is not mapped to a GEMM (f32 accumulate only)");
+      if (outT.elt != "f32") {
+        // e.g. an f16 multiply-add (test/PlaidML/CppEdsl.DotF16.mlir): every step rounds to the
+        // element type, which an f32-accumulating GEMM would not reproduce; the loop nest does
+        if (op.name == "linalg.generic") {
+          loopNestOp(op, fr, stream, where, "matmul accumulating in " + outT.elt + ": f32 accumulate only on the GEMM kernels");
+          break;
+        }
+        die(where + "matmul accumulating in " + outT.elt + " is not mapped to a GEMM (f32 accumulate only)");
+      }
       Value &C0 = get(fr, op.outs[0], op);
       // stored shapes: A [M,K] ([K,M] when transposed), B [K,N] ([N,K] when transposed)
       const int64_t M = A.type.shape[c.transA ? 1 : 0], K = A.type.shape[c.transA ? 0 : 1];
@@ -748,17 +1026,23 @@ private:
       //   truncf   the f32 result rounded once to bf16 / f16
       std::string finalRes = res;
       const Value *biasV = nullptr;
-      auto us = usersOf(finalRes, b);
+      // a value may be folded into the launch only when every use of it is in this block
+      auto fusableUsers = [&](const std::string &v) {
+        return allUsesVisible(v, b, uses) ? usersOf(v, b) : std::vector<const Op *>();
+      };
+      auto us = fusableUsers(finalRes);
       if (us.size() == 1 && classOf(us[0], fr).kind == Kind::Add) {
         const std::string &other = us[0]->ins[0] == finalRes ? us[0]->ins[1] : us[0]->ins[0];
         const Op *bp = producer(other, defs);
-        if (classOf(bp, fr).kind == Kind::BroadcastRow) {
+        if (classOf(bp, fr).kind == Kind::BroadcastRow && allUsesVisible(other, b, uses) &&
+            usersOf(other, b).size() == 1 && forceViewChain(bp->ins[0], fr, defs)) {
           const Value &v = get(fr, bp->ins[0], *bp);
           if (v.type.elt == "f32" && v.type.shape.size() == 1 && v.type.shape[0] == N) {
             biasV = &v;
             absorbed.insert(us[0]);
+            absorbed.insert(bp);  // the broadcast itself: nothing to materialise
             finalRes = us[0]->results[0];
-            us = usersOf(finalRes, b);
+            us = fusableUsers(finalRes);
           }
         }
       }
@@ -767,7 +1051,7 @@ private:
         epi = IMEX_EPI_RELU;
         absorbed.insert(us[0]);
         finalRes = us[0]->results[0];
-        us = usersOf(finalRes, b);
+        us = fusableUsers(finalRes);
       } else if (us.size() == 2 && classOf(us[0], fr).kind == Kind::Sigmoid &&
                  classOf(us[1], fr).kind == Kind::Mul && us[1]->ins[0] == us[0]->results[0] &&
                  us[1]->ins[1] == finalRes) {
@@ -775,7 +1059,7 @@ private:
         absorbed.insert(us[0]);
         absorbed.insert(us[1]);
         finalRes = us[1]->results[0];
-        us = usersOf(finalRes, b);
+        us = fusableUsers(finalRes);
       }
       Type finalT = outT;
       if (us.size() == 1 && classOf(us[0], fr).kind == Kind::TruncF) {
@@ -867,13 +1151,14 @@ private:
       std::string finalRes = res;
       if (c.kind == Kind::Sigmoid) {
         auto us = usersOf(res, b);
-        if (us.size() == 1 && classOf(us[0], fr).kind == Kind::Mul && us[0]->ins[0] == res &&
-            us[0]->ins[1] == op.ins[0]) {
+        if (us.size() == 1 && allUsesVisible(res, b, uses) && classOf(us[0], fr).kind == Kind::Mul &&
+            us[0]->ins[0] == res && us[0]->ins[1] == op.ins[0]) {
           epi = IMEX_EPI_SILU;
           absorbed.insert(us[0]);
           finalRes = us[0]->results[0];
-        } else {
-          die(where + "sigmoid generic that is not followed by x * sigmoid(x)");
+        } else {  // a sigmoid on its own: an elementwise kernel like any other
+          elementwiseOp(op, b, fr, where);
+          break;
         }
       }
       Value out = makeTensor(stream, outT);
@@ -901,13 +1186,19 @@ private:
           if (k == Kind::RowSum) sum = u;
           if (k == Kind::DivRowBcast && u->ins[0] == ex->results[0]) dv = u;
         }
-      if (!(sub && ex && sum && dv && dv->ins[1] == sum->results[0]))
-        die(where + "row max that does not start a softmax chain (max, subtract, exp, sum, divide)");
-      if (!init.isFill) die(where + "softmax row max must start from a filled tensor");
-      const bool negInf = std::isinf(init.fillValue) && init.fillValue < 0;
-      if (!negInf && !(init.fillValue <= -3.4e38)) die(where + "softmax row max must start from -inf or -FLT_MAX");
-      if ((X.type.elt != "f32" && X.type.elt != "f16" && X.type.elt != "bf16") || X.type.shape.size() != 2)
-        die(where + "softmax is f32 / f16 / bf16, rank 2 only");
+      const bool negInf = init.isFill && std::isinf(init.fillValue) && init.fillValue < 0;
+      bool chain = sub && ex && sum && dv && dv->ins[1] == sum->results[0] && init.isFill &&
+                   (negInf || init.fillValue <= -3.4e38) && X.type.shape.size() == 2 &&
+                   (X.type.elt == "f32" || X.type.elt == "f16" || X.type.elt == "bf16");
+      // the chain's temporaries disappear: all of their uses must be the chain's own
+      chain = chain && allUsesVisible(res, b, uses) && usersOf(res, b).size() == 1 &&
+              allUsesVisible(sub->results[0], b, uses) && usersOf(sub->results[0], b).size() == 1 &&
+              allUsesVisible(ex->results[0], b, uses) && usersOf(ex->results[0], b).size() == 2 &&
+              allUsesVisible(sum->results[0], b, uses) && usersOf(sum->results[0], b).size() == 1;
+      if (!chain) {  // a row max on its own (test/PlaidML/OpTest.Max.mlir): a loop nest, one thread per row
+        loopNestOp(op, fr, stream, where, "a row max that does not start a softmax chain");
+        break;
+      }
       // The chain runs as one kernel when its LAST op (the divide) is reached: the row
       // sum's initial tensor may be defined between here and there.
       for (const Op *o : {sub, ex, sum}) absorbed.insert(o);
@@ -920,8 +1211,10 @@ private:
     }
     case Kind::DivRowBcast: {
       auto it = pendingSoftmax.find(&op);
-      if (it == pendingSoftmax.end())
-        die(where + "row-broadcast divide outside a softmax chain; no CPU fallback");
+      if (it == pendingSoftmax.end()) {  // a row-broadcast divide on its own
+        elementwiseOp(op, b, fr, where);
+        break;
+      }
       const SoftmaxPlan plan = it->second;
       pendingSoftmax.erase(it);
       Value &X = get(fr, plan.x, op);
@@ -965,9 +1258,12 @@ private:
         fr.vals[res] = out;
         break;
       }
+      if (maybeOpen.type.elt != "f32") {  // integer and f64 sums: a loop nest (exact, ascending order)
+        loopNestOp(op, fr, stream, where, "the sum kernels are f32 only");
+        break;
+      }
       Value &X = get(fr, op.ins[0], op);
       Value &init = get(fr, op.outs[0], op);
-      if (X.type.elt != "f32") die(where + "sum reductions are f32 only");
       Value out = makeTensor(stream, outT);
       uint32_t opc = c.kind == Kind::RowSum ? IMEX_OP_REDUCE_ROWS
                      : c.kind == Kind::ReduceLeading ? IMEX_OP_REDUCE_LEADING : IMEX_OP_REDUCE_ALL;
@@ -1008,22 +1304,18 @@ private:
           d.dims[3 + i] = c.perm[i];
         }
         launch(stream, d, {X.buf->ptr, out.buf->ptr}, "transpose3d");
-      } else {
-        die(where + "only rank-2 and rank-3 permutations of 2- and 4-byte elements have kernels");
+      } else {  // other ranks and element widths: a loop nest (one thread per element)
+        loopNestOp(op, fr, stream, where, "the transpose kernels take rank 2 and 3, 2- and 4-byte elements");
+        break;
       }
       fr.vals[res] = out;
       break;
     }
     default: {
-      ElementwiseInfo standalone;
-      if (classifyElementwise(op, fr.constants, standalone)) {  // e.g. an exp or a mul on its own
-        elementwiseOp(op, b, fr, where);
-        break;
-      }
-      die(where + std::string(kindName(c.kind)) + " generic outside the chain it belongs to (softmax / silu); no CPU fallback");
+      elementwiseOp(op, b, fr, where);  // e.g. an exp or a mul on its own; a loop nest when all else fails
+      break;
     }
     }
-    (void)uses;
   }
 };
 
@@ -1044,6 +1336,7 @@ int main(int argc, char **argv) {
     if (a == "-e" && i + 1 < argc) entry = argv[++i];
     else if (a.rfind("-e=", 0) == 0) entry = a.substr(3);
     else if (a == "--emit-plan") g_plan = true;
+    else if (a == "--all-loopnests") g_allLoopNests = true;
     else if (a == "--trace") g_trace = true;
     else if (a.rfind("--entry-point-result", 0) == 0 || a.rfind("-entry-point-result", 0) == 0) {
       if (a.find("void") == std::string::npos) die("only --entry-point-result=void is supported");
@@ -1056,6 +1349,7 @@ int main(int argc, char **argv) {
     }
   }
   if (std::getenv("IMEX_B200_TRACE")) g_trace = true;
+  if (std::getenv("IMEX_B200_ALL_LOOPNESTS")) g_allLoopNests = true;
   if (file.empty()) die("usage: imex-b200-runner FILE.mlir [-e main] [--entry-point-result=void] [--emit-plan]");
   try {
     Module m = parseModule(readFile(file));

@@ -12,10 +12,8 @@
 //
 // Arithmetic is that of eltwise_expr.cu: every operation in f32, rounded to the element
 // type after every operation, no contraction.
+#include "jit_common.h"
 #include "kernels.h"
-
-#include <cuda.h>
-#include <dlfcn.h>
 
 #include <cstdio>
 #include <cstdlib>
@@ -28,73 +26,6 @@
 
 namespace imex {
 namespace {
-
-// ---- NVRTC, through dlopen ------------------------------------------------------
-struct Nvrtc {
-  using Program = void *;
-  int (*createProgram)(Program *, const char *, const char *, int, const char *const *,
-                       const char *const *) = nullptr;
-  int (*compileProgram)(Program, int, const char *const *) = nullptr;
-  int (*getCUBINSize)(Program, size_t *) = nullptr;
-  int (*getCUBIN)(Program, char *) = nullptr;
-  int (*getProgramLogSize)(Program, size_t *) = nullptr;
-  int (*getProgramLog)(Program, char *) = nullptr;
-  int (*destroyProgram)(Program *) = nullptr;
-  bool ok = false;
-};
-
-const Nvrtc &nvrtc() {
-  static Nvrtc n = [] {
-    Nvrtc r;
-    void *h = nullptr;
-    for (const char *name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
-                             "/usr/local/cuda/lib64/libnvrtc.so"}) {
-      h = dlopen(name, RTLD_NOW | RTLD_LOCAL);
-      if (h) break;
-    }
-    if (!h) return r;
-    auto sym = [&](const char *s) { return dlsym(h, s); };
-    r.createProgram = reinterpret_cast<decltype(r.createProgram)>(sym("nvrtcCreateProgram"));
-    r.compileProgram = reinterpret_cast<decltype(r.compileProgram)>(sym("nvrtcCompileProgram"));
-    r.getCUBINSize = reinterpret_cast<decltype(r.getCUBINSize)>(sym("nvrtcGetCUBINSize"));
-    r.getCUBIN = reinterpret_cast<decltype(r.getCUBIN)>(sym("nvrtcGetCUBIN"));
-    r.getProgramLogSize = reinterpret_cast<decltype(r.getProgramLogSize)>(sym("nvrtcGetProgramLogSize"));
-    r.getProgramLog = reinterpret_cast<decltype(r.getProgramLog)>(sym("nvrtcGetProgramLog"));
-    r.destroyProgram = reinterpret_cast<decltype(r.destroyProgram)>(sym("nvrtcDestroyProgram"));
-    r.ok = r.createProgram && r.compileProgram && r.getCUBINSize && r.getCUBIN && r.destroyProgram;
-    return r;
-  }();
-  return n;
-}
-
-// ---- the three driver calls needed to run a cubin -------------------------------------
-struct Driver {
-  CUresult (*moduleLoadData)(CUmodule *, const void *) = nullptr;
-  CUresult (*moduleGetFunction)(CUfunction *, CUmodule, const char *) = nullptr;
-  CUresult (*launchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
-                           unsigned, CUstream, void **, void **) = nullptr;
-  bool ok = false;
-};
-
-const Driver &driver() {
-  static Driver d = [] {
-    Driver r;
-    auto get = [](const char *name) -> void * {
-      void *p = nullptr;
-      cudaDriverEntryPointQueryResult q;
-      if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess ||
-          q != cudaDriverEntryPointSuccess)
-        return nullptr;
-      return p;
-    };
-    r.moduleLoadData = reinterpret_cast<decltype(r.moduleLoadData)>(get("cuModuleLoadData"));
-    r.moduleGetFunction = reinterpret_cast<decltype(r.moduleGetFunction)>(get("cuModuleGetFunction"));
-    r.launchKernel = reinterpret_cast<decltype(r.launchKernel)>(get("cuLaunchKernel"));
-    r.ok = r.moduleLoadData && r.moduleGetFunction && r.launchKernel;
-    return r;
-  }();
-  return d;
-}
 
 // ---- source generation -----------------------------------------------------------------
 const char *kPrelude = R"SRC(
@@ -255,52 +186,14 @@ std::string generate(const unsigned char *code, int ncode, int n_inputs, int dty
   return os.str();
 }
 
-struct Compiled {
-  CUfunction fn = nullptr;
-  bool failed = false;
-};
+using jit::Compiled;
+using jit::driver;
+using jit::nvrtc;
 
 std::mutex g_mu;
 std::map<std::string, Compiled> g_cache;
 
-Compiled compile(const std::string &src) {
-  Compiled c;
-  const Nvrtc &n = nvrtc();
-  const Driver &d = driver();
-  Nvrtc::Program prog = nullptr;
-  if (n.createProgram(&prog, src.c_str(), "imex_expr.cu", 0, nullptr, nullptr) != 0) {
-    c.failed = true;
-    return c;
-  }
-  const char *opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", "--fmad=false"};
-  const int rc = n.compileProgram(prog, 4, opts);
-  if (rc != 0) {
-    if (getenv("IMEX_B200_JIT_VERBOSE") && n.getProgramLogSize && n.getProgramLog) {
-      size_t sz = 0;
-      n.getProgramLogSize(prog, &sz);
-      std::string log(sz, '\0');
-      n.getProgramLog(prog, &log[0]);
-      fprintf(stderr, "[imex expr jit] compilation failed:\n%s\n%s\n", log.c_str(), src.c_str());
-    }
-    n.destroyProgram(&prog);
-    c.failed = true;
-    return c;
-  }
-  size_t size = 0;
-  std::vector<char> cubin;
-  if (n.getCUBINSize(prog, &size) == 0 && size > 0) {
-    cubin.resize(size);
-    if (n.getCUBIN(prog, cubin.data()) != 0) cubin.clear();
-  }
-  n.destroyProgram(&prog);
-  CUmodule mod = nullptr;
-  if (cubin.empty() || d.moduleLoadData(&mod, cubin.data()) != CUDA_SUCCESS ||
-      d.moduleGetFunction(&c.fn, mod, "expr_kernel") != CUDA_SUCCESS) {
-    c.fn = nullptr;
-    c.failed = true;
-  }
-  return c;
-}
+Compiled compile(const std::string &src) { return jit::compile_kernel(src, "expr_kernel"); }
 
 } // namespace
 

@@ -82,6 +82,7 @@ struct PairParams {
   int epilogue;
   int accumulate;
   int out_dtype;  // kF32 (TMA tile stores) or kBF16 / kF16 (packed 16-byte stores)
+  int fast_epilogue;  // silu through the hardware exp2 / reciprocal units
   uint32_t idesc;
   long long *stats;   // optional per-CTA cycle counters (nullptr = off), 8 per CTA
 };
@@ -91,6 +92,14 @@ struct WorkItem {
   int kb0, kb1;  // k blocks [kb0, kb1)
   int slot;      // partial slot, or -1 for a whole tile (normal epilogue)
 };
+
+// Epilogue of the tensor-core path.  The f32 reference chain of silu (expf, IEEE divide)
+// costs ~25 instructions per output element; on config 5 that is 13 G instructions per
+// step beside a GEMM that runs at the board's power limit.  `fast` evaluates the same
+// function with ex2.approx and rcp.approx (relative error ~1e-6 against a 1e-3 budget).
+__device__ __forceinline__ float pair_epilogue(float v, int epilogue, int fast) {
+  return fast ? apply_epilogue_fast(v, epilogue) : apply_epilogue(v, epilogue);
+}
 
 // cycle counter for the optional in-kernel statistics; free when they are off
 template <bool STATS> __device__ __forceinline__ long long now() {
@@ -386,8 +395,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 uint32_t o[4];
 #pragma unroll
                 for (int e = 0; e < 8; e += 2)
-                  o[e >> 1] = static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v[e], p.epilogue), p.out_dtype)) |
-                              (static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v[e + 1], p.epilogue), p.out_dtype)) << 16);
+                  o[e >> 1] = static_cast<uint32_t>(f32_to_half_bits(pair_epilogue(v[e], p.epilogue, p.fast_epilogue), p.out_dtype)) |
+                              (static_cast<uint32_t>(f32_to_half_bits(pair_epilogue(v[e + 1], p.epilogue, p.fast_epilogue), p.out_dtype)) << 16);
                 *reinterpret_cast<uint4 *>(c16 + col) = make_uint4(o[0], o[1], o[2], o[3]);
               }
             }
@@ -407,10 +416,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
                   v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
                 }
-                v.x = apply_epilogue(v.x, p.epilogue);
-                v.y = apply_epilogue(v.y, p.epilogue);
-                v.z = apply_epilogue(v.z, p.epilogue);
-                v.w = apply_epilogue(v.w, p.epilogue);
+                v.x = pair_epilogue(v.x, p.epilogue, p.fast_epilogue);
+                v.y = pair_epilogue(v.y, p.epilogue, p.fast_epilogue);
+                v.z = pair_epilogue(v.z, p.epilogue, p.fast_epilogue);
+                v.w = pair_epilogue(v.w, p.epilogue, p.fast_epilogue);
                 *reinterpret_cast<float4 *>(c_row + col) = v;
               }
             }
@@ -433,10 +442,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
               }
             }
-            v.x = apply_epilogue(v.x, p.epilogue);
-            v.y = apply_epilogue(v.y, p.epilogue);
-            v.z = apply_epilogue(v.z, p.epilogue);
-            v.w = apply_epilogue(v.w, p.epilogue);
+            v.x = pair_epilogue(v.x, p.epilogue, p.fast_epilogue);
+            v.y = pair_epilogue(v.y, p.epilogue, p.fast_epilogue);
+            v.z = pair_epilogue(v.z, p.epilogue, p.fast_epilogue);
+            v.w = pair_epilogue(v.w, p.epilogue, p.fast_epilogue);
             st_shared_v4(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4), v);
           }
           fence_async_smem();
@@ -506,10 +515,10 @@ gemm_splitk_fixup_kernel(const PairParams p) {
         v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
       }
       uint2 o;
-      o.x = static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.x, p.epilogue), p.out_dtype)) |
-            (static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.y, p.epilogue), p.out_dtype)) << 16);
-      o.y = static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.z, p.epilogue), p.out_dtype)) |
-            (static_cast<uint32_t>(f32_to_half_bits(apply_epilogue(v.w, p.epilogue), p.out_dtype)) << 16);
+      o.x = static_cast<uint32_t>(f32_to_half_bits(pair_epilogue(v.x, p.epilogue, p.fast_epilogue), p.out_dtype)) |
+            (static_cast<uint32_t>(f32_to_half_bits(pair_epilogue(v.y, p.epilogue, p.fast_epilogue), p.out_dtype)) << 16);
+      o.y = static_cast<uint32_t>(f32_to_half_bits(pair_epilogue(v.z, p.epilogue, p.fast_epilogue), p.out_dtype)) |
+            (static_cast<uint32_t>(f32_to_half_bits(pair_epilogue(v.w, p.epilogue, p.fast_epilogue), p.out_dtype)) << 16);
       *reinterpret_cast<uint2 *>(c) = o;
       continue;
     }
@@ -522,10 +531,10 @@ gemm_splitk_fixup_kernel(const PairParams p) {
       const float4 b = *reinterpret_cast<const float4 *>(p.bias + col);
       v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
     }
-    v.x = apply_epilogue(v.x, p.epilogue);
-    v.y = apply_epilogue(v.y, p.epilogue);
-    v.z = apply_epilogue(v.z, p.epilogue);
-    v.w = apply_epilogue(v.w, p.epilogue);
+    v.x = pair_epilogue(v.x, p.epilogue, p.fast_epilogue);
+    v.y = pair_epilogue(v.y, p.epilogue, p.fast_epilogue);
+    v.z = pair_epilogue(v.z, p.epilogue, p.fast_epilogue);
+    v.w = pair_epilogue(v.w, p.epilogue, p.fast_epilogue);
     *reinterpret_cast<float4 *>(c) = v;
   }
 }
@@ -621,6 +630,8 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   p.epilogue = g.epilogue;
   p.accumulate = g.accumulate ? 1 : 0;
   p.out_dtype = g.out_dtype;
+  static const bool precise_epilogue = getenv("IMEX_GEMM_PRECISE_EPILOGUE") != nullptr;
+  p.fast_epilogue = precise_epilogue ? 0 : 1;
   p.stats = nullptr;
   static long long *stats_buf = nullptr;
   const bool want_stats = with_stats && variant == 1 && !transposed;  // development aid (IMEX_GEMM_STATS=1)

@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <string>
 
 namespace imex {
 
@@ -119,6 +120,14 @@ cudaError_t launch_expr(const void *const *inputs, int n_inputs, void *out, int6
 cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, int64_t rows, int64_t cols,
                             const unsigned char *code, int ncode, float c0, float c1, int dtype,
                             int out_dtype, bool reduce_leading, bool accumulate, cudaStream_t stream);
+
+// A loop-nest kernel given as CUDA C++ text (one `extern "C" __global__ void
+// imex_loopnest(pointers...)` written against loopnest_prelude()): compiled for sm_100a at
+// first use, cached by text, launched over `threads` points.  cudaErrorNotSupported when it
+// cannot be compiled (*log then holds the compiler's output).
+const char *loopnest_prelude();
+cudaError_t launch_loopnest(const char *source, size_t source_bytes, void *const *ptrs, int n_ptrs,
+                            int64_t threads, cudaStream_t stream, std::string *log);
 
 // Y[i] = convert(X[i]): f32 <-> bf16 / f16 (arith.extf / arith.truncf generics)
 cudaError_t launch_convert(const void *x, void *y, int64_t n, int in_dtype, int out_dtype,

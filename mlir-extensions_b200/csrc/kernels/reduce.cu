@@ -12,8 +12,6 @@
 // order as the loop nest, bit-identical, and coalesced across the warp.
 #include "kernels.h"
 
-#include <cstdlib>
-
 namespace imex {
 namespace {
 
@@ -33,19 +31,12 @@ __device__ __forceinline__ float4 ldg_stream(const float4 *p) {
 
 constexpr int ROWS_WARPS = 8;
 
-// INTERLEAVED = false: CTAs of ROWS_WARPS warps, warp w of the grid starts at row w.
-// INTERLEAVED = true (few rows per SM): one CTA per SM with as many warps as its share of
-// the rows, row r on CTA r % gridDim.x, so that every SM owns the same number of rows to
-// within one and has all of its loads in flight from the start.
-template <bool INTERLEAVED>
-__global__ void __launch_bounds__(INTERLEAVED ? 1024 : ROWS_WARPS * 32)
+__global__ void __launch_bounds__(ROWS_WARPS * 32)
 reduce_rows_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows,
                         int64_t cols, int accumulate, int vec_ok) {
   const int lane = threadIdx.x & 31;
-  const int warps_cta = blockDim.x >> 5;
-  const int64_t warp0 = INTERLEAVED ? blockIdx.x + static_cast<int64_t>(gridDim.x) * (threadIdx.x >> 5)
-                                    : static_cast<int64_t>(blockIdx.x) * warps_cta + (threadIdx.x >> 5);
-  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_cta;
+  const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * ROWS_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * ROWS_WARPS;
   for (int64_t row = warp0; row < rows; row += nwarps) {
     const float *xr = x + row * cols;
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
@@ -165,25 +156,10 @@ cudaError_t launch_reduce_rows_f32(const float *x, float *y, int64_t rows, int64
                                                                               accumulate ? 1 : 0);
     return cudaGetLastError();
   }
-  static const int sms = [] {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n > 0 ? n : 148;
-  }();
-  if (rows <= 128LL * sms && !getenv("IMEX_REDUCE_PLAIN_GRID")) {
-    const int64_t per_sm = (rows + sms - 1) / sms;
-    const int64_t rounds = (per_sm + 31) / 32;
-    const int warps_cta = static_cast<int>((per_sm + rounds - 1) / rounds);
-    const unsigned grid = static_cast<unsigned>(rows < sms ? rows : sms);
-    reduce_rows_warp_kernel<true><<<grid, 32 * warps_cta, 0, stream>>>(x, y, rows, cols, accumulate ? 1 : 0,
-                                                                       vec_ok);
-    return cudaGetLastError();
-  }
   int64_t blocks = (rows + ROWS_WARPS - 1) / ROWS_WARPS;
   const int64_t cap = 148 * 8 * 4;  // 8 resident blocks per SM, a few waves
   if (blocks > cap) blocks = cap;
-  reduce_rows_warp_kernel<false><<<static_cast<unsigned>(blocks), ROWS_WARPS * 32, 0, stream>>>(
+  reduce_rows_warp_kernel<<<static_cast<unsigned>(blocks), ROWS_WARPS * 32, 0, stream>>>(
       x, y, rows, cols, accumulate ? 1 : 0, vec_ok);
   return cudaGetLastError();
 }

@@ -81,10 +81,12 @@ struct Stream {
 
 struct Kernel {
   ImexKernelDesc desc;
+  const std::string *source = nullptr;  // IMEX_OP_LOOPNEST: kernel text, owned by the module
 };
 
 struct Module {
   std::vector<ImexKernelDesc> kernels;
+  std::vector<std::string> sources;  // per kernel: the text of an IMEX_OP_LOOPNEST kernel, else empty
   std::vector<std::unique_ptr<Kernel>> handles;  // one per table row, made on first gpuKernelGet
 };
 
@@ -107,6 +109,7 @@ const char *op_name(uint32_t op) {
   case IMEX_OP_FILL_NORMAL: return "fill_normal";
   case IMEX_OP_EXPR: return "expr";
   case IMEX_OP_ATTENTION_FWD: return "attention_fwd";
+  case IMEX_OP_LOOPNEST: return "loopnest";
   }
   return nullptr;
 }
@@ -202,11 +205,19 @@ Module *load_module(const void *data, size_t size) {
   m->kernels.resize(h.num_kernels);
   memcpy(m->kernels.data(), static_cast<const char *>(data) + sizeof h,
          h.num_kernels * sizeof(ImexKernelDesc));
-  for (auto &k : m->kernels) {
+  m->sources.resize(h.num_kernels);
+  for (size_t i = 0; i < m->kernels.size(); ++i) {
+    auto &k = m->kernels[i];
     k.name[IMEX_KERNEL_NAME_MAX - 1] = 0;
     if (!op_name(k.op))
       throw std::runtime_error(std::string("gpuModuleLoad: kernel '") + k.name +
                                "' names an unknown op " + std::to_string(k.op));
+    if (k.op == IMEX_OP_LOOPNEST) {  // the kernel's text lies in the payload behind the table
+      const int64_t off = k.dims[1], len = k.dims[2];
+      if (off < 0 || len <= 0 || static_cast<uint64_t>(off) + static_cast<uint64_t>(len) > size)
+        throw std::runtime_error(std::string("gpuModuleLoad: kernel '") + k.name + "' points outside the blob");
+      m->sources[i].assign(static_cast<const char *>(data) + off, static_cast<size_t>(len));
+    }
   }
   std::lock_guard<std::mutex> lock(g_mutex);
   auto &slot = g_modules[data];
@@ -224,6 +235,7 @@ Kernel *get_kernel(Module *m, const char *name) {
       if (!m->handles[i]) {
         m->handles[i] = std::make_unique<Kernel>();
         m->handles[i]->desc = m->kernels[i];
+        m->handles[i]->source = &m->sources[i];
       }
       return m->handles[i].get();
     }
@@ -268,7 +280,7 @@ void ensure_scratch(Stream *s, size_t bytes) {
 }
 
 // One enqueue of the op a kernel handle stands for.
-void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
+void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs, const std::string *source = nullptr) {
   auto need = [&](size_t n) {
     if (nptrs < n)
       throw std::runtime_error(std::string("gpuLaunchKernel: '") + d.name + "' (" + op_name(d.op) +
@@ -447,6 +459,20 @@ void enqueue(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     err = imex::launch_flash_attention_fwd(ptrs[0], ptrs[1], ptrs[2], ptrs[3], d.dims[0], d.dims[1], d.dims[2],
                                            d.fparams[0], static_cast<int>(d.in_dtype), s->status_dev, s->stream);
     break;
+  case IMEX_OP_LOOPNEST: {
+    const size_t want = static_cast<size_t>(d.dims[3]);
+    if (want < 1 || want > 32) throw std::runtime_error("gpuLaunchKernel: loop-nest kernels take 1..32 pointers");
+    need(want);
+    if (!source || source->empty()) throw std::runtime_error("gpuLaunchKernel: loop-nest kernel without text");
+    std::string log;
+    s->last_kernel = "loopnest_jit";
+    err = imex::launch_loopnest(source->data(), source->size(), ptrs, static_cast<int>(want), d.dims[0],
+                                s->stream, &log);
+    if (err == cudaErrorNotSupported)
+      throw std::runtime_error(std::string("gpuLaunchKernel: the loop-nest kernel '") + d.name +
+                               "' could not be compiled for sm_100a (there is no interpreter behind it): " + log);
+    break;
+  }
   case IMEX_OP_FILL_UNIFORM:
     need(1);
     s->last_kernel = "fill_uniform";
@@ -480,7 +506,7 @@ void check_status(Stream *s) {
 // The reference's profiling loop (LevelZeroRuntimeWrappers.cpp:521-597): warm-ups,
 // then `rounds` timed launches, optionally flushing the last-level cache before
 // each by writing a buffer twice its size; one statistics line on stdout.
-void profile(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
+void profile(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs, const std::string *source) {
   long rounds = 1000, warmups = 3;
   if (const char *e = getenv("IMEX_PROFILING_RUNS")) {
     long v = strtol(e, nullptr, 10);
@@ -499,7 +525,7 @@ void profile(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
     cache_bytes = 2 * static_cast<size_t>(l2);
     CHECK_CUDA(cudaMalloc(&cache, cache_bytes));
   }
-  for (long r = 0; r < warmups; ++r) enqueue(s, d, ptrs, nptrs);
+  for (long r = 0; r < warmups; ++r) enqueue(s, d, ptrs, nptrs, source);
   cudaEvent_t e0, e1;
   CHECK_CUDA(cudaEventCreate(&e0));
   CHECK_CUDA(cudaEventCreate(&e1));
@@ -507,7 +533,7 @@ void profile(Stream *s, const ImexKernelDesc &d, void **ptrs, size_t nptrs) {
   for (long r = 0; r < rounds; ++r) {
     if (flush) CHECK_CUDA(cudaMemsetAsync(cache, 0, cache_bytes, s->stream));
     CHECK_CUDA(cudaEventRecord(e0, s->stream));
-    enqueue(s, d, ptrs, nptrs);
+    enqueue(s, d, ptrs, nptrs, source);
     CHECK_CUDA(cudaEventRecord(e1, s->stream));
     CHECK_CUDA(cudaEventSynchronize(e1));
     CHECK_CUDA(cudaEventElapsedTime(&ms[static_cast<size_t>(r)], e0, e1));
@@ -578,8 +604,8 @@ Event *launch(Stream *s, Kernel *k, size_t sharedMemBytes, ImexParamDesc *params
     for (size_t i = 0; deps[i].event; ++i)
       CHECK_CUDA(cudaStreamWaitEvent(s->stream, static_cast<Event *>(deps[i].event)->ev, 0));
   for (void *p : ptrs) prefetch_managed(s, p);
-  if (getenv("IMEX_ENABLE_PROFILING")) profile(s, k->desc, ptrs.data(), ptrs.size());
-  enqueue(s, k->desc, ptrs.data(), ptrs.size());
+  if (getenv("IMEX_ENABLE_PROFILING")) profile(s, k->desc, ptrs.data(), ptrs.size(), k->source);
+  enqueue(s, k->desc, ptrs.data(), ptrs.size(), k->source);
   Event *ev = &s->events[s->next_event++ % kEventSlots];
   if (!ev->ev) CHECK_CUDA(cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming));
   CHECK_CUDA(cudaEventRecord(ev->ev, s->stream));

@@ -82,7 +82,12 @@ def test_elementwise_chains_fuse_into_one_launch_each():
 def test_ir_outside_the_hot_path_is_refused():
     rc, out, err = plan(os.path.join(MLIR, "unrecognised.mlir"))
     assert rc == 1
-    assert "line 8" in err and "erf(in0)" in err and "no CPU fallback" in err
+    assert "line 9" in err and "math.ctlz" in err and "loop nest" in err and "no CPU fallback" in err
+
+
+def test_linalg_ops_on_buffers_are_refused_not_dropped():
+    rc, out, err = plan(os.path.join(MLIR, "buffer_form.mlir"))
+    assert rc == 1 and "line 8" in err and "on buffers" in err
 
 
 def test_parse_errors_name_the_line(tmp_path):
@@ -141,9 +146,12 @@ def test_reference_tests_are_recognised(rel, expect):
 
 def test_f16_multiply_add_is_not_sent_to_the_tensor_cores():
     # test/PlaidML/CppEdsl.DotF16.mlir multiplies and adds in f16: rounding at every
-    # step, which an f32-accumulating GEMM would not reproduce
+    # step, which an f32-accumulating GEMM would not reproduce; it runs as a loop nest
+    # (one thread per output, k ascending, f16 rounding after the multiply and after the add)
     rc, out, err = plan(reference_files.need("test/PlaidML/CppEdsl.DotF16.mlir"))
-    assert rc == 1 and "f32 accumulate only" in err
+    assert rc == 0, err
+    ks = kernels(out)
+    assert not any(k.startswith("gemm") for k in ks) and any(k.startswith("loopnest[2 parallel, 1 reduction") for k in ks), ks
 
 
 @pytest.mark.parametrize("name,subst,expect", [
