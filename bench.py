@@ -339,7 +339,7 @@ def main():
     ap.add_argument("--comm-ms", type=float, default=0.5,
                     help="N>1, --overlap calls: how long the first GEMM launch (NCCL beside it) should last")
     ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "calls"),
-                    choices=["slabs", "calls", "prefetch"],
+                    choices=["slabs", "calls", "prefetch", "ce"],
                     help="N>1: hide the replication of B inside a call (column slabs) or across calls")
     ap.add_argument("--case", default=None, choices=sorted(CASES),
                     help="run ONE small kernel case --iters times and exit (ncu captures)")
@@ -406,6 +406,8 @@ def main():
     gemm = RowShardedGemm(sess, rank, world, M_total, N_DIM, K_DIM, B.BF16, epi, src=0,
                           sm_margin=args.sm_margin, device=dev, overlap=args.overlap, comm_ms=args.comm_ms)
     assert (gemm.row0, gemm.rows) == (row0, rows)
+    if world > 1 and args.overlap == "ce":
+        gemm.register_b(Bm)  # B enters the copy-engine replication once; every step replicates it again
 
     def step():
         # world > 1: B lives on rank 0; its column slabs are NCCL-broadcast on a side
@@ -438,6 +440,7 @@ def main():
     e1.record()
     barrier()
     sess.wait()
+    gemm.check()
     launches = rt.imexLaunchCount() - launches0
     gemm_kernel_name = sess.last_kernel()
     total_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -472,7 +475,7 @@ def main():
 
     # optional: when does each broadcast run relative to the GEMMs (ms since the first event)
     timeline = None
-    if world > 1 and args.timeline > 0 and args.overlap != "prefetch":
+    if world > 1 and args.timeline > 0 and args.overlap in ("calls", "slabs"):
         barrier()
         base = torch.cuda.Event(enable_timing=True)
         base.record()
@@ -625,7 +628,11 @@ def main():
                                           "and whose second uses all SMs" if gemm.overlap == "calls" else
                                           "as one slab %s started by the previous step, beside its main GEMM "
                                           "launch; a helper launch takes over the %d SMs the broadcast held"))
-                                      % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 else "none",
+                                      % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 and gemm.overlap != "ce"
+                       else ("B replicated from rank 0 inside every step by the copy engines over NVLink (IPC-mapped "
+                             "buffers: each rank pulls its slice from rank 0, a stream-ordered barrier, then the other "
+                             "slices from their holders), beside the previous step's GEMM; one GEMM launch on all SMs, "
+                             "no NCCL kernel") if world > 1 else "none",
                        "gemm_launch_columns": [int(k_.dims[1]) for k_ in gemm.launch_descs],
                        "l2": "inputs (%d MiB A shard + 128 MiB B) and the %d MiB C shard exceed the 126 MB L2"
                              % (rows * K_DIM * 2 >> 20, rows * N_DIM * 4 >> 20)},
@@ -659,6 +666,7 @@ def main():
                                    "bound": v["roofline"]["bound"], "traffic": v["roofline"].get("traffic")}
                                for k, v in kernels.items()}
         print(json.dumps(line), flush=True)
+    gemm.close()
     sess.close()
     if world > 1:
         dist.destroy_process_group()

@@ -111,6 +111,33 @@ void *imexStreamNative(void *stream);
  * pair: imexEventRecord returns a new timing event recorded on the stream. */
 void *imexEventRecord(void *stream);
 float imexEventElapsedMs(void *startEvent, void *stopEvent);
+/* Device address of the stream's status word (0 = fine): kernels with bounded waits store a
+ * code there when a wait runs out, gpuWait reads it. */
+void *imexStreamStatusWord(void *stream);
+/* Adds n to the launch counter (for kernels launched outside gpuLaunchKernel). */
+void imexNoteLaunches(uint64_t n);
+
+/* ---- peer memory between the processes of one node (one process per GPU).  No reference
+ * counterpart: the reference leaves data exchange between ranks to its distributed runtime
+ * (the `_idtr_*` calls behind lib/Dialect/DistRuntime).  Used by the row-sharded GEMM to
+ * replicate B with the copy engines over NVLink instead of an SM-based collective.
+ *
+ * imexIpcExport: writes the 64-byte CUDA IPC handle of a gpuMemAlloc allocation (devPtr must
+ *   be the pointer gpuMemAlloc returned) to handleOut.  imexIpcOpen: maps an allocation
+ *   another process exported and returns its address here; imexIpcClose unmaps it.
+ * imexMemCopyAsync: cudaMemcpyAsync on the stream, no wait (gpuMemCopy blocks); with an
+ *   IPC-mapped source this is a DMA over NVLink that occupies no SM.
+ * imexPeerBarrier: stream-ordered barrier over `world` ranks.  peerFlags[r] is rank r's flag
+ *   array (`world` zero-initialised uint32 words, the local one for r == rank, IPC-mapped
+ *   otherwise); every rank passes the same, strictly growing `epoch`.  A one-block kernel
+ *   stores the epoch into this rank's slot of every peer's array and polls the local array;
+ *   the wait is bounded (~2 s; IMEX_PEER_WAIT_CYCLES) and its expiry is reported by gpuWait. */
+int imexIpcExport(void *devPtr, void *handleOut);
+void *imexIpcOpen(const void *handle);
+void imexIpcClose(void *mapped);
+void imexMemCopyAsync(void *stream, void *dst, const void *src, size_t bytes);
+void imexPeerBarrier(void *stream, void **peerFlags, int world, int rank, uint32_t epoch);
+
 /* Kernels of this library launched since load (all streams). */
 uint64_t imexLaunchCount(void);
 /* Name of the device kernel family the last gpuLaunchKernel on this stream

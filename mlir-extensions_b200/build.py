@@ -38,6 +38,7 @@ RUNTIME_SOURCES = [
     "kernels/flash_attention.cu",
     "kernels/wait_selftest.cu",
     "runtime/cuda_runtime_wrappers.cu",
+    "runtime/peer_copy.cu",
     "runtime/stats.cpp",
 ]
 UTILS_SOURCES = ["utils/runner_utils.cpp"]

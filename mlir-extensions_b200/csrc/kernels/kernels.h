@@ -19,6 +19,7 @@ enum Status : unsigned {
   kStatusTmaWaitTimeout = 1,   // producer gave up waiting for a free smem stage
   kStatusMmaWaitTimeout = 2,   // MMA warp gave up waiting for operands / a free accumulator
   kStatusEpiWaitTimeout = 3,   // epilogue gave up waiting for an accumulator
+  kStatusPeerWaitTimeout = 4,  // the cross-rank barrier gave up waiting for a peer
   kStatusSelfTestTimeout = 99  // the wait self-test ran out, as it is meant to
 };
 

@@ -730,6 +730,12 @@ void *imexStreamNative(void *stream) {
   return stream ? static_cast<void *>(static_cast<Stream *>(stream)->stream) : nullptr;
 }
 
+void *imexStreamStatusWord(void *stream) {
+  return stream ? static_cast<void *>(static_cast<Stream *>(stream)->status_dev) : nullptr;
+}
+
+void imexNoteLaunches(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
 void *imexEventRecord(void *stream) {
   return catchAll([&]() -> void * {
     auto *s = static_cast<Stream *>(stream);

@@ -35,7 +35,12 @@ Two ways to hide the replication (`overlap=`):
              the GEMM is a main launch on all SMs but 32 and, on a second
              stream, a helper launch on those 32 SMs that starts when the
              replication has left them.  Written for 8 GPUs, where the first
-             launch of "calls" cannot be made short enough; not yet measured.
+             launch of "calls" cannot be made short enough.
+    "ce"     no NCCL kernel at all: B is replicated by the copy engines over NVLink
+             (PeerReplicator: IPC-mapped buffers, a pull of this rank's slice from the
+             source, a stream-ordered barrier, pulls of the other slices from their
+             holders), beside the GEMM of the previous call; every call is ONE GEMM
+             launch on all SMs.  B has to be handed over once with register_b().
 """
 from . import blob as B
 from . import runtime as rt
@@ -153,6 +158,102 @@ def plan_main_helper(rows, n_cols, k, sm_count=148, comm_sms=32, comm_ms=0.4, tf
     return w_main, n_cols - w_main
 
 
+def plan_peer_slices(rows, world, src=0):
+    """Row slices of B for the copy-engine replication: B's `rows` rows are cut into one
+    block per rank other than `src` (the partition rule of shard_rows over world-1 parts).
+    Returns {rank: (row0, nrows)} for the non-source ranks, in rank order.  Rank r pulls its
+    own slice from `src` first, then every other slice from the rank that holds it."""
+    holders = [r for r in range(world) if r != src]
+    out = {}
+    for i, r in enumerate(holders):
+        out[r] = (rt.imexShardOffset(i, len(holders), rows), rt.imexShardSize(i, len(holders), rows))
+    return out
+
+
+class PeerReplicator:
+    """B[k, n] of rank `src` copied into every rank's own HBM by the copy engines.
+
+    Buffers come from gpuMemAlloc and are shared between the processes with CUDA IPC
+    (imexIpcExport / imexIpcOpen); all copies are imexMemCopyAsync on `comm_session`'s stream
+    (DMA over NVLink, no SM); the ranks meet once per replication in imexPeerBarrier.
+    Per call, on a rank r other than src:   pull slice r from src   ->   barrier   ->
+    pull slice j from rank j for every other j.  src only takes part in the barrier.
+    Two replica buffers alternate so that the replication for the next call can run while
+    the GEMM of this one still reads the other buffer.  Collective: every rank constructs,
+    registers and replicates in the same order."""
+
+    def __init__(self, comm_session, rank, world, k, n, elt_bytes, src=0, group=None):
+        import ctypes as C
+
+        import torch.distributed as dist
+        self.C, self.dist, self.group = C, dist, group
+        self.sess, self.rank, self.world, self.src = comm_session, rank, world, src
+        self.k, self.n, self.esz = k, n, elt_bytes
+        self.nbytes = k * n * elt_bytes
+        self.slices = plan_peer_slices(k, world, src)
+        self.epoch = 0
+        self.local = {}    # name -> local device pointer
+        self.peer = {}     # (name, rank) -> address of rank's buffer in this process
+        names = ["flags"] + (["source"] if rank == src else ["replica0", "replica1"])
+        for name in names:
+            size = 256 if name == "flags" else self.nbytes
+            self.local[name] = comm_session.alloc(size)
+        zeros = (C.c_char * 256)()
+        rt.gpuMemCopy(comm_session.stream, self.local["flags"], C.addressof(zeros), 256)
+        mine = {}
+        for name, ptr in self.local.items():
+            buf = (C.c_char * 64)()
+            rt.library().imexIpcExport(ptr, C.addressof(buf))
+            mine[name] = bytes(buf)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        for r, handles in enumerate(everyone):
+            for name, h in handles.items():
+                if r == rank:
+                    self.peer[(name, r)] = self.local[name]
+                else:
+                    hb = (C.c_char * 64).from_buffer_copy(h)
+                    self.peer[(name, r)] = rt.library().imexIpcOpen(C.addressof(hb))
+        self.flag_ptrs = (C.c_void_p * world)(*[self.peer[("flags", r)] for r in range(world)])
+        dist.barrier(group=group)  # nobody starts copying before everyone has mapped everything
+
+    def register_source(self, b_full_ptr):
+        """src: copies B (device pointer) into the shared source buffer.  Other ranks: no-op.
+        Call again whenever B changes; the next replicate() carries the new contents."""
+        if self.rank == self.src:
+            rt.gpuMemCopy(self.sess.stream, self.local["source"], b_full_ptr, self.nbytes)
+
+    def local_b(self, which):
+        """Device pointer of the full B on this rank after replicate(which)."""
+        return self.local["source"] if self.rank == self.src else self.local["replica%d" % which]
+
+    def replicate(self, which):
+        """Enqueues one replication into replica buffer `which` on the comm stream."""
+        lib, st = rt.library(), self.sess.stream
+        row_bytes = self.n * self.esz
+        if self.rank != self.src:
+            r0, nr = self.slices[self.rank]
+            lib.imexMemCopyAsync(st, self.local["replica%d" % which] + r0 * row_bytes,
+                                 self.peer[("source", self.src)] + r0 * row_bytes, nr * row_bytes)
+        self.epoch += 1
+        lib.imexPeerBarrier(st, self.flag_ptrs, self.world, self.rank, self.epoch)
+        lib.imexNoteLaunches(1)
+        if self.rank != self.src:
+            holders = [r for r in self.slices if r != self.rank]
+            # start with the next rank up so that no holder serves everybody at once
+            holders = sorted(holders, key=lambda r: (r - self.rank) % self.world)
+            for j in holders:
+                r0, nr = self.slices[j]
+                lib.imexMemCopyAsync(st, self.local["replica%d" % which] + r0 * row_bytes,
+                                     self.peer[("replica%d" % which, j)] + r0 * row_bytes, nr * row_bytes)
+
+    def close(self):
+        for (name, r), ptr in self.peer.items():
+            if r != self.rank:
+                rt.library().imexIpcClose(ptr)
+        self.peer.clear()
+
+
 class RowShardedGemm:
     """C[rows of this rank, :] = epilogue(A[rows of this rank, :] . B), B replicated
     from rank `src` inside every call."""
@@ -167,11 +268,11 @@ class RowShardedGemm:
         self.sess, self.rank, self.world, self.src = session, rank, world, src
         self.m_total, self.n, self.k = m_total, n, k
         self.row0, self.rows = shard_rows(rank, world, m_total)
-        if overlap not in ("slabs", "calls", "prefetch"):
-            raise ValueError("overlap must be 'slabs', 'calls' or 'prefetch'")
+        if overlap not in ("slabs", "calls", "prefetch", "ce"):
+            raise ValueError("overlap must be 'slabs', 'calls', 'prefetch' or 'ce'")
         self.overlap = overlap
         if sm_margin is None:
-            sm_margin = 8 if overlap == "slabs" else 32
+            sm_margin = 8 if overlap == "slabs" else 0 if overlap == "ce" else 32
         self.margin = sm_margin if world > 1 else 0
         if slabs is None:
             slabs = plan_slabs(self.rows, n, world, sm_margin=sm_margin) if overlap == "slabs" else [(0, n)]
@@ -184,7 +285,14 @@ class RowShardedGemm:
         self.slab_sets = None
         self.calls = 0
         self.done_events = [None, None]
-        if world > 1:
+        self.peer = None
+        if world > 1 and overlap == "ce":
+            # copy-engine replication: library-owned buffers shared over CUDA IPC, no NCCL kernel
+            from .session import Session
+            dev_index = device.index if hasattr(device, "index") and device.index is not None else 0
+            self.comm_sess = Session(device=dev_index, adopt_stream=self.comm_stream.cuda_stream)
+            self.peer = PeerReplicator(self.comm_sess, rank, world, k, n, B.DTYPE_BYTES[in_dtype], src=src)
+        elif world > 1:
             self.slab_sets = [[torch.empty((k, w), dtype=elt, device=device) for _, w in self.slabs]
                               for _ in range(2)]
             self.slab_bufs = self.slab_sets[0]
@@ -210,6 +318,10 @@ class RowShardedGemm:
                                ldb=n, ldc=n, sm_margin=max(0, 148 - self.margin))
                 self.launch_descs.append(hdesc)
                 self.helper = (w_main, self.helper_sess.kernel(hdesc))
+        elif world > 1 and overlap == "ce":
+            desc = B.gemm("row_sharded_gemm_whole", self.rows, n, k, in_dtype, epilogue, sm_margin=self.margin)
+            self.launch_descs.append(desc)
+            self.launches.append((0, 0, 0, session.kernel(desc)))
         elif world > 1 and overlap == "calls" and len(self.slabs) == 1:
             w1, w2 = plan_two_parts(self.rows, n, k, comm_sms=self.margin, comm_ms=comm_ms)
             for j, (c0, w, margin) in enumerate([(0, w1, self.margin), (w1, w2, 0)]):
@@ -253,6 +365,60 @@ class RowShardedGemm:
             cur.wait_event(joined)
             return len(self.launches) + 1
         return len(self.launches)
+
+    class _Ptr:
+        """A device address with the data_ptr() of a tensor."""
+
+        def __init__(self, ptr):
+            self.ptr = int(ptr)
+
+        def data_ptr(self):
+            return self.ptr
+
+    def register_b(self, b_full):
+        """overlap="ce": hands B (valid on `src`) to the copy-engine replication.  Collective;
+        needed once, and again whenever B's contents change."""
+        if self.peer is not None:
+            self.torch.cuda.current_stream().synchronize()
+            self.peer.register_source(b_full.data_ptr())
+            self.registered = b_full.data_ptr()
+
+    def check(self):
+        """Waits for the replication stream and raises (through the library's error convention)
+        if a cross-rank barrier gave up waiting for a peer."""
+        if self.peer is not None:
+            self.comm_sess.wait()
+
+    def close(self):
+        """Collective: unmaps the peers' buffers, then frees this rank's."""
+        if self.peer is not None:
+            self.torch.cuda.synchronize()
+            self.peer.dist.barrier()
+            self.peer.close()
+            self.peer.dist.barrier()
+            self.comm_sess.close()
+            self.peer = None
+
+    def _call_ce(self, a_shard, c_shard):
+        """One call with the replication on the copy engines: replica buffer `which` is filled
+        on the comm stream (beside the GEMM of the previous call, which reads the other
+        buffer), then ONE GEMM launch on all SMs."""
+        torch = self.torch
+        cur = torch.cuda.current_stream()
+        which = self.calls & 1
+        self.calls += 1
+        if self.done_events[which] is not None:  # the GEMM that last read this replica buffer
+            self.comm_stream.wait_event(self.done_events[which])
+        self.peer.replicate(which)
+        ready = torch.cuda.Event()
+        ready.record(self.comm_stream)
+        cur.wait_event(ready)
+        self.slab_bufs = [RowShardedGemm._Ptr(self.peer.local_b(which))]
+        n_launch = self.launch_gemms(a_shard, c_shard, self.slab_bufs)
+        done = torch.cuda.Event()
+        done.record(cur)
+        self.done_events[which] = done
+        return n_launch
 
     def _call_prefetch(self, a_shard, b_full, c_shard, b_ready, prefetch_next):
         """overlap="prefetch": see the module text.  All of the call's work, the helper launch
@@ -323,6 +489,10 @@ class RowShardedGemm:
         torch = self.torch
         if self.world == 1:
             return self.launch_gemms(a_shard, c_shard, bufs=[b_full])
+        if self.overlap == "ce":
+            if getattr(self, "registered", None) is None:
+                raise RuntimeError("overlap='ce': call register_b(b_full) on every rank first")
+            return self._call_ce(a_shard, c_shard)
         if self.overlap == "prefetch":
             return self._call_prefetch(a_shard, b_full, c_shard, b_ready, prefetch_next)
         cur = torch.cuda.current_stream()

@@ -59,6 +59,13 @@ def _load():
         "imexShardOffset": (C.c_int64, [C.c_int64, C.c_int64, C.c_int64]),
         "imexStat": (C.c_float, [C.c_int, C.POINTER(C.c_float), sz]),
         "imexSelfTestWaitTimeout": (None, [vp]),
+        "imexStreamStatusWord": (vp, [vp]),
+        "imexNoteLaunches": (None, [C.c_uint64]),
+        "imexIpcExport": (C.c_int, [vp, vp]),
+        "imexIpcOpen": (vp, [vp]),
+        "imexIpcClose": (None, [vp]),
+        "imexMemCopyAsync": (None, [vp, vp, vp, sz]),
+        "imexPeerBarrier": (None, [vp, C.POINTER(vp), C.c_int, C.c_int, C.c_uint32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
