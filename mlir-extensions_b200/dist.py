@@ -170,36 +170,23 @@ def plan_peer_slices(rows, world, src=0):
     return out
 
 
-class PeerReplicator:
-    """B[k, n] of rank `src` copied into every rank's own HBM by the copy engines.
+class _PeerBuffers:
+    """Device buffers of this rank shared with the other processes of the node over CUDA IPC,
+    the peers' buffers mapped here, and the flag arrays of imexPeerBarrier.  Collective."""
 
-    Buffers come from gpuMemAlloc and are shared between the processes with CUDA IPC
-    (imexIpcExport / imexIpcOpen); all copies are imexMemCopyAsync on `comm_session`'s stream
-    (DMA over NVLink, no SM); the ranks meet once per replication in imexPeerBarrier.
-    Per call, on a rank r other than src:   pull slice r from src   ->   barrier   ->
-    pull slice j from rank j for every other j.  src only takes part in the barrier.
-    Two replica buffers alternate so that the replication for the next call can run while
-    the GEMM of this one still reads the other buffer.  Collective: every rank constructs,
-    registers and replicates in the same order."""
-
-    def __init__(self, comm_session, rank, world, k, n, elt_bytes, src=0, group=None):
+    def __init__(self, session, rank, world, sizes, group=None):
         import ctypes as C
 
         import torch.distributed as dist
         self.C, self.dist, self.group = C, dist, group
-        self.sess, self.rank, self.world, self.src = comm_session, rank, world, src
-        self.k, self.n, self.esz = k, n, elt_bytes
-        self.nbytes = k * n * elt_bytes
-        self.slices = plan_peer_slices(k, world, src)
+        self.sess, self.rank, self.world = session, rank, world
         self.epoch = 0
         self.local = {}    # name -> local device pointer
-        self.peer = {}     # (name, rank) -> address of rank's buffer in this process
-        names = ["flags"] + (["source"] if rank == src else ["replica0", "replica1"])
-        for name in names:
-            size = 256 if name == "flags" else self.nbytes
-            self.local[name] = comm_session.alloc(size)
+        self.peer = {}     # (name, rank) -> address of that rank's buffer in this process
+        for name, size in list(sizes.items()) + [("flags", 256)]:
+            self.local[name] = session.alloc(size)
         zeros = (C.c_char * 256)()
-        rt.gpuMemCopy(comm_session.stream, self.local["flags"], C.addressof(zeros), 256)
+        rt.gpuMemCopy(session.stream, self.local["flags"], C.addressof(zeros), 256)
         mine = {}
         for name, ptr in self.local.items():
             buf = (C.c_char * 64)()
@@ -217,6 +204,41 @@ class PeerReplicator:
         self.flag_ptrs = (C.c_void_p * world)(*[self.peer[("flags", r)] for r in range(world)])
         dist.barrier(group=group)  # nobody starts copying before everyone has mapped everything
 
+    def barrier(self, stream=None):
+        """Stream-ordered barrier over the ranks (every rank calls it the same number of times)."""
+        self.epoch += 1
+        rt.library().imexPeerBarrier(stream or self.sess.stream, self.flag_ptrs, self.world, self.rank, self.epoch)
+        rt.library().imexNoteLaunches(1)
+
+    def pull(self, dst, src, nbytes, stream=None):
+        rt.library().imexMemCopyAsync(stream or self.sess.stream, dst, src, nbytes)
+
+    def close(self):
+        for (name, r), ptr in self.peer.items():
+            if r != self.rank:
+                rt.library().imexIpcClose(ptr)
+        self.peer.clear()
+
+
+class PeerReplicator(_PeerBuffers):
+    """B[k, n] of rank `src` copied into every rank's own HBM by the copy engines.
+
+    Buffers come from gpuMemAlloc and are shared between the processes with CUDA IPC
+    (imexIpcExport / imexIpcOpen); all copies are imexMemCopyAsync on `comm_session`'s stream
+    (DMA over NVLink, no SM); the ranks meet once per replication in imexPeerBarrier.
+    Per call, on a rank r other than src:   pull slice r from src   ->   barrier   ->
+    pull slice j from rank j for every other j.  src only takes part in the barrier.
+    Two replica buffers alternate so that the replication for the next call can run while
+    the GEMM of this one still reads the other buffer.  Collective: every rank constructs,
+    registers and replicates in the same order."""
+
+    def __init__(self, comm_session, rank, world, k, n, elt_bytes, src=0, group=None):
+        self.src, self.k, self.n, self.esz = src, k, n, elt_bytes
+        self.nbytes = k * n * elt_bytes
+        self.slices = plan_peer_slices(k, world, src)
+        sizes = {"source": self.nbytes} if rank == src else {"replica0": self.nbytes, "replica1": self.nbytes}
+        super().__init__(comm_session, rank, world, sizes, group)
+
     def register_source(self, b_full_ptr):
         """src: copies B (device pointer) into the shared source buffer.  Other ranks: no-op.
         Call again whenever B changes; the next replicate() carries the new contents."""
@@ -229,29 +251,50 @@ class PeerReplicator:
 
     def replicate(self, which):
         """Enqueues one replication into replica buffer `which` on the comm stream."""
-        lib, st = rt.library(), self.sess.stream
         row_bytes = self.n * self.esz
+        name = "replica%d" % which
         if self.rank != self.src:
             r0, nr = self.slices[self.rank]
-            lib.imexMemCopyAsync(st, self.local["replica%d" % which] + r0 * row_bytes,
-                                 self.peer[("source", self.src)] + r0 * row_bytes, nr * row_bytes)
-        self.epoch += 1
-        lib.imexPeerBarrier(st, self.flag_ptrs, self.world, self.rank, self.epoch)
-        lib.imexNoteLaunches(1)
+            self.pull(self.local[name] + r0 * row_bytes, self.peer[("source", self.src)] + r0 * row_bytes,
+                      nr * row_bytes)
+        self.barrier()
         if self.rank != self.src:
-            holders = [r for r in self.slices if r != self.rank]
             # start with the next rank up so that no holder serves everybody at once
-            holders = sorted(holders, key=lambda r: (r - self.rank) % self.world)
-            for j in holders:
+            for j in sorted((r for r in self.slices if r != self.rank), key=lambda r: (r - self.rank) % self.world):
                 r0, nr = self.slices[j]
-                lib.imexMemCopyAsync(st, self.local["replica%d" % which] + r0 * row_bytes,
-                                     self.peer[("replica%d" % which, j)] + r0 * row_bytes, nr * row_bytes)
+                self.pull(self.local[name] + r0 * row_bytes, self.peer[(name, j)] + r0 * row_bytes, nr * row_bytes)
 
-    def close(self):
-        for (name, r), ptr in self.peer.items():
-            if r != self.rank:
-                rt.library().imexIpcClose(ptr)
-        self.peer.clear()
+
+class PeerAllGather(_PeerBuffers):
+    """An array of `rows` rows of `row_bytes` each, of which every rank fills its own block of
+    rows (the partition rule of shard_rows) and fetches the others' blocks over NVLink with
+    the copy engines.  Used by the host-buffer pipeline: the ranks of a node upload 1/world
+    of B each instead of all of B each."""
+
+    def __init__(self, session, rank, world, rows, row_bytes, group=None):
+        self.rows, self.row_bytes = rows, row_bytes
+        self.blocks = [shard_rows(r, world, rows) for r in range(world)]
+        super().__init__(session, rank, world, {"array": rows * row_bytes}, group)
+
+    @property
+    def array(self):
+        return self.local["array"]
+
+    def own_block(self):
+        """(byte offset, bytes) of the rows this rank has to fill before exchange()."""
+        r0, nr = self.blocks[self.rank]
+        return r0 * self.row_bytes, nr * self.row_bytes
+
+    def exchange(self, stream=None):
+        """Enqueues: barrier (every block is filled), pulls of the other ranks' blocks, barrier
+        (nobody still reads a block that its owner may refill)."""
+        self.barrier(stream)
+        for j in sorted((r for r in range(self.world) if r != self.rank), key=lambda r: (r - self.rank) % self.world):
+            r0, nr = self.blocks[j]
+            if nr:
+                self.pull(self.array + r0 * self.row_bytes, self.peer[("array", j)] + r0 * self.row_bytes,
+                          nr * self.row_bytes, stream)
+        self.barrier(stream)
 
 
 class RowShardedGemm:

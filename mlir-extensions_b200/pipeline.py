@@ -6,9 +6,12 @@ lib/Conversion/GPUXToLLVM/GPUXToLLVMPass.cpp:691-707); gpuMemCopy blocks, as in
 both reference back-ends.  For operands that start and end in host memory that
 order leaves the GPU idle during the transfers and the PCIe link idle in one
 direction at a time.  Here the rows of A are cut into chunks and three host
-threads, each with its own stream handle, run a pipeline:
+threads and the B loader, each with its own stream handle, run a pipeline:
 
-    uploader    gpuMemCopy(B), then gpuMemCopy(A chunk i)            host -> device
+    B loader    gpuMemCopy(B) — or, when the ranks of a node share the upload of B
+                (b_gather): gpuMemCopy(this rank's rows of B), then the other rows
+                from the peers over NVLink                            host -> device
+    uploader    gpuMemCopy(A chunk i)                                 host -> device
     launcher    gpuLaunchKernel(GEMM on chunk i); gpuWait
     downloader  gpuMemCopy(C chunk i)                                device -> host
 
@@ -27,7 +30,10 @@ from . import runtime as rt
 class HostPipelinedGemm:
     """C_host[rows, n] = epilogue(A_host[rows, k] . B_host[k, n]) for host arrays given by address."""
 
-    def __init__(self, device, rows, n, k, in_dtype=B.BF16, epilogue=B.EPI_NONE, chunks=8):
+    def __init__(self, device, rows, n, k, in_dtype=B.BF16, epilogue=B.EPI_NONE, chunks=8, b_gather=None):
+        """b_gather: None, or a dist.PeerAllGather over B's k rows of n elements shared by the
+        ranks of the node: this process then uploads only its own block of rows of B and
+        fetches the other blocks from the ranks that uploaded them (NVLink, copy engines)."""
         import ctypes as C
         self._dev = C.c_int32(int(device))
         self.rows, self.n, self.k = rows, n, k
@@ -36,10 +42,12 @@ class HostPipelinedGemm:
         self.bounds = [(rows * i // chunks, rows * (i + 1) // chunks) for i in range(chunks)]
         dev = C.addressof(self._dev)
         self.s_up = rt.gpuCreateStream(dev, None)
+        self.s_b = rt.gpuCreateStream(dev, None)
         self.s_run = rt.gpuCreateStream(dev, None)
         self.s_down = rt.gpuCreateStream(dev, None)
+        self.b_gather = b_gather
         self.dA = rt.gpuMemAlloc(self.s_run, rows * k * self.esz, 64, False)
-        self.dB = rt.gpuMemAlloc(self.s_run, k * n * self.esz, 64, False)
+        self.dB = b_gather.array if b_gather is not None else rt.gpuMemAlloc(self.s_run, k * n * self.esz, 64, False)
         self.dC = rt.gpuMemAlloc(self.s_run, rows * n * 4, 64, False)
         self.kernels = []
         self._blobs = []
@@ -65,8 +73,20 @@ class HostPipelinedGemm:
                     computed.put(None)
             return run
 
+        b_ready = threading.Event()
+
+        def upload_b():
+            if self.b_gather is None:
+                rt.gpuMemCopy(self.s_b, self.dB, b_host_ptr, self.k * self.n * self.esz)
+            else:  # this rank's rows of B from the host, the rest from the peers
+                off, nbytes = self.b_gather.own_block()
+                if nbytes:
+                    rt.gpuMemCopy(self.s_b, self.dB + off, b_host_ptr + off, nbytes)
+                self.b_gather.exchange(self.s_b)
+                rt.gpuWait(self.s_b)
+            b_ready.set()
+
         def upload():
-            rt.gpuMemCopy(self.s_up, self.dB, b_host_ptr, self.k * self.n * self.esz)
             for i, (r0, r1) in enumerate(self.bounds):
                 off = r0 * self.k * self.esz
                 rt.gpuMemCopy(self.s_up, self.dA + off, a_host_ptr + off, (r1 - r0) * self.k * self.esz)
@@ -77,6 +97,10 @@ class HostPipelinedGemm:
             while True:
                 i = uploaded.get()
                 if i is None:
+                    break
+                while not b_ready.wait(0.05) and not errors:  # B travels beside the first chunks of A
+                    pass
+                if errors:
                     break
                 r0, _ = self.bounds[i]
                 rt.gpuLaunchKernel(self.s_run, self.kernels[i], (1, 1, 1), (1, 1, 1), 0,
@@ -94,7 +118,7 @@ class HostPipelinedGemm:
                 off = r0 * self.n * 4
                 rt.gpuMemCopy(self.s_down, c_host_ptr + off, self.dC + off, (r1 - r0) * self.n * 4)
 
-        threads = [threading.Thread(target=guard(f)) for f in (upload, launch, download)]
+        threads = [threading.Thread(target=guard(f)) for f in (upload_b, upload, launch, download)]
         for t in threads:
             t.start()
         for t in threads:
@@ -103,7 +127,7 @@ class HostPipelinedGemm:
             raise errors[0]
 
     def close(self):
-        for p in (self.dA, self.dB, self.dC):
+        for p in (self.dA, self.dC) + (() if self.b_gather is not None else (self.dB,)):
             rt.gpuMemFree(self.s_run, p)
-        for s in (self.s_up, self.s_run, self.s_down):
+        for s in (self.s_up, self.s_b, self.s_run, self.s_down):
             rt.gpuStreamDestroy(s)

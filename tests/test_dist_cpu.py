@@ -152,3 +152,22 @@ def test_main_and_helper_plan_for_the_benchmark_gemm(world):
     t_help = 0.4 + est * (w_help / n) * 148 / 32
     assert abs(t_main - t_help) <= 0.25 * max(t_main, t_help)
     assert rows.plan_main_helper(1024, 256, 64) == (256, 0)   # one column block: nothing to hand over
+
+
+def test_copy_engine_replication_slices_cover_b_once():
+    """Row slices of B for the copy-engine replication: one block per rank other than the source,
+    by the reference's partition rule over world-1 parts; together they cover every row once."""
+    from mlir_extensions_b200.dist import plan_peer_slices
+    for world in (2, 3, 4, 8):
+        for src in (0, world - 1):
+            for rows in (8192, 1000, 7, 1):
+                slices = plan_peer_slices(rows, world, src)
+                assert sorted(slices) == [r for r in range(world) if r != src]
+                covered = []
+                for r in sorted(slices):
+                    r0, nr = slices[r]
+                    covered += list(range(r0, r0 + nr))
+                assert covered == list(range(rows))
+                sizes = [n for _, n in slices.values()]
+                assert max(sizes) - min(sizes) <= 1
+    assert plan_peer_slices(8192, 8, 0)[1] == (0, 1170) and plan_peer_slices(8192, 8, 0)[7] == (7021, 1171)
