@@ -566,15 +566,15 @@ def main():
         # the public host-buffer call: rows of A in chunks, three host threads (upload /
         # launch+wait / download), every transfer a blocking gpuMemCopy through the C ABI
         from mlir_extensions_b200.pipeline import HostPipelinedGemm
-        gather, gsess = None, None
+        b_gather, gsess = None, None
         if world > 1 and not args.e2e_full_b:
             # the ranks share the upload of B: each sends its own block of rows over PCIe and
             # fetches the other blocks from its peers over NVLink (copy engines)
             from mlir_extensions_b200.dist import PeerAllGather
             gsess = pkg.Session(device=local_rank)
-            gather = PeerAllGather(gsess, rank, world, K_DIM, N_DIM * 2)
+            b_gather = PeerAllGather(gsess, rank, world, K_DIM, N_DIM * 2)
         own = HostPipelinedGemm(local_rank, rows, N_DIM, K_DIM, B.BF16, B.EPI_SILU, chunks=args.e2e_chunks,
-                                b_gather=gather)
+                                b_gather=b_gather)
 
         def e2e_step():
             own(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
@@ -590,7 +590,7 @@ def main():
         # sums its parts in another order than a whole one: equal to the last bits, not bit for bit
         assert torch.allclose(hC[:64], Cm[:64].cpu(), rtol=1e-4, atol=1e-6), \
             "e2e result differs from the resident run"
-        b_up = gather.own_block()[1] if gather is not None else hB.numel() * 2
+        b_up = b_gather.own_block()[1] if b_gather is not None else hB.numel() * 2
         h2d, d2h = int(hA.numel() * 2 + b_up), int(hC.numel() * 4)
         e2e = {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
@@ -600,13 +600,13 @@ def main():
                                       "d2h": world * d2h / (e2e_ms * 1e-3) / 1e9},
                "note": "per rank; every rank uploads its A shard and " +
                        ("its 1/%d of B (the other rows of B come from the peers over NVLink)" % world
-                        if gather is not None else "B") +
+                        if b_gather is not None else "B") +
                        ", downloads its C shard; uploads, GEMMs on row chunks and downloads overlap "
                        "(host threads, blocking gpuMemCopy / gpuLaunchKernel / gpuWait only)"}
         own.close()
-        if gather is not None:
+        if b_gather is not None:
             barrier()
-            gather.close()
+            b_gather.close()
             barrier()
             gsess.close()
         del hA, hB, hC

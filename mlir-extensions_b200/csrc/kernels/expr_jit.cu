@@ -37,6 +37,19 @@ __device__ __forceinline__ u16 f2b(float f) { u16 h; asm("cvt.rn.bf16.f32 %0, %1
 __device__ __forceinline__ float maximumf(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
 __device__ __forceinline__ float minimumf(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 __device__ __forceinline__ float relu_ugt(float x) { return !(x <= 0.0f) ? x : 0.0f; }
+// two 16-bit values in one register (element 0 in the low half)
+__device__ __forceinline__ unsigned pack_h(float lo, float hi) { unsigned d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
+__device__ __forceinline__ unsigned pack_b(float lo, float hi) { unsigned d; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
+__device__ __forceinline__ float lo_h(unsigned x) { return h2f((u16)(x & 0xffffu)); }
+__device__ __forceinline__ float hi_h(unsigned x) { return h2f((u16)(x >> 16)); }
+__device__ __forceinline__ float lo_b(unsigned x) { return __uint_as_float(x << 16); }
+__device__ __forceinline__ float hi_b(unsigned x) { return __uint_as_float(x & 0xffff0000u); }
+__device__ __forceinline__ unsigned add_h(unsigned a, unsigned b) { unsigned d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned sub_h(unsigned a, unsigned b) { unsigned d; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned mul_h(unsigned a, unsigned b) { unsigned d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned add_b(unsigned a, unsigned b) { unsigned d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned sub_b(unsigned a, unsigned b) { unsigned d; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned mul_b(unsigned a, unsigned b) { unsigned d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 )SRC";
 
 struct TypeInfo {
@@ -87,6 +100,68 @@ std::string emit_body(const unsigned char *code, int ncode, const std::string &r
       const char *f = op == 64 ? "__fadd_rn" : op == 65 ? "__fsub_rn" : op == 66 ? "__fmul_rn"
                       : op == 67 ? "__fdiv_rn" : op == 68 ? "maximumf" : "minimumf";
       st.push_back(def(std::string(f) + "(" + a + ", " + b + ")", true));
+    }
+  }
+  return st.back();
+}
+
+// The same program on PAIRS of 16-bit values held in one 32-bit register (f16 / bf16
+// elementwise kernels).  add / sub / mul run as one packed instruction on both values:
+// rounding the exact result once to an 11-bit (8-bit) significand equals rounding it to
+// f32's 24 bits first and then to 16 bits (24 >= 2 * 11 + 2, so the double rounding is
+// innocuous), i.e. the result is bit for bit that of extend - operate in f32 - round.  neg
+// and abs are sign-bit operations.  Everything else unpacks to f32, applies the f32
+// function and packs with one rounding conversion for both values.
+std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, std::ostringstream &os) {
+  const std::string sfx = bf16 ? "_b" : "_h";
+  std::vector<std::string> st;
+  int t = 0;
+  auto def = [&](const std::string &rhs) {
+    const std::string name = "t" + std::to_string(t++);
+    os << "    const unsigned " << name << " = " << rhs << ";\n";
+    return name;
+  };
+  auto via_f32 = [&](const std::string &fn_lo, const std::string &fn_hi) {
+    return "pack" + sfx + "(" + fn_lo + ", " + fn_hi + ")";
+  };
+  for (int i = 0; i < ncode; ++i) {
+    const int op = code[i];
+    if (op >= 1 && op <= 12) {
+      st.push_back("x" + std::to_string((op - 1) % 4));
+    } else if (op == 13 || op == 14) {
+      st.push_back(op == 13 ? "pc0" : "pc1");
+    } else if (op == 15) {
+      st.push_back("0u");
+    } else if (op == 16) {
+      st.push_back(bf16 ? "0x3f803f80u" : "0x3c003c00u");
+    } else if (op < 64) {
+      const std::string a = st.back();
+      st.pop_back();
+      if (op == 32) { st.push_back(def("(" + a + " ^ 0x80008000u)")); continue; }
+      if (op == 33) { st.push_back(def("(" + a + " & 0x7fff7fffu)")); continue; }
+      const std::string lo = "lo" + sfx + "(" + a + ")", hi = "hi" + sfx + "(" + a + ")";
+      auto f = [&](const std::string &x) -> std::string {
+        switch (op) {
+        case 34: return "logf(" + x + ")";
+        case 35: return "expf(" + x + ")";
+        case 36: return "__fsqrt_rn(" + x + ")";
+        case 37: return "__fdiv_rn(1.0f, __fsqrt_rn(" + x + "))";
+        case 38: return "tanhf(" + x + ")";
+        default: return "relu_ugt(" + x + ")";
+        }
+      };
+      st.push_back(def(via_f32(f(lo), f(hi))));
+    } else {
+      const std::string b = st.back();
+      st.pop_back();
+      const std::string a = st.back();
+      st.pop_back();
+      if (op == 64) { st.push_back(def("add" + sfx + "(" + a + ", " + b + ")")); continue; }
+      if (op == 65) { st.push_back(def("sub" + sfx + "(" + a + ", " + b + ")")); continue; }
+      if (op == 66) { st.push_back(def("mul" + sfx + "(" + a + ", " + b + ")")); continue; }
+      const char *fn = op == 67 ? "__fdiv_rn" : op == 68 ? "maximumf" : "minimumf";
+      st.push_back(def(via_f32(std::string(fn) + "(lo" + sfx + "(" + a + "), lo" + sfx + "(" + b + "))",
+                               std::string(fn) + "(hi" + sfx + "(" + a + "), hi" + sfx + "(" + b + "))")));
     }
   }
   return st.back();
@@ -168,6 +243,26 @@ std::string generate(const unsigned char *code, int ncode, int n_inputs, int dty
          << "    *reinterpret_cast<" << vec_type(vec * in_bytes) << " *>(v" << k << ") = *reinterpret_cast<const "
          << vec_type(vec * in_bytes) << " *>(p" << k << " + " << (sh.mode[k] == 0 ? "base" : "col") << ");\n";
     }
+  }
+  if (dtype != kF32 && vec >= 2) {
+    // 16-bit arithmetic on pairs: see emit_body_packed
+    const bool bf = dtype == kBF16;
+    const std::string sfx = bf ? "_b" : "_h";
+    os << "    const unsigned pc0 = pack" << sfx << "(c0, c0), pc1 = pack" << sfx << "(c1, c1);\n";
+    os << "    __align__(16) " << out.ctype << " r[" << vec << "];\n"
+       << "#pragma unroll\n    for (int e = 0; e < " << vec / 2 << "; ++e) {\n";
+    for (int k = 0; k < n_inputs; ++k) {
+      if (sh.mode[k] < 0) continue;
+      if (sh.mode[k] == 2) os << "    const unsigned x" << k << " = pack" << sfx << "(s" << k << ", s" << k << ");\n";
+      else os << "    const unsigned x" << k << " = reinterpret_cast<const unsigned *>(v" << k << ")[e];\n";
+    }
+    const std::string r = emit_body_packed(code, ncode, bf, os);
+    if (out_dtype == kF32) os << "    r[2 * e] = lo" << sfx << "(" << r << ");\n    r[2 * e + 1] = hi" << sfx << "(" << r << ");\n    }\n";
+    else os << "    reinterpret_cast<unsigned *>(r)[e] = " << r << ";\n    }\n";
+    os << "    *reinterpret_cast<" << vec_type(vec * out_bytes) << " *>(y + base) = *reinterpret_cast<const "
+       << vec_type(vec * out_bytes) << " *>(r);\n";
+    os << "  }\n}\n";
+    return os.str();
   }
   os << "    __align__(16) " << out.ctype << " r[" << vec << "];\n"
      << "#pragma unroll\n    for (int e = 0; e < " << vec << "; ++e) {\n";
