@@ -339,7 +339,8 @@ private:
 
 } // namespace
 
-bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why) {
+bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why,
+                   const std::vector<Type> *types) {
   if (op.name != "linalg.generic" || !op.body) {
     why = "not a linalg.generic";
     return false;
@@ -359,7 +360,14 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
       why = "indexing maps over different iteration spaces";
       return false;
     }
-  auto typeOf = [&](size_t k) -> const Type & { return k < nIn ? op.insTypes[k] : op.outsTypes[k - nIn]; };
+  if (types && types->size() != nIn + nOut) {
+    why = "operand type list of the wrong length";
+    return false;
+  }
+  auto typeOf = [&](size_t k) -> const Type & {
+    if (types) return (*types)[k];
+    return k < nIn ? op.insTypes[k] : op.outsTypes[k - nIn];
+  };
   for (size_t k = 0; k < nIn + nOut; ++k) {
     const Type &t = typeOf(k);
     if (!computeType(t.elt)) {

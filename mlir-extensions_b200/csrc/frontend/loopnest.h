@@ -35,7 +35,10 @@ struct LoopNestKernel {
 // False (with `why`) when the op cannot be written as a loop nest: dynamic shapes, an
 // operation or element type without a C counterpart, an output indexed by a reduction
 // dimension, or a parallel dimension missing from an output's map.
-bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why);
+// `types`, when given, replaces the operand types written in the op (ins, then outs): the
+// shapes the operands actually have here (one rank's rows of a row-sharded array).
+bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why,
+                   const std::vector<Type> *types = nullptr);
 
 } // namespace fe
 } // namespace imex

@@ -64,8 +64,8 @@ public:
       skip();
     }
     bool wrapped = false;
-    if (startsWith("module")) {
-      pos += 6;
+    if (startsWith("builtin.module") || startsWith("module")) {
+      pos += startsWith("builtin.module") ? 14 : 6;
       skip();
       if (peek() == '@') m.name = ident();
       skip();
@@ -86,6 +86,22 @@ public:
       }
       if (startsWith("func.func") || startsWith("func ")) {
         m.functions.push_back(function());
+      } else if (startsWith("shard.grid") || startsWith("mesh.mesh")) {
+        // shard.grid @mesh4(shape = 4)   (test/Dialect/NDArray/Extensions/sharding_propagation.mlir:4)
+        pos += startsWith("shard.grid") ? 10 : 9;
+        Grid g;
+        g.name = ident();
+        expect('(');
+        expectWord("shape");
+        expect('=');
+        do {
+          skip();
+          if (peek() == '?') { ++pos; g.shape.push_back(-1); }
+          else g.shape.push_back(static_cast<int64_t>(number().value));
+          skip();
+        } while (peek() == 'x' && ++pos);
+        expect(')');
+        m.grids.push_back(g);
       } else if (startsWith("memref.global") || startsWith("llvm.func") ||
                  startsWith("llvm.mlir.global")) {
         skipLineOrRegion();
@@ -841,6 +857,50 @@ private:
       expect(':');
       op->operandTypes.push_back(type());
       expectWord("into");
+      op->resultTypes.push_back(type());
+    } else if (n == "shard.sharding" || n == "mesh.sharding") {
+      // %s = shard.sharding @mesh4 split_axes = [[0]] [sharded_dims_offsets = [..]] : !shard.sharding
+      op->callee = ident();  // the grid
+      expectWord("split_axes");
+      expect('=');
+      expect('[');
+      skip();
+      if (peek() != ']') {
+        do {
+          expect('[');
+          std::vector<int64_t> axes;
+          skip();
+          if (peek() != ']') {
+            do {
+              axes.push_back(static_cast<int64_t>(number().value));
+            } while (accept(','));
+          }
+          expect(']');
+          op->reassociation.push_back(axes);
+        } while (accept(','));
+      }
+      expect(']');
+      for (const char *extra : {"halo_sizes", "sharded_dims_offsets", "partial"})
+        if (acceptWord(extra)) {
+          expect('=');
+          skip();
+          if (peek() == '[') skipBalanced('[', ']');
+          else attrValue();
+        }
+      expect(':');
+      skip();
+      while (!eof() && (identChar(s[pos]) || s[pos] == '!')) ++pos;  // !shard.sharding
+      Type t;
+      t.kind = Type::Scalar;
+      t.elt = "sharding";
+      op->resultTypes.push_back(t);
+    } else if (n == "shard.shard" || n == "mesh.shard") {
+      // %1 = shard.shard %0 to %s [annotate_for_users] : tensor<..>
+      operandList(op->operands);
+      expectWord("to");
+      operandList(op->operands);
+      acceptWord("annotate_for_users");
+      expect(':');
       op->resultTypes.push_back(type());
     } else if (n == "memref.dealloc" || n == "gpu.dealloc") {
       operandList(op->operands);

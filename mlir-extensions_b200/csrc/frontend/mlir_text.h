@@ -96,9 +96,17 @@ struct Function {
   Block body;
 };
 
+// shard.grid @name(shape = 4): a grid of processes arrays are split over
+// (test/Dialect/NDArray/Extensions/sharding_propagation.mlir:4)
+struct Grid {
+  std::string name;
+  std::vector<int64_t> shape;
+};
+
 struct Module {
   std::string name;
   std::vector<Function> functions;
+  std::vector<Grid> grids;
   const Function *find(const std::string &symbol) const;
 };
 

@@ -17,6 +17,10 @@
 //
 //   imex-b200-runner FILE.mlir [-e main] [--entry-point-result=void]
 //                    [--shared-libs=...] [--emit-plan] [--trace] [--all-loopnests]
+//                    [--shard-rank R --shard-count N]
+// --shard-rank / --shard-count: this process is rank R of the N ranks of the program's
+//              shard.grid; tensors annotated `shard.shard ... split_axes = [[0]]` are held
+//              and computed by rows, rank R owning its block of the partition rule.
 // --emit-plan: recognise and print the kernels and ABI calls without touching
 //              a GPU.   --trace (or IMEX_B200_TRACE=1): log ABI calls to stderr.
 #include "../../../include/imex_b200_blob.h"
@@ -47,6 +51,9 @@ bool g_trace = false;  // log ABI calls
 // reference's linalg-to-loops lowering makes of it (a self-check of the hot-path kernels
 // against the plain lowering, and the mode the CPU checker under oracle/ runs in)
 bool g_allLoopNests = false;
+// --shard-rank R --shard-count N: this process is rank R of the N ranks of a shard.grid;
+// values annotated `split_axes = [[0]]` hold only this rank's block of rows
+int g_shardRank = 0, g_shardCount = 1;
 
 [[noreturn]] void die(const std::string &msg) {
   std::cout.flush();
@@ -159,11 +166,20 @@ struct Value {
   // what is known about the contents without reading them back
   bool isFill = false;
   double fillValue = 0;
+  // >= 0: the tensor is split by rows over the ranks of a shard.grid; this is the extent of
+  // dim 0 of the whole array, type.shape[0] the rows this rank holds
+  int64_t globalRows = -1;
+};
+
+struct Sharding {  // a shard.sharding value
+  std::string grid;
+  std::vector<std::vector<int64_t>> splitAxes;
 };
 
 struct Frame {
   std::map<std::string, Value> vals;
   ConstantTable constants;
+  std::map<std::string, Sharding> shardings;
 };
 
 class Runner {
@@ -192,7 +208,30 @@ private:
   std::vector<std::unique_ptr<std::vector<char>>> blobs;  // modules are cached by blob address
 
   // ---- device helpers ---------------------------------------------------
-  Value makeTensor(void *stream, const Type &t) {
+  // While a linalg op with a row-sharded operand runs: extent of the split dimension in the
+  // whole array (G), rows of this rank (L) and their offset.  Results whose leading extent is
+  // G are allocated with L rows and are row-sharded themselves.
+  struct ShardCtx {
+    bool active = false;
+    int64_t G = 0, L = 0, r0 = 0;
+  } curShard;
+
+  Type localType(Type t) const {
+    if (curShard.active && !t.shape.empty() && t.shape[0] == curShard.G) t.shape[0] = curShard.L;
+    return t;
+  }
+
+  Value makeTensor(void *stream, const Type &declared) {
+    const Type t = localType(declared);
+    Value made = makeTensorExact(stream, t);
+    // every tensor an op on a row-sharded operand makes is split the same way
+    if (curShard.active && !declared.shape.empty() &&
+        (declared.shape[0] == curShard.G || declared.shape[0] == curShard.L))
+      made.globalRows = curShard.G;
+    return made;
+  }
+
+  Value makeTensorExact(void *stream, const Type &t) {
     if (t.unranked) die("cannot allocate an unranked tensor");
     for (auto d : t.shape)
       if (d < 0) die("dynamic shapes are not supported: kernel arguments carry no shape");
@@ -441,7 +480,7 @@ private:
   void materialise(Value &v) {
     ExprProgram p;
     if (!compile(v.lazy, p)) die("internal: an elementwise chain outgrew the fused kernel");
-    Value out = makeTensor(curStream, v.type);
+    Value out = makeTensorExact(curStream, v.type);
     int64_t rows, cols;
     shape2d(v.type, v.lazy, rows, cols);
     std::vector<void *> ptrs;
@@ -487,7 +526,8 @@ private:
   // it at the loop point, or the column reduce of kInputFusion.mlir.in:29-39).
   void elementwiseOp(const Op &op, const Block &b, Frame &fr, const std::string &where) {
     ElementwiseInfo info;
-    const Type outT = op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0];
+    const Type declaredT = op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0];
+    const Type outT = localType(declaredT);
     bool fusable = classifyElementwise(op, fr.constants, info) &&
                    (outT.elt == "f32" || outT.elt == "f16" || outT.elt == "bf16");
     bool broadcast = false;
@@ -533,6 +573,7 @@ private:
     out.kind = Value::Tensor;
     out.type = outT;
     out.lazy = tree;
+    if (curShard.active && !declaredT.shape.empty() && declaredT.shape[0] == curShard.G) out.globalRows = curShard.G;
     const std::string res = op.results.empty() ? "" : op.results[0];
     bool defer = !res.empty() && (!curUses || allUsesVisible(res, b, *curUses));
     auto us = usersOf(res, b);
@@ -657,7 +698,15 @@ private:
     std::string why;
     if (op.results.empty())
       die(where + "linalg ops on buffers (no results) are not supported: the runner works on tensors");
-    if (!buildLoopNest(op, fr.constants, k, why))
+    std::vector<Type> actual;  // operand types as they are here: this rank's rows of a row-sharded array
+    if (curShard.active) {
+      for (size_t i = 0; i < op.ins.size(); ++i) {
+        auto it = fr.vals.find(op.ins[i]);
+        actual.push_back(it != fr.vals.end() && it->second.kind == Value::Tensor ? it->second.type : op.insTypes[i]);
+      }
+      for (auto &t : op.outsTypes) actual.push_back(localType(t));
+    }
+    if (!buildLoopNest(op, fr.constants, k, why, actual.empty() ? nullptr : &actual))
       die(where + op.name + " is not a recognised hot-path op (" + because + ") and cannot be written as a loop nest (" +
           why + "); no CPU fallback");
     std::vector<void *> ptrs;
@@ -794,6 +843,13 @@ private:
         }
         fr.constants[op.results[0]] = v.scalar;
         fr.vals[op.results[0]] = v;
+      } else if (n == "shard.sharding" || n == "mesh.sharding") {
+        Sharding sh;
+        sh.grid = op.callee;
+        sh.splitAxes = op.reassociation;
+        fr.shardings[op.results[0]] = sh;
+      } else if (n == "shard.shard" || n == "mesh.shard") {
+        shardOp(op, fr, stream);
       } else if (n == "memref.dealloc" || n == "gpu.dealloc") {
         fr.vals.erase(op.operands[0]);
       } else if (n == "call" || n == "func.call" || n == "llvm.call") {
@@ -834,6 +890,43 @@ private:
       }
     }
     return {};
+  }
+
+  // %1 = shard.shard %0 to %s: with `split_axes = [[0]]` (dim 0 over the grid's axis 0,
+  // test/Dialect/NDArray/Extensions/sharding_propagation.mlir:9-12) the result is this rank's
+  // block of rows by the partition rule of lib/Dialect/NDArray/Extensions/MeshShardingExtensions.cpp:
+  // 74-100; an unsplit sharding (replication) leaves the value whole.
+  void shardOp(const Op &op, Frame &fr, void *stream) {
+    const std::string where = "line " + std::to_string(op.line) + ": ";
+    if (op.operands.size() != 2) die(where + "shard.shard takes a value and a sharding");
+    auto sit = fr.shardings.find(op.operands[1]);
+    if (sit == fr.shardings.end()) die(where + "unknown sharding " + op.operands[1]);
+    const Sharding &sh = sit->second;
+    Value &x = get(fr, op.operands[0], op);
+    bool split0 = false;
+    for (size_t axis = 0; axis < sh.splitAxes.size(); ++axis) {
+      if (sh.splitAxes[axis].empty()) continue;
+      if (axis != 0 || sh.splitAxes[axis] != std::vector<int64_t>{0})
+        die(where + "only row sharding (split_axes = [[0]]) is mapped onto the ranks; columns stay whole");
+      split0 = true;
+    }
+    const Grid *grid = nullptr;
+    for (auto &g : mod.grids)
+      if (g.name == sh.grid) grid = &g;
+    if (!grid) die(where + "unknown grid " + sh.grid);
+    if (!split0 || g_shardCount == 1 || x.kind != Value::Tensor || x.globalRows >= 0) {
+      fr.vals[op.results[0]] = x;  // replicated, a single rank, or already this rank's rows
+      return;
+    }
+    if (grid->shape.empty() || (grid->shape[0] >= 0 && grid->shape[0] != g_shardCount))
+      die(where + "grid " + sh.grid + " has " + (grid->shape.empty() ? std::string("no") : std::to_string(grid->shape[0])) +
+          " ranks on its first axis but the runner was started with --shard-count " + std::to_string(g_shardCount));
+    if (x.type.shape.empty()) die(where + "a rank-0 tensor cannot be split");
+    const int64_t G = x.type.shape[0];
+    const int64_t r0 = imexShardOffset(g_shardRank, g_shardCount, G), rows = imexShardSize(g_shardRank, g_shardCount, G);
+    trace("shard: rows [" + std::to_string(r0) + ", " + std::to_string(r0 + rows) + ") of " + std::to_string(G) +
+          " on rank " + std::to_string(g_shardRank) + " of " + std::to_string(g_shardCount));
+    fr.vals[op.results[0]] = rowBlock(stream, x, r0, rows);
   }
 
   void scalarOp(const Op &op, Frame &fr) {
@@ -969,8 +1062,99 @@ private:
     return out;
   }
 
+  // This rank's block of rows of `v` (whose dim 0 has extent G): a copy of the contiguous rows.
+  Value rowBlock(void *stream, Value &whole, int64_t r0, int64_t rows) {
+    if (whole.lazy) materialise(whole);
+    Type t = whole.type;
+    const int64_t G = t.shape[0];
+    t.shape[0] = rows;
+    Value v = makeTensorExact(stream, t);
+    v.isFill = whole.isFill;
+    v.fillValue = whole.fillValue;
+    v.globalRows = G;
+    const size_t rowBytes = G ? whole.buf->bytes / static_cast<size_t>(G) : 0;
+    trace("gpuMemCopy(device -> device, " + std::to_string(v.buf->bytes) + " bytes)  // rows [" + std::to_string(r0) +
+          ", " + std::to_string(r0 + rows) + ") of " + std::to_string(G) + ": this rank's block");
+    if (!g_plan && v.buf->bytes)
+      gpuMemCopy(stream, v.buf->ptr, static_cast<char *>(whole.buf->ptr) + static_cast<size_t>(r0) * rowBytes, v.buf->bytes);
+    return v;
+  }
+
+  // A linalg op one of whose operands is split by rows over the ranks of a shard.grid
+  // (shard.shard ... split_axes = [[0]]): every rank runs the op on its own rows.  The loop
+  // dimension that walks the split rows must be a parallel one and must index dim 0 of every
+  // operand it indexes at all; those operands (and the result) are taken, or allocated, with
+  // this rank's rows only.  Anything that would need an exchange between the ranks — a
+  // reduction over the split dimension, a transpose of it — is refused.
   void linalgOp(const Op &op, const Block &b, Frame &fr, void *stream, std::set<const Op *> &absorbed,
                 std::map<std::string, const Op *> &defs, std::map<std::string, int> &uses) {
+    auto where = "line " + std::to_string(op.line) + ": ";
+    int sharded = -1;
+    for (size_t i = 0; i < op.ins.size() && sharded < 0; ++i) {
+      auto it = fr.vals.find(op.ins[i]);
+      if (it != fr.vals.end() && it->second.globalRows >= 0) sharded = static_cast<int>(i);
+    }
+    if (sharded < 0) {
+      linalgOpBody(op, b, fr, stream, absorbed, defs, uses);
+      return;
+    }
+    const Value &sv = fr.vals[op.ins[sharded]];
+    ShardCtx ctx;
+    ctx.active = true;
+    ctx.G = sv.globalRows;
+    ctx.L = sv.type.shape[0];
+    ctx.r0 = imexShardOffset(g_shardRank, g_shardCount, ctx.G);
+    // which loop dimension walks the split rows, and which operands it indexes
+    const size_t nIn = op.ins.size(), nAll = nIn + op.outs.size();
+    std::vector<int> pos(nAll, -1);  // position of that dimension in each operand's map, -1: not used
+    if (op.name == "linalg.matmul" || op.name == "linalg.matmul_transpose_b") {
+      if (sharded != 0) die(where + "only the rows of A (and C) of a matmul can be split over ranks");
+      pos[0] = 0;
+      pos[nIn] = 0;
+    } else if (op.name == "linalg.generic" && op.maps.size() == nAll) {
+      const MapResult &r0 = op.maps[sharded].results.empty() ? MapResult() : op.maps[sharded].results[0];
+      if (op.maps[sharded].results.empty() || !r0.simple || r0.isConst)
+        die(where + "the split dimension of a row-sharded operand must be indexed by a plain loop dimension");
+      const int sd = static_cast<int>(r0.value);
+      if (op.iterators[sd] != "parallel")
+        die(where + "a reduction over the dimension that is split over ranks needs an exchange between them: not supported");
+      for (size_t k = 0; k < nAll; ++k)
+        for (size_t r = 0; r < op.maps[k].results.size(); ++r) {
+          const MapResult &mr = op.maps[k].results[r];
+          if (!mr.simple) {
+            if (mr.expr.find("d" + std::to_string(sd)) != std::string::npos)
+              die(where + "the split dimension inside a compound index expression is not supported");
+            continue;
+          }
+          if (!mr.isConst && mr.value == sd) {
+            if (r != 0) die(where + "the dimension that is split over ranks must index dim 0 of every operand (no transposes of it)");
+            pos[k] = 0;
+          }
+        }
+    } else {
+      die(where + op.name + " on a row-sharded operand is not supported");
+    }
+    if (pos[nIn] != 0) die(where + "the result of an op on a row-sharded operand must be split the same way");
+    // operands the split dimension indexes but that are still whole: take this rank's rows
+    std::vector<std::pair<std::string, Value>> saved;
+    for (size_t k = 0; k < nAll; ++k) {
+      if (pos[k] != 0) continue;
+      const std::string &name = k < nIn ? op.ins[k] : op.outs[k - nIn];
+      auto it = fr.vals.find(name);
+      if (it == fr.vals.end() || it->second.kind != Value::Tensor || it->second.globalRows >= 0) continue;
+      if (it->second.type.shape.empty() || it->second.type.shape[0] != ctx.G) continue;
+      saved.emplace_back(name, it->second);
+      Value local = rowBlock(stream, it->second, ctx.r0, ctx.L);
+      fr.vals[name] = local;
+    }
+    curShard = ctx;
+    linalgOpBody(op, b, fr, stream, absorbed, defs, uses);
+    curShard = ShardCtx();
+    for (auto &sv2 : saved) fr.vals[sv2.first] = sv2.second;
+  }
+
+  void linalgOpBody(const Op &op, const Block &b, Frame &fr, void *stream, std::set<const Op *> &absorbed,
+                    std::map<std::string, const Op *> &defs, std::map<std::string, int> &uses) {
     Classified c = classify(op, fr.constants);
     auto where = "line " + std::to_string(op.line) + ": ";
     if (op.results.empty())
@@ -989,7 +1173,7 @@ private:
       return;
     }
     const std::string res = op.results.empty() ? "" : op.results[0];
-    const Type outT = op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0];
+    const Type outT = localType(op.resultTypes.empty() ? op.outsTypes[0] : op.resultTypes[0]);
 
     switch (c.kind) {
     case Kind::Matmul: {
@@ -1337,6 +1521,8 @@ int main(int argc, char **argv) {
     else if (a.rfind("-e=", 0) == 0) entry = a.substr(3);
     else if (a == "--emit-plan") g_plan = true;
     else if (a == "--all-loopnests") g_allLoopNests = true;
+    else if (a == "--shard-rank" && i + 1 < argc) g_shardRank = std::atoi(argv[++i]);
+    else if (a == "--shard-count" && i + 1 < argc) g_shardCount = std::atoi(argv[++i]);
     else if (a == "--trace") g_trace = true;
     else if (a.rfind("--entry-point-result", 0) == 0 || a.rfind("-entry-point-result", 0) == 0) {
       if (a.find("void") == std::string::npos) die("only --entry-point-result=void is supported");
@@ -1350,6 +1536,7 @@ int main(int argc, char **argv) {
   }
   if (std::getenv("IMEX_B200_TRACE")) g_trace = true;
   if (std::getenv("IMEX_B200_ALL_LOOPNESTS")) g_allLoopNests = true;
+  if (g_shardCount < 1 || g_shardRank < 0 || g_shardRank >= g_shardCount) die("--shard-rank must lie in [0, --shard-count)");
   if (file.empty()) die("usage: imex-b200-runner FILE.mlir [-e main] [--entry-point-result=void] [--emit-plan]");
   try {
     Module m = parseModule(readFile(file));

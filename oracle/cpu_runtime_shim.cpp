@@ -201,6 +201,17 @@ void *gpuLaunchKernel(void *, void *kernel, size_t, size_t, size_t, size_t, size
   return nullptr;
 }
 
+// Block partition of the reference (lib/Dialect/NDArray/Extensions/MeshShardingExtensions.cpp:
+// 74-100): shards are extent / n long and the last extent % n of them one longer.
+int64_t imexShardSize(int64_t shard, int64_t numShards, int64_t extent) {
+  const int64_t longer_from = numShards - extent % numShards;
+  return extent / numShards + (shard >= longer_from ? 1 : 0);
+}
+int64_t imexShardOffset(int64_t shard, int64_t numShards, int64_t extent) {
+  const int64_t longer_from = numShards - extent % numShards;
+  return shard * (extent / numShards) + (shard > longer_from ? shard - longer_from : 0);
+}
+
 void gpuWait(void *) {}
 void gpuModuleUnload(void *) {}
 
