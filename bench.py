@@ -236,6 +236,8 @@ CASES = {
     "transpose": "transpose 8192x8192 (config 4b)",
     "attention": "attention forward, 4 heads x 4096 keys x d 64, f16 (the reference test's shape)",
     "loop_fusion": "fused elementwise chain (log, absf, addf, subf) on 8192x8192 f32",
+    "loop_fusion_f16": "the same chain on 8192x8192 f16 (packed 16-bit arithmetic)",
+    "loop_fusion_bf16": "the same chain on 8192x8192 bf16 (packed 16-bit arithmetic)",
 }
 
 
@@ -283,13 +285,15 @@ def run_case(name, iters):
         k = sess.kernel(B.attention_fwd(name, heads, n_ctx, 64, B.F16, 0.5))
         ptrs = [Q.data_ptr(), Kt.data_ptr(), Vt.data_ptr(), Ot.data_ptr()]
         work, unit = 4.0 * heads * n_ctx * n_ctx * 64 / 1e12, "TFLOP/s"
-    elif name == "loop_fusion":
-        X = torch.empty((8192, 8192), dtype=torch.float32, device=dev).uniform_(0.5, 4.0)
-        X1 = torch.empty((8192, 8192), dtype=torch.float32, device=dev).uniform_(-2.0, 2.0)
+    elif name.startswith("loop_fusion"):
+        tdt, bdt = {"loop_fusion": (torch.float32, B.F32), "loop_fusion_f16": (torch.float16, B.F16),
+                    "loop_fusion_bf16": (torch.bfloat16, B.BF16)}[name]
+        X = torch.empty((8192, 8192), dtype=tdt, device=dev).uniform_(0.5, 4.0)
+        X1 = torch.empty((8192, 8192), dtype=tdt, device=dev).uniform_(-2.0, 2.0)
         Y = torch.empty_like(X)
-        k = sess.kernel(B.expr(name, 8192, 8192, "in0 log in1 abs add in0 sub", B.F32))
+        k = sess.kernel(B.expr(name, 8192, 8192, "in0 log in1 abs add in0 sub", bdt))
         ptrs = [X.data_ptr(), X1.data_ptr(), Y.data_ptr()]
-        work, unit = 3 * X.numel() * 4 / 1e9, "GB/s"
+        work, unit = 3 * X.numel() * X.element_size() / 1e9, "GB/s"
     elif name.startswith("reduce"):
         nrows = 32768 if name == "reduce" else 4096
         X = torch.empty((nrows, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
@@ -340,8 +344,8 @@ def main():
                          "every broadcast and every step's GEMM launches and report the intervals")
     ap.add_argument("--comm-ms", type=float, default=0.5,
                     help="N>1, --overlap calls: how long the first GEMM launch (NCCL beside it) should last")
-    ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "calls"),
-                    choices=["slabs", "calls", "prefetch", "ce"],
+    ap.add_argument("--overlap", default=os.environ.get("IMEX_BENCH_OVERLAP", "ce"),
+                    choices=["slabs", "calls", "ce"],
                     help="N>1: hide the replication of B inside a call (column slabs) or across calls")
     ap.add_argument("--case", default=None, choices=sorted(CASES),
                     help="run ONE small kernel case --iters times and exit (ncu captures)")
@@ -414,8 +418,6 @@ def main():
     def step():
         # world > 1: B lives on rank 0; its column slabs are NCCL-broadcast on a side
         # stream and land in local HBM, each slab's GEMM starts when its slab is in
-        if args.overlap == "prefetch":  # this step also starts the replication for the next one
-            return gemm(A, Bm, Cm, b_ready=True, prefetch_next=Bm)
         return gemm(A, Bm, Cm, b_ready=True)  # B is resident on rank 0 before the step
 
     sampler = ClockSampler(local_rank)
@@ -639,19 +641,18 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_total": M_total, "rows_per_rank": rows,
                        "partition": "block rows, last extent%N shards one longer",
-                       "collective": (("NCCL broadcast of B from rank 0 inside every step, "
-                                       + ("in column slabs %s overlapped with the slab GEMMs; every GEMM "
-                                          "launch leaves %d SMs free" if gemm.overlap == "slabs" else
-                                          "as one slab %s into one of two replica buffers, overlapped with "
-                                          "the previous step's GEMM, whose first launch leaves %d SMs free "
-                                          "and whose second uses all SMs" if gemm.overlap == "calls" else
-                                          "as one slab %s started by the previous step, beside its main GEMM "
-                                          "launch; a helper launch takes over the %d SMs the broadcast held"))
-                                      % ([w for _, w in gemm.slabs], gemm.margin)) if world > 1 and gemm.overlap != "ce"
-                       else ("B replicated from rank 0 inside every step by the copy engines over NVLink (IPC-mapped "
-                             "buffers: each rank pulls its slice from rank 0, a stream-ordered barrier, then the other "
-                             "slices from their holders), beside the previous step's GEMM; one GEMM launch on all SMs, "
-                             "no NCCL kernel") if world > 1 else "none",
+                       "collective": ("none" if world == 1 else
+                                      "B replicated from rank 0 inside every step by the copy engines over NVLink "
+                                      "(buffers shared over CUDA IPC: each rank pulls its slice from rank 0, a "
+                                      "stream-ordered barrier, then the other slices from their holders), beside "
+                                      "the previous step's GEMM; one GEMM launch on all SMs, no NCCL kernel"
+                                      if gemm.overlap == "ce" else
+                                      "NCCL broadcast of B from rank 0 inside every step, " +
+                                      ("in column slabs %s overlapped with the slab GEMMs; every GEMM launch "
+                                       "leaves %d SMs free" if gemm.overlap == "slabs" else
+                                       "as one slab %s into one of two replica buffers, overlapped with the "
+                                       "previous step's GEMM, whose first launch leaves %d SMs free and whose "
+                                       "second uses all SMs") % ([w for _, w in gemm.slabs], gemm.margin)),
                        "gemm_launch_columns": [int(k_.dims[1]) for k_ in gemm.launch_descs],
                        "l2": "inputs (%d MiB A shard + 128 MiB B) and the %d MiB C shard exceed the 126 MB L2"
                              % (rows * K_DIM * 2 >> 20, rows * N_DIM * 4 >> 20)},

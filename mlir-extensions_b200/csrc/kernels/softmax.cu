@@ -290,6 +290,18 @@ __device__ __forceinline__ float round16(float v) {
   return __half2float(__float2half_rn(v));
 }
 template <bool BF16>
+__device__ __forceinline__ uint16_t to_bits16(float v) {  // v holds a 16-bit value exactly
+  if (BF16) return static_cast<uint16_t>(__float_as_uint(v) >> 16);
+  return __half_as_ushort(__float2half_rn(v));
+}
+template <bool BF16>
+__device__ __forceinline__ uint16_t add16(uint16_t a, uint16_t b) {
+  uint16_t d;
+  if (BF16) asm("add.rn.bf16 %0, %1, %2;" : "=h"(d) : "h"(a), "h"(b));
+  else asm("add.rn.f16 %0, %1, %2;" : "=h"(d) : "h"(a), "h"(b));
+  return d;
+}
+template <bool BF16>
 __global__ void __launch_bounds__(256)
 softmax_rows_x16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ y, int64_t rows,
                         int cols, float max_init) {
@@ -314,9 +326,23 @@ softmax_rows_x16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ y
       row[i] = round16<BF16>(expf(round16<BF16>(__fsub_rn(row[i], mx))));
     __syncthreads();
     if (threadIdx.x == 0) {
-      float sum = 0.0f;
-      for (int i = 0; i < cols; ++i) sum = round16<BF16>(__fadd_rn(row[i], sum));
-      total = sum;
+      // The chain s <- round16(x_i + s) is the critical path of the kernel.  One native 16-bit
+      // add per step (add.rn.f16 / add.rn.bf16, latency of one instruction) gives the same
+      // bits as add in f32 and round: the exact sum rounded once to 11 (8) bits equals the sum
+      // rounded to f32's 24 bits and then to 11 (8), since 24 >= 2 * 11 + 2.  The values of
+      // the row are already 16-bit values held in f32, so converting them is exact and off
+      // the chain.
+      uint16_t sum = 0;
+      int i = 0;
+      for (; i + 4 <= cols; i += 4) {
+        uint16_t v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = to_bits16<BF16>(row[i + u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum = add16<BF16>(v[u], sum);
+      }
+      for (; i < cols; ++i) sum = add16<BF16>(to_bits16<BF16>(row[i]), sum);
+      total = BF16 ? __uint_as_float(static_cast<uint32_t>(sum) << 16) : __half2float(__ushort_as_half(sum));
     }
     __syncthreads();
     const float sum = total;

@@ -19,28 +19,23 @@ multiple of the CTA pairs in flight) so that cutting B costs no tail.  The
 GEMM leaves `sm_margin` SMs free so that the NCCL kernel of the next slab can
 run beside it.  Softmax and row-reduce shard by rows with no exchange at all.
 
-Two ways to hide the replication (`overlap=`):
+Three ways to replicate B (`overlap=`):
 
-    "slabs"  inside one call, as above: several GEMM launches per call.
-    "calls"  across calls (default): B travels as ONE slab into one of two
-             replica buffers and the replication for call i+1 runs beside the
-             GEMM of call i (the host enqueues ahead).  NCCL's broadcast runs
-             32 CTAs and finishes only when all of them have had an SM, so the
-             GEMM is cut into two launches over column ranges of the same
-             replica: the first leaves 32 SMs free and lasts about as long as
-             the replication, the second uses the whole machine.  A lone call
-             pays the whole replication up front.
-    "prefetch"  as "calls", but the caller names the NEXT call's B
-             (`prefetch_next=`) and the call itself starts that replication;
-             the GEMM is a main launch on all SMs but 32 and, on a second
-             stream, a helper launch on those 32 SMs that starts when the
-             replication has left them.  Written for 8 GPUs, where the first
-             launch of "calls" cannot be made short enough.
-    "ce"     no NCCL kernel at all: B is replicated by the copy engines over NVLink
-             (PeerReplicator: IPC-mapped buffers, a pull of this rank's slice from the
-             source, a stream-ordered barrier, pulls of the other slices from their
-             holders), beside the GEMM of the previous call; every call is ONE GEMM
-             launch on all SMs.  B has to be handed over once with register_b().
+    "ce"     (default) no NCCL kernel at all: B is replicated by the copy engines over
+             NVLink (PeerReplicator: buffers shared over CUDA IPC, a pull of this rank's
+             slice from the source, a stream-ordered barrier, pulls of the other slices
+             from their holders), beside the GEMM of the previous call; every call is ONE
+             GEMM launch on all SMs.  B is handed over once with register_b().
+             Measured on 8 GPUs: 0.81 ms per step against 0.88 ms for "calls".
+    "calls"  NCCL broadcast across calls: B travels as ONE slab into one of two replica
+             buffers and the replication for call i+1 runs beside the GEMM of call i (the
+             host enqueues ahead).  NCCL's broadcast runs 32 CTAs and finishes only when
+             all of them have had an SM, so the GEMM is cut into two launches over column
+             ranges of the same replica: the first leaves 32 SMs free and lasts about as
+             long as the replication, the second uses the whole machine.  For processes
+             that cannot share memory over CUDA IPC.
+    "slabs"  NCCL broadcast inside one call, as described above: several GEMM launches
+             per call; for a lone call.
 """
 from . import blob as B
 from . import runtime as rt
@@ -140,22 +135,6 @@ def plan_two_parts(rows, n_cols, k, sm_count=148, comm_sms=32, comm_ms=0.5, tflo
             best = (cost, cb1)
     w1 = min(best[1] * PAIR_TILE, n_cols)
     return w1, n_cols - w1
-
-
-def plan_main_helper(rows, n_cols, k, sm_count=148, comm_sms=32, comm_ms=0.4, tflops=1400.0):
-    """Column split (w_main, w_helper) for `overlap="prefetch"`: the main launch runs on
-    sm_count - comm_sms SMs for the whole call, the helper on comm_sms SMs once the
-    replication (comm_ms) has left them; widths in whole 256-column blocks, chosen so that
-    both finish together.  w_helper may be 0 (too few column blocks)."""
-    col_blocks = -(-n_cols // PAIR_TILE)
-    if col_blocks < 2:
-        return n_cols, 0
-    est_ms = 2.0 * rows * n_cols * k / (tflops * 1e9)            # on all SMs
-    total = (est_ms * sm_count + comm_sms * comm_ms) / sm_count   # helper's SMs idle for comm_ms
-    frac_main = min(1.0, (sm_count - comm_sms) * total / (est_ms * sm_count))
-    main_blocks = min(col_blocks - 1, max(1, round(frac_main * col_blocks)))
-    w_main = main_blocks * PAIR_TILE
-    return w_main, n_cols - w_main
 
 
 def plan_peer_slices(rows, world, src=0):
@@ -302,17 +281,18 @@ class RowShardedGemm:
     from rank `src` inside every call."""
 
     def __init__(self, session, rank, world, m_total, n, k, in_dtype=B.BF16, epilogue=B.EPI_NONE,
-                 src=0, sm_margin=None, slabs=None, device=None, overlap="calls", comm_ms=0.5):
-        """overlap="slabs": sm_margin (default 8) SMs stay free during every slab GEMM.
-        overlap="calls": the first of two launches leaves sm_margin (default 32: NCCL
-        runs 32 CTAs here) SMs free, the second none (see plan_two_parts)."""
+                 src=0, sm_margin=None, slabs=None, device=None, overlap="ce", comm_ms=0.5):
+        """overlap="ce": one launch on all SMs (sm_margin 0).  overlap="slabs": sm_margin (default
+        8) SMs stay free during every slab GEMM.  overlap="calls": the first of two launches
+        leaves sm_margin (default 32: NCCL runs 32 CTAs here) SMs free, the second none (see
+        plan_two_parts)."""
         import torch
         self.torch = torch
         self.sess, self.rank, self.world, self.src = session, rank, world, src
         self.m_total, self.n, self.k = m_total, n, k
         self.row0, self.rows = shard_rows(rank, world, m_total)
-        if overlap not in ("slabs", "calls", "prefetch", "ce"):
-            raise ValueError("overlap must be 'slabs', 'calls', 'prefetch' or 'ce'")
+        if overlap not in ("slabs", "calls", "ce"):
+            raise ValueError("overlap must be 'slabs', 'calls' or 'ce'")
         self.overlap = overlap
         if sm_margin is None:
             sm_margin = 8 if overlap == "slabs" else 0 if overlap == "ce" else 32
@@ -342,26 +322,8 @@ class RowShardedGemm:
         # launches: (slab index, first column inside the slab, first column of C, kernel)
         self.launches, self.launch_descs = [], []
         self.trace = None         # set to a list to collect four timing events per call (see __call__)
-        self.helper = None        # overlap="prefetch": (first column, kernel of the helper session)
-        self._prefetched = None   # (replica index, work handle, tensor holding B on this rank)
         self.slab_bufs = self.slab_sets[0] if self.slab_sets else None
-        if world > 1 and overlap == "prefetch" and len(self.slabs) == 1:
-            from .session import Session
-            w_main, w_help = plan_main_helper(self.rows, n, k, comm_sms=self.margin, comm_ms=comm_ms)
-            desc = B.gemm("row_sharded_gemm_main", self.rows, w_main, k, in_dtype, epilogue,
-                          ldb=n if w_main != n else 0, ldc=n if w_main != n else 0, sm_margin=self.margin)
-            self.launch_descs.append(desc)
-            self.launches.append((0, 0, 0, session.kernel(desc)))
-            if w_help:
-                # its own stream and session: own k-split workspace, own status word
-                self.helper_stream = torch.cuda.Stream(device=device)
-                dev_index = device.index if hasattr(device, "index") and device.index is not None else 0
-                self.helper_sess = Session(device=dev_index, adopt_stream=self.helper_stream.cuda_stream)
-                hdesc = B.gemm("row_sharded_gemm_helper", self.rows, w_help, k, in_dtype, epilogue,
-                               ldb=n, ldc=n, sm_margin=max(0, 148 - self.margin))
-                self.launch_descs.append(hdesc)
-                self.helper = (w_main, self.helper_sess.kernel(hdesc))
-        elif world > 1 and overlap == "ce":
+        if world > 1 and overlap == "ce":
             desc = B.gemm("row_sharded_gemm_whole", self.rows, n, k, in_dtype, epilogue, sm_margin=self.margin)
             self.launch_descs.append(desc)
             self.launches.append((0, 0, 0, session.kernel(desc)))
@@ -396,17 +358,6 @@ class RowShardedGemm:
                     on_first_wait()
             self.sess.launch(kern, [a_shard.data_ptr(), bufs[slab].data_ptr() + self.elt_bytes * b_col,
                                     c_shard.data_ptr() + 4 * c_col], wait=False)
-        if self.helper is not None:  # the helper's columns, beside the main launch
-            torch = self.torch
-            cur = torch.cuda.current_stream()
-            col, kern = self.helper
-            self.helper_stream.wait_stream(cur)
-            self.helper_sess.launch(kern, [a_shard.data_ptr(), bufs[0].data_ptr() + self.elt_bytes * col,
-                                           c_shard.data_ptr() + 4 * col], wait=False)
-            joined = torch.cuda.Event()
-            joined.record(self.helper_stream)
-            cur.wait_event(joined)
-            return len(self.launches) + 1
         return len(self.launches)
 
     class _Ptr:
@@ -463,62 +414,7 @@ class RowShardedGemm:
         self.done_events[which] = done
         return n_launch
 
-    def _call_prefetch(self, a_shard, b_full, c_shard, b_ready, prefetch_next):
-        """overlap="prefetch": see the module text.  All of the call's work, the helper launch
-        included, is ordered before whatever the caller enqueues next on the current stream."""
-        torch = self.torch
-        import torch.distributed as dist
-        cur = torch.cuda.current_stream()
-        is_src = self.rank == self.src
-        if self._prefetched is not None:
-            which, work, b_here = self._prefetched
-            self._prefetched = None
-        else:  # nothing was prefetched for this call: replicate now
-            which = self.calls & 1
-            if b_ready is None:
-                self.comm_stream.wait_stream(cur)
-            elif b_ready is not True:
-                self.comm_stream.wait_event(b_ready)
-            if self.done_events[which] is not None:
-                self.comm_stream.wait_event(self.done_events[which])
-            b_here = b_full if is_src else self.slab_sets[which][0]
-            with torch.cuda.stream(self.comm_stream):
-                work = dist.broadcast(b_here, src=self.src, async_op=True)
-        self.calls += 1
-        self.slab_bufs = [b_here]
-        work_next = None
-        if prefetch_next is not None:  # resident on `src` already: starts at once
-            nb = which ^ 1
-            if self.done_events[nb] is not None:
-                self.comm_stream.wait_event(self.done_events[nb])
-            b_next = prefetch_next if is_src else self.slab_sets[nb][0]
-            with torch.cuda.stream(self.comm_stream):
-                work_next = dist.broadcast(b_next, src=self.src, async_op=True)
-            self._prefetched = (nb, work_next, b_next)
-        if self.helper is not None:
-            self.helper_stream.wait_stream(cur)       # A and whatever else precedes this call
-        work.wait()
-        self.sess.launch(self.launches[0][3], [a_shard.data_ptr(), b_here.data_ptr(), c_shard.data_ptr()],
-                         wait=False)
-        n_launch = 1
-        if self.helper is not None:
-            col, kern = self.helper
-            with torch.cuda.stream(self.helper_stream):
-                work.wait()
-                if work_next is not None:
-                    work_next.wait()                   # the SMs the replication held are free now
-                self.helper_sess.launch(kern, [a_shard.data_ptr(), b_here.data_ptr() + self.elt_bytes * col,
-                                               c_shard.data_ptr() + 4 * col], wait=False)
-            joined = torch.cuda.Event()
-            joined.record(self.helper_stream)
-            cur.wait_event(joined)
-            n_launch = 2
-        done = torch.cuda.Event()
-        done.record(cur)
-        self.done_events[which] = done
-        return n_launch
-
-    def __call__(self, a_shard, b_full, c_shard, b_ready=None, prefetch_next=None):
+    def __call__(self, a_shard, b_full, c_shard, b_ready=None):
         """a_shard [rows,k], c_shard [rows,n] on this rank; b_full [k,n] valid on `src`
         (a scratch tensor of that shape elsewhere).  Enqueues on the current stream.
 
@@ -527,8 +423,7 @@ class RowShardedGemm:
                  True  -> b_full is already complete in memory (resident weights): the
                           broadcast starts at once and overlaps earlier GEMMs;
                  event -> the broadcast waits for that CUDA event only.
-        prefetch_next (overlap="prefetch" only): the B of the NEXT call, already complete in
-        memory on `src`; its replication starts inside this call."""
+        overlap="ce" replicates the B handed over with register_b() and ignores b_full / b_ready."""
         torch = self.torch
         if self.world == 1:
             return self.launch_gemms(a_shard, c_shard, bufs=[b_full])
@@ -536,8 +431,6 @@ class RowShardedGemm:
             if getattr(self, "registered", None) is None:
                 raise RuntimeError("overlap='ce': call register_b(b_full) on every rank first")
             return self._call_ce(a_shard, c_shard)
-        if self.overlap == "prefetch":
-            return self._call_prefetch(a_shard, b_full, c_shard, b_ready, prefetch_next)
         cur = torch.cuda.current_stream()
         which = self.calls & 1
         self.calls += 1

@@ -138,22 +138,6 @@ def test_two_part_plan_for_the_benchmark_gemm(world):
     assert rows.plan_two_parts(4096, 512, 512) == (512, 0)
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_main_and_helper_plan_for_the_benchmark_gemm(world):
-    """overlap="prefetch": the helper's columns are what 32 SMs can do in the time the main
-    launch needs on the other 116, less the time the replication holds them."""
-    from mlir_extensions_b200 import dist as rows
-    n = k = 8192
-    r = 65536 // world
-    w_main, w_help = rows.plan_main_helper(r, n, k)
-    assert w_main + w_help == n and w_main % 256 == 0 and w_help >= 256
-    est = 2.0 * r * n * k / 1.4e12                   # ms on 148 SMs
-    t_main = est * (w_main / n) * 148 / 116
-    t_help = 0.4 + est * (w_help / n) * 148 / 32
-    assert abs(t_main - t_help) <= 0.25 * max(t_main, t_help)
-    assert rows.plan_main_helper(1024, 256, 64) == (256, 0)   # one column block: nothing to hand over
-
-
 def test_copy_engine_replication_slices_cover_b_once():
     """Row slices of B for the copy-engine replication: one block per rank other than the source,
     by the reference's partition rule over world-1 parts; together they cover every row once."""
@@ -171,3 +155,58 @@ def test_copy_engine_replication_slices_cover_b_once():
                 sizes = [n for _, n in slices.values()]
                 assert max(sizes) - min(sizes) <= 1
     assert plan_peer_slices(8192, 8, 0)[1] == (0, 1170) and plan_peer_slices(8192, 8, 0)[7] == (7021, 1171)
+
+
+def _leaving_worker(rank, world, port, tmp):
+    """Two steps of slab replication; rank 1 leaves between the steps (no collective of its in
+    flight).  Rank 0 must come out of its next replication with an error within the group's
+    timeout, not hang."""
+    import datetime
+    import sys
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    load_package()
+    from mlir_extensions_b200 import dist as rows
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    k, n = 16, 512
+    b_full = torch.ones((k, n)) if rank == 0 else torch.zeros((k, n))
+    slabs = [(0, 256), (256, 256)]
+    bufs = [torch.empty((k, w)) for _, w in slabs]
+    for w in rows.replicate_slabs(b_full, bufs, slabs, src=0, is_src=rank == 0):
+        w.wait()
+    step1_ok = all(bool((b == 1).all()) for b in bufs)
+    if rank == 1:
+        with open(os.path.join(tmp, "rank1.txt"), "w") as f:
+            f.write("left after step 1, step1_ok=%s" % step1_ok)
+        os._exit(0)  # between steps: nothing of this rank is in flight
+    t0 = time.time()
+    outcome = "no error"
+    try:
+        for w in rows.replicate_slabs(b_full, bufs, slabs, src=0, is_src=True):
+            w.wait()
+        dist.barrier()  # a broadcast's sender may complete locally; the barrier needs the peer
+    except Exception as e:  # noqa: BLE001 - the error is what the test is about
+        outcome = "error: " + type(e).__name__
+    with open(os.path.join(tmp, "rank0.txt"), "w") as f:
+        f.write("%s after %.1f s, step1_ok=%s" % (outcome, time.time() - t0, step1_ok))
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_replication_with_an_error(tmp_path):
+    """Failure detection on the host side (no GPU involved): the surviving rank learns of the
+    loss through the process group (connection closed, or the group's short timeout) and gets
+    an exception instead of waiting for ever."""
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung after its peer left"
+    r0 = (tmp_path / "rank0.txt").read_text()
+    assert "left after step 1, step1_ok=True" in (tmp_path / "rank1.txt").read_text()
+    assert r0.startswith("error: ") and "step1_ok=True" in r0, r0
+    assert float(r0.split("after ")[1].split(" s")[0]) < 30
