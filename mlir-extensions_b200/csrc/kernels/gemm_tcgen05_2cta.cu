@@ -573,11 +573,8 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   if (!gemm_tcgen05_2cta_supported(g)) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  static int variant = 1;  // 0: 6 stages x 64 k, 1: 3 stages x 128 k, 2: 4 stages x 64 k
   static bool with_stats = false;
   std::call_once(once, [] {
-    if (const char *e = getenv("IMEX_GEMM_VARIANT")) variant = atoi(e);
-    if (variant < 0 || variant > 2) variant = 1;
     with_stats = getenv("IMEX_GEMM_STATS") != nullptr;
     auto set = [](const void *fn, int bytes) {
       return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -585,16 +582,14 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
     const cudaError_t e[] = {
         set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, false, false>, smem_bytes(3, 128)),
         set((const void *)gemm_tcgen05_2cta_kernel<3, 128, true, false, false>, smem_bytes(3, 128)),
-        set((const void *)gemm_tcgen05_2cta_kernel<6, 64, false, false, false>, smem_bytes(6, 64)),
-        set((const void *)gemm_tcgen05_2cta_kernel<4, 64, false, false, false>, smem_bytes(4, 64)),
         set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, true, false>, smem_bytes(3, 128)),
         set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, false, true>, smem_bytes(3, 128)),
         set((const void *)gemm_tcgen05_2cta_kernel<3, 128, false, true, true>, smem_bytes(3, 128))};
     for (cudaError_t x : e)
       if (x != cudaSuccess && attr_err == cudaSuccess) attr_err = x;
   });
-  const bool transposed = g.trans_a || g.trans_b;  // served by the 3 x 128 kernels only
-  const int BK = (variant == 1 || transposed) ? 128 : 64;
+  const bool transposed = g.trans_a || g.trans_b;
+  const int BK = 128;  // 3 stages of 128 k (see the header of this file)
   if (attr_err != cudaSuccess) return attr_err;
 
   const int64_t lda = g.lda > 0 ? g.lda : (g.trans_a ? g.M : g.K);
@@ -634,7 +629,7 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   p.fast_epilogue = precise_epilogue ? 0 : 1;
   p.stats = nullptr;
   static long long *stats_buf = nullptr;
-  const bool want_stats = with_stats && variant == 1 && !transposed;  // development aid (IMEX_GEMM_STATS=1)
+  const bool want_stats = with_stats && !transposed;  // development aid (IMEX_GEMM_STATS=1)
   if (want_stats) {
     if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 148 * sizeof(long long));
     p.stats = stats_buf;
@@ -681,10 +676,6 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
     gemm_tcgen05_2cta_kernel<3, 128, false, true, false><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
   else if (g.trans_b)
     gemm_tcgen05_2cta_kernel<3, 128, false, false, true><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
-  else if (variant == 0)
-    gemm_tcgen05_2cta_kernel<6, 64, false, false, false><<<grid, block, smem_bytes(6, 64), stream>>>(ta, tb, tc_, tp, p);
-  else if (variant == 2)
-    gemm_tcgen05_2cta_kernel<4, 64, false, false, false><<<grid, block, smem_bytes(4, 64), stream>>>(ta, tb, tc_, tp, p);
   else if (with_stats)
     gemm_tcgen05_2cta_kernel<3, 128, true, false, false><<<grid, block, sm3, stream>>>(ta, tb, tc_, tp, p);
   else

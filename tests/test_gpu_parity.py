@@ -338,12 +338,13 @@ def test_gemm_transposed_and_16bit_on_the_exact_simt_path(pkg, sess, kind):
     assert got16.tobytes() == oracle.to_f16_bits(ref).tobytes()
 
 
-@pytest.mark.parametrize("variant", ["0", "1", "2"])
+@pytest.mark.parametrize("silu", ["hardware exp2 / reciprocal (default)", "reference chain"])
 @pytest.mark.parametrize("shape", [(512, 1024, 128), (300, 520, 200), (1000, 1544, 72), (2304, 4608, 256),
                                    (20000, 512, 64)])
-def test_gemm_pair_kernel_stage_variants(shape, variant):
-    """6 stages x 64 k, 3 stages x 128 k (default) and 4 stages x 64 k of the CTA-pair kernel;
-    the variant is read once per process, so each runs in a child process."""
+def test_gemm_pair_kernel_silu_flavours(shape, silu):
+    """The CTA-pair kernel's silu: through the hardware exp2 / reciprocal units (default) and,
+    with IMEX_GEMM_PRECISE_EPILOGUE=1, as the reference's chain expf - add - IEEE divide - mul;
+    the setting is read once per process, so each runs in a child process."""
     import subprocess
     import sys
     M, N, K = shape
@@ -362,7 +363,9 @@ def test_gemm_pair_kernel_stage_variants(shape, variant):
         "ref = oracle.silu(oracle.matmul_x16_f32(A, Bm, True))\n"
         "err = oracle.rel_frobenius(got, ref)\n"
         "assert not np.isnan(got).any() and err <= 1e-3, err\n" % (os.path.dirname(HERE), M, N, K))
-    env = dict(os.environ, IMEX_GEMM_VARIANT=variant)
+    env = dict(os.environ)
+    if silu == "reference chain":
+        env["IMEX_GEMM_PRECISE_EPILOGUE"] = "1"
     r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env)
     assert r.returncode == 0, r.stdout + r.stderr
 
