@@ -43,7 +43,7 @@ RUNTIME_SOURCES = [
 ]
 UTILS_SOURCES = ["utils/runner_utils.cpp"]
 FRONTEND_SOURCES = ["frontend/mlir_text.cpp", "frontend/recognise.cpp", "frontend/loopnest.cpp",
-                    "frontend/runner_main.cpp"]
+                    "frontend/gpu_kernels.cpp", "frontend/host_loops.cpp", "frontend/runner_main.cpp"]
 BIN = os.path.join(PKG, "bin")
 
 

@@ -86,6 +86,8 @@ public:
       }
       if (startsWith("func.func") || startsWith("func ")) {
         m.functions.push_back(function());
+      } else if (startsWith("gpu.module")) {
+        gpuModule(m);
       } else if (startsWith("shard.grid") || startsWith("mesh.mesh")) {
         // shard.grid @mesh4(shape = 4)   (test/Dialect/NDArray/Extensions/sharding_propagation.mlir:4)
         pos += startsWith("shard.grid") ? 10 : 9;
@@ -512,6 +514,52 @@ private:
     return affineMapAttr();
   }
 
+  // gpu.module @name [targets] { gpu.func @k(%a: memref<..>, ...) kernel [attributes {..}] { body } ... }
+  void gpuModule(Module &m) {
+    pos += 10;
+    const std::string modName = ident();
+    while (!eof() && peek() != '{') ++pos;  // target attributes
+    expect('{');
+    for (;;) {
+      skip();
+      if (eof()) fail("unterminated gpu.module");
+      if (peek() == '}') {
+        ++pos;
+        return;
+      }
+      if (!startsWith("gpu.func")) {
+        skipLineOrRegion();
+        continue;
+      }
+      pos += 8;
+      GpuKernel k;
+      k.module = modName;
+      k.line = lineNo();
+      k.name = ident();
+      expect('(');
+      skip();
+      if (peek() != ')') {
+        do {
+          k.args.push_back(ident());
+          expect(':');
+          k.argTypes.push_back(type());
+          skipTypeAttrs();
+        } while (accept(','));
+      }
+      expect(')');
+      acceptWord("kernel");
+      if (acceptWord("attributes")) {
+        skip();
+        skipBalanced('{', '}');
+      }
+      skip();
+      const size_t b = pos;
+      skipBalanced('{', '}');
+      k.body = s.substr(b, pos - b);
+      m.gpuKernels.push_back(std::move(k));
+    }
+  }
+
   // ---- functions -------------------------------------------------------------
   Function function() {
     Function f;
@@ -902,6 +950,101 @@ private:
       acceptWord("annotate_for_users");
       expect(':');
       op->resultTypes.push_back(type());
+    } else if (n == "gpu.alloc" || n == "memref.alloc" || n == "memref.alloca") {
+      // %m = gpu.alloc [host_shared] () : memref<..>    /    %m = memref.alloc() : memref<..>
+      if (acceptWord("host_shared")) op->predicate = "host_shared";
+      expect('(');
+      expect(')');
+      skip();
+      if (peek() == '{') skipBalanced('{', '}');
+      expect(':');
+      op->resultTypes.push_back(type());
+    } else if (n == "gpu.memcpy") {
+      operandList(op->operands);  // dst, src
+      expect(':');
+      do {
+        op->operandTypes.push_back(type());
+      } while (accept(','));
+    } else if (n == "gpu.wait") {
+      acceptWord("async");
+    } else if (n == "gpu.launch_func") {
+      // gpu.launch_func @mod::@kernel blocks in (..) threads in (..) args(%a : t, ...)
+      op->callee = ident();
+      expect(':');
+      expect(':');
+      op->callee += "::" + ident();
+      expectWord("blocks");
+      expectWord("in");
+      expect('(');
+      std::vector<std::string> geometry;
+      operandList(geometry);
+      expect(')');
+      expectWord("threads");
+      expectWord("in");
+      expect('(');
+      operandList(geometry);
+      expect(')');
+      if (acceptWord("dynamic_shared_memory_size")) operandList(geometry);
+      if (acceptWord("args")) {
+        expect('(');
+        skip();
+        if (peek() != ')') {
+          do {
+            op->operands.push_back(ident());
+            expect(':');
+            op->operandTypes.push_back(type());
+          } while (accept(','));
+        }
+        expect(')');
+      }
+    } else if (n == "memref.load") {
+      operandList(op->operands);
+      expect('[');
+      operandList(op->operands);
+      expect(']');
+      expect(':');
+      Type t = type();
+      op->operandTypes.push_back(t);
+      Type e;
+      e.kind = Type::Scalar;
+      e.elt = t.elt;
+      op->resultTypes.push_back(e);
+    } else if (n == "memref.store") {
+      operandList(op->operands);  // value, memref
+      expect('[');
+      operandList(op->operands);
+      expect(']');
+      expect(':');
+      op->operandTypes.push_back(type());
+    } else if (n == "memref.subview") {
+      // %v = memref.subview %m[o0, o1][s0, s1][t0, t1] : memref<..> to memref<.., strided<..>>
+      operandList(op->operands);
+      for (int part = 0; part < 3; ++part) {
+        expect('[');
+        std::vector<int64_t> vals;
+        skip();
+        if (peek() != ']') {
+          do {
+            skip();
+            if (peek() == '%') fail("memref.subview with dynamic offsets or sizes is outside the supported subset");
+            vals.push_back(static_cast<int64_t>(number().value));
+          } while (accept(','));
+        }
+        expect(']');
+        op->reassociation.push_back(vals);
+      }
+      expect(':');
+      op->operandTypes.push_back(type());
+      expectWord("to");
+      op->resultTypes.push_back(type());
+    } else if (n == "vector.print") {
+      if (acceptWord("str")) {
+        op->text = stringLit();
+      } else {
+        operandList(op->operands);
+        expect(':');
+        op->operandTypes.push_back(type());
+      }
     } else if (n == "memref.dealloc" || n == "gpu.dealloc") {
       operandList(op->operands);
       expect(':');

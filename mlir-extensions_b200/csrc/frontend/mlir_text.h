@@ -79,7 +79,8 @@ struct Op {
   std::vector<uint64_t> rawBits;       // hex literals keep their bits (0xFF800000)
   std::vector<bool> isRaw;
   // call / cmpf / misc
-  std::string callee;                  // "@printMemrefF32"
+  std::string callee;                  // "@printMemrefF32"; gpu.launch_func: "@module::@kernel"
+  std::string text;                    // vector.print str "..."
   std::string predicate;               // cmpf / cmpi predicate
   int64_t intAttr = 0;                 // linalg.index dimension
   std::vector<Type> bodyOperandTypes;  // per operand of a scalar op, when the syntax gives them
@@ -103,10 +104,22 @@ struct Grid {
   std::vector<int64_t> shape;
 };
 
+// A gpu.func inside a gpu.module: its signature and the text of its body.  The body is
+// device code of another dialect (XeGPU in the reference's integration tests); it is kept as
+// text for the kernel recogniser (gpu_kernels.h), not parsed into operations.
+struct GpuKernel {
+  std::string module, name;  // "@test_kernel", "@test_kernel"
+  std::vector<std::string> args;
+  std::vector<Type> argTypes;
+  std::string body;
+  int line = 0;
+};
+
 struct Module {
   std::string name;
   std::vector<Function> functions;
   std::vector<Grid> grids;
+  std::vector<GpuKernel> gpuKernels;
   const Function *find(const std::string &symbol) const;
 };
 

@@ -26,6 +26,8 @@
 #include "../../../include/imex_b200_blob.h"
 #include "../../../include/imex_cuda_runtime.h"
 #include "../../../include/imex_runner_utils.h"
+#include "gpu_kernels.h"
+#include "host_loops.h"
 #include "loopnest.h"
 #include "mlir_text.h"
 #include "recognise.h"
@@ -138,6 +140,7 @@ struct Buffer {  // a device allocation, freed with the last reference
   void *stream = nullptr;
   void *ptr = nullptr;
   size_t bytes = 0;
+  bool hostVisible = false;  // memref.alloc / gpu.alloc host_shared: managed memory the host code reads and writes
   ~Buffer() {
     if (ptr && !g_plan) {
       trace("gpuMemFree");
@@ -231,7 +234,7 @@ private:
     return made;
   }
 
-  Value makeTensorExact(void *stream, const Type &t) {
+  Value makeTensorExact(void *stream, const Type &t, bool hostVisible = false) {
     if (t.unranked) die("cannot allocate an unranked tensor");
     for (auto d : t.shape)
       if (d < 0) die("dynamic shapes are not supported: kernel arguments carry no shape");
@@ -241,8 +244,10 @@ private:
     v.buf = std::make_shared<Buffer>();
     v.buf->stream = stream;
     v.buf->bytes = static_cast<size_t>(t.count()) * eltBytes(t.elt);
-    trace("gpuMemAlloc(" + std::to_string(v.buf->bytes) + " bytes, align 64, device)  // " + t.str());
-    if (!g_plan) v.buf->ptr = gpuMemAlloc(stream, v.buf->bytes, 64, false);
+    v.buf->hostVisible = hostVisible;
+    trace("gpuMemAlloc(" + std::to_string(v.buf->bytes) + " bytes, align 64, " + (hostVisible ? "host_shared" : "device") +
+          ")  // " + t.str());
+    if (!g_plan) v.buf->ptr = gpuMemAlloc(stream, v.buf->bytes, 64, hostVisible);
     return v;
   }
 
@@ -294,7 +299,7 @@ private:
 
   // One kernel: module with one descriptor, loaded, looked up, launched, waited for.
   void launch(void *stream, ImexKernelDesc d, const std::vector<void *> &ptrs, const std::string &what,
-              const std::string &payload = std::string()) {
+              const std::string &payload = std::string(), bool wait = true) {
     std::snprintf(d.name, sizeof d.name, "imex_b200_kernel_%d", kernelCounter++);
     auto blob = std::make_unique<std::vector<char>>(sizeof(ImexBlobHeader) + sizeof(ImexKernelDesc) + payload.size());
     ImexBlobHeader h{IMEX_BLOB_MAGIC, IMEX_BLOB_VERSION, 1};
@@ -312,7 +317,7 @@ private:
     trace(std::string("gpuModuleLoad(blob, ") + std::to_string(blob->size()) + " bytes)");
     trace(std::string("gpuKernelGet(\"") + d.name + "\")");
     trace("gpuLaunchKernel(" + std::to_string(ptrs.size()) + " pointer params)");
-    trace("gpuWait");
+    if (wait) trace("gpuWait");
     if (!g_plan) {
       void *m = gpuModuleLoad(stream, blob->data(), blob->size());
       void *k = gpuKernelGet(stream, m, d.name);
@@ -322,7 +327,7 @@ private:
       params.push_back(ImexParamDesc{nullptr, 0});
       ImexEventDesc none[1] = {{nullptr}};
       gpuLaunchKernel(stream, k, 1, 1, 1, 1, 1, 1, 0, params.data(), none);
-      gpuWait(stream);
+      if (wait) gpuWait(stream);  // a linalg op's launch is synchronous; gpu.launch_func has its own gpu.wait
     }
     blobs.push_back(std::move(blob));
   }
@@ -854,6 +859,49 @@ private:
         fr.vals.erase(op.operands[0]);
       } else if (n == "call" || n == "func.call" || n == "llvm.call") {
         doCall(op, fr, stream);
+      } else if (n == "gpu.alloc" || n == "memref.alloc" || n == "memref.alloca") {
+        // host code's own arrays are memory both sides can touch (managed), as gpu.alloc
+        // host_shared is (lib/Transforms/InsertGPUAllocs.cpp:376-412); gpu.alloc () is device memory
+        const bool host = n != "gpu.alloc" || op.predicate == "host_shared";
+        fr.vals[op.results[0]] = makeTensorExact(stream, op.resultTypes[0], host);
+      } else if (n == "gpu.memcpy") {
+        Value &dst = get(fr, op.operands[0], op), &src = get(fr, op.operands[1], op);
+        if (dst.kind != Value::Tensor || src.kind != Value::Tensor || dst.buf->bytes != src.buf->bytes)
+          die("line " + std::to_string(op.line) + ": gpu.memcpy between arrays of different sizes");
+        trace("gpuMemCopy(" + std::string(src.buf->hostVisible ? "host" : "device") + " -> " +
+              (dst.buf->hostVisible ? "host" : "device") + ", " + std::to_string(dst.buf->bytes) + " bytes)");
+        if (!g_plan && dst.buf->bytes) gpuMemCopy(stream, dst.buf->ptr, src.buf->ptr, dst.buf->bytes);
+      } else if (n == "gpu.wait") {
+        trace("gpuWait");
+        if (!g_plan) gpuWait(stream);
+      } else if (n == "gpu.launch_func") {
+        launchFunc(op, fr, stream);
+      } else if (n == "memref.load" || n == "memref.store") {
+        hostElement(op, fr);
+      } else if (n == "memref.subview") {
+        subview(op, fr, stream);
+      } else if (n == "vector.print") {
+        if (g_plan) continue;
+        if (op.operands.empty()) {
+          std::string out;  // the string attribute with its escapes resolved
+          for (size_t i = 0; i < op.text.size(); ++i) {
+            if (op.text[i] == '\\' && i + 1 < op.text.size()) {
+              const char e = op.text[++i];
+              out += e == 'n' ? '\n' : e == 't' ? '\t' : e;
+            } else {
+              out += op.text[i];
+            }
+          }
+          std::cout << out;
+        } else {
+          const Value &v = get(fr, op.operands[0], op);
+          const std::string &e = op.operandTypes[0].elt;
+          if (e == "f32" || e == "f64") std::cout << v.scalar << "\n";
+          else std::cout << static_cast<long long>(v.scalar) << "\n";
+        }
+        std::cout.flush();
+      } else if (n == "scf.for" && op.iterArgs.empty() && hostLoop(op, fr)) {
+        // ran as a compiled host loop nest (host_loops.h)
       } else if (n == "scf.for") {
         const int64_t lb = static_cast<int64_t>(get(fr, op.operands[0], op).scalar);
         const int64_t ub = static_cast<int64_t>(get(fr, op.operands[1], op).scalar);
@@ -862,6 +910,7 @@ private:
         std::vector<Value> carried;
         for (auto &i : op.iterInits) carried.push_back(get(fr, i, op));
         for (int64_t i = lb; i < ub; i += st) {
+          if (g_plan && i != lb) break;  // a plan lists each launch of a loop body once
           Value iv;
           iv.kind = Value::Scalar;
           iv.type.kind = Type::Scalar;
@@ -929,6 +978,144 @@ private:
     fr.vals[op.results[0]] = rowBlock(stream, x, r0, rows);
   }
 
+  // ---- GPU-dialect host code (gpu.launch_func of a recognised kernel, host memrefs) ---------
+  // gpu.launch_func @module::@kernel ... args(...): the gpu.func is XeGPU-dialect device code;
+  // what it computes is recognised from its data flow (gpu_kernels.h) and served by the GEMM
+  // kernels of this runtime through a descriptor, with the launch's arguments put in the
+  // descriptor's pointer order.
+  void launchFunc(const Op &op, Frame &fr, void *stream) {
+    const std::string where = "line " + std::to_string(op.line) + ": ";
+    const GpuKernel *k = nullptr;
+    for (auto &g : mod.gpuKernels)
+      if (g.module + "::" + g.name == op.callee) k = &g;
+    if (!k) die(where + "gpu.launch_func of unknown kernel " + op.callee);
+    if (k->args.size() != op.operands.size()) die(where + "argument count differs from the kernel's signature");
+    GpuGemm g;
+    std::string why;
+    if (!recogniseGpuGemm(*k, g, why))
+      die(where + "the gpu.func " + op.callee + " is not a kernel this runtime can stand in for (" + why +
+          "); its device code is of another dialect and cannot be compiled for sm_100a");
+    auto arg = [&](int i) -> Value & {
+      Value &v = get(fr, op.operands[i], op);
+      if (v.kind != Value::Tensor) die(where + "kernel argument " + op.operands[i] + " is not a memref");
+      return v;
+    };
+    Value &A = arg(g.a), &Bv = arg(g.b), &C = arg(g.c);
+    ImexKernelDesc d = desc(IMEX_OP_GEMM, dtypeCode(A.type.elt), dtypeCode(C.type.elt));
+    d.dims[0] = g.M;
+    d.dims[1] = g.N;
+    d.dims[2] = g.K;
+    if (g.transA) d.flags |= IMEX_FLAG_TRANS_A;
+    if (g.transB) d.flags |= IMEX_FLAG_TRANS_B;
+    if (g.readsC) d.flags |= IMEX_FLAG_ACCUMULATE;
+    std::vector<void *> ptrs = {A.buf->ptr, Bv.buf->ptr, C.buf->ptr};
+    if (g.bias >= 0) {
+      d.flags |= IMEX_FLAG_BIAS;
+      ptrs.push_back(arg(g.bias).buf->ptr);
+    }
+    launch(stream, d, ptrs,
+           std::string("gemm ") + A.type.elt + "->" + C.type.elt + (g.transA ? " A^T" : "") + (g.transB ? " B^T" : "") +
+               (g.bias >= 0 ? " +bias" : "") + (g.readsC ? " +C" : "") + "  // gpu.func " + op.callee,
+           std::string(), /*wait=*/false);
+  }
+
+  // memref.load / memref.store executed one at a time (outside compiled loop nests)
+  void hostElement(const Op &op, Frame &fr) {
+    const bool ld = op.name == "memref.load";
+    Value &m = get(fr, op.operands[ld ? 0 : 1], op);
+    if (m.kind != Value::Tensor || !m.buf->hostVisible)
+      die("line " + std::to_string(op.line) + ": " + op.name + " needs a host-visible memref (memref.alloc or gpu.alloc host_shared)");
+    if (g_plan) {
+      if (ld) {
+        Value v;
+        v.kind = Value::Scalar;
+        v.type = op.resultTypes[0];
+        fr.vals[op.results[0]] = v;
+      }
+      return;
+    }
+    const size_t first = ld ? 1 : 2;
+    int64_t lin = 0;
+    for (size_t i = first; i < op.operands.size(); ++i)
+      lin = lin * m.type.shape[i - first] + static_cast<int64_t>(get(fr, op.operands[i], op).scalar);
+    char *p = static_cast<char *>(m.buf->ptr);
+    const std::string &e = m.type.elt;
+    if (e != "f32" && e != "i32" && e != "f64" && e != "i64" && e != "index")
+      die("line " + std::to_string(op.line) + ": single " + op.name + " of " + e + " (use it inside an scf.for nest)");
+    if (ld) {
+      Value v;
+      v.kind = Value::Scalar;
+      v.type = op.resultTypes[0];
+      if (e == "f32") { float f; std::memcpy(&f, p + 4 * lin, 4); v.scalar = f; }
+      else if (e == "i32") { int32_t x; std::memcpy(&x, p + 4 * lin, 4); v.scalar = x; }
+      else if (e == "f64") { std::memcpy(&v.scalar, p + 8 * lin, 8); }
+      else { int64_t x; std::memcpy(&x, p + 8 * lin, 8); v.scalar = static_cast<double>(x); }
+      fr.constants[op.results[0]] = v.scalar;
+      fr.vals[op.results[0]] = v;
+    } else {
+      const double val = get(fr, op.operands[0], op).scalar;
+      if (e == "f32") { float f = static_cast<float>(val); std::memcpy(p + 4 * lin, &f, 4); }
+      else if (e == "i32") { int32_t x = static_cast<int32_t>(val); std::memcpy(p + 4 * lin, &x, 4); }
+      else if (e == "f64") { std::memcpy(p + 8 * lin, &val, 8); }
+      else { int64_t x = static_cast<int64_t>(val); std::memcpy(p + 8 * lin, &x, 8); }
+    }
+  }
+
+  // memref.subview of whole leading rows ([r0, 0, ..][n, full, ..][1, 1, ..]): a copy of the
+  // contiguous block (the tests only print such views)
+  void subview(const Op &op, Frame &fr, void *stream) {
+    const std::string where = "line " + std::to_string(op.line) + ": ";
+    Value &m = get(fr, op.operands[0], op);
+    const auto &off = op.reassociation[0], &size = op.reassociation[1], &stride = op.reassociation[2];
+    const size_t rank = m.type.shape.size();
+    if (off.size() != rank || size.size() != rank || stride.size() != rank) die(where + "memref.subview rank mismatch");
+    for (size_t d = 0; d < rank; ++d)
+      if (stride[d] != 1 || (d > 0 && (off[d] != 0 || size[d] != m.type.shape[d])))
+        die(where + "only subviews of whole leading rows are supported");
+    Type t = m.type;
+    t.shape[0] = size[0];
+    Value v = makeTensorExact(stream, t, m.buf->hostVisible);
+    const size_t rowBytes = m.type.shape[0] ? m.buf->bytes / static_cast<size_t>(m.type.shape[0]) : 0;
+    trace("gpuMemCopy(" + std::to_string(v.buf->bytes) + " bytes)  // subview rows [" + std::to_string(off[0]) + ", " +
+          std::to_string(off[0] + size[0]) + ")");
+    if (!g_plan && v.buf->bytes)
+      gpuMemCopy(stream, v.buf->ptr, static_cast<char *>(m.buf->ptr) + static_cast<size_t>(off[0]) * rowBytes, v.buf->bytes);
+    fr.vals[op.results[0]] = v;
+  }
+
+  // An scf.for nest of scalar code over host-visible memrefs, compiled and run (host_loops.h);
+  // false when it holds anything else (kernel launches, calls, tensors): the interpreter's.
+  bool hostLoop(const Op &op, Frame &fr) {
+    HostLoopProgram prog;
+    std::string why;
+    bool touchesArrays = false;
+    auto lookup = [&](const std::string &name, double &scalar, HostArray &arr, bool &isArray) {
+      auto it = fr.vals.find(name);
+      if (it == fr.vals.end()) return false;
+      const Value &v = it->second;
+      if (v.kind == Value::Scalar) {
+        scalar = v.scalar;
+        isArray = false;
+        return true;
+      }
+      if (v.kind != Value::Tensor || v.lazy || !v.buf || !v.buf->hostVisible) return false;
+      arr.data = v.buf->ptr;
+      arr.elt = v.type.elt;
+      arr.shape = v.type.shape;
+      isArray = true;
+      touchesArrays = true;
+      return true;
+    };
+    if (!prog.compile(op, lookup, why)) return false;
+    if (!touchesArrays) return false;  // pure scalar loops stay with the interpreter (they bind results)
+    trace("host loop nest at line " + std::to_string(op.line) + " (compiled)");
+    if (!g_plan) {
+      if (curStream) gpuWait(curStream);  // the device is done with what the host is about to touch
+      prog.run();
+    }
+    return true;
+  }
+
   void scalarOp(const Op &op, Frame &fr) {
     auto a = [&](size_t i) { return get(fr, op.operands[i], op).scalar; };
     Value v;
@@ -958,6 +1145,76 @@ private:
     if (c == "@printF64") { if (!g_plan) printF64(get(fr, op.operands[0], op).scalar); return; }
     if (c == "@printF32") { if (!g_plan) printF32(static_cast<float>(get(fr, op.operands[0], op).scalar)); return; }
     if (c == "@printNewline") { if (!g_plan) printNewline(); return; }
+    static const std::set<std::string> kHostUtils = {
+        "@fillResource1DF32", "@fillResource1DF16", "@fillResource1DBF16", "@fillResource1DRandomF32",
+        "@fillResource1DRandomF16", "@fillResource1DRandomBF16", "@gemmF16F16F32", "@gemmF16F16F16",
+        "@gemmBF16BF16F32"};
+    if (kHostUtils.count(c)) {
+      // runner-utils functions that write a memref (lib/ExecutionEngine/ImexRunnerUtils.cpp:38-50,
+      // 217-338): they run on the host, on the array itself when the host can see it, else on a
+      // copy that is written back
+      if (g_plan) { trace("host call " + c); return; }
+      struct HostView {
+        std::vector<char> copy;
+        std::vector<int64_t> words;
+        ImexUnrankedMemRef u;
+        Value *v = nullptr;
+      };
+      std::vector<std::unique_ptr<HostView>> views;
+      std::vector<double> scalars;
+      gpuWait(stream);
+      for (size_t i = 0; i < op.operands.size(); ++i) {
+        Value &v = get(fr, op.operands[i], op);
+        if (v.kind == Value::Scalar) { scalars.push_back(v.scalar); continue; }
+        auto h = std::make_unique<HostView>();
+        h->v = &v;
+        void *base = v.buf->ptr;
+        if (!v.buf->hostVisible) {
+          h->copy.resize(v.buf->bytes ? v.buf->bytes : 1);
+          if (v.buf->bytes) gpuMemCopy(stream, h->copy.data(), v.buf->ptr, v.buf->bytes);
+          base = h->copy.data();
+        }
+        const int64_t rank = static_cast<int64_t>(v.type.shape.size());
+        h->words.assign(3 + 2 * rank, 0);
+        std::memcpy(&h->words[0], &base, 8);
+        std::memcpy(&h->words[1], &base, 8);
+        int64_t stride = 1;
+        for (int64_t d = rank - 1; d >= 0; --d) {
+          h->words[3 + d] = v.type.shape[d];
+          h->words[3 + rank + d] = stride;
+          stride *= v.type.shape[d];
+        }
+        h->u = ImexUnrankedMemRef{rank, h->words.data()};
+        views.push_back(std::move(h));
+      }
+      auto elt = [&](size_t i) { return views.at(i)->v->type.elt; };
+      const std::string where = "line " + std::to_string(op.line) + ": ";
+      if (c.rfind("@fillResource1DRandom", 0) == 0) {
+        if (views.size() != 1 || scalars.size() != 3) die(where + c + " takes a memref, two bounds and a flag");
+        const float lo = static_cast<float>(scalars[0]), hi = static_cast<float>(scalars[1]);
+        const bool ints = scalars[2] != 0;
+        if (elt(0) == "f32") _mlir_ciface_fillResource1DRandomF32(&views[0]->u, lo, hi, ints);
+        else if (elt(0) == "f16") _mlir_ciface_fillResource1DRandomF16(&views[0]->u, lo, hi, ints);
+        else if (elt(0) == "bf16") _mlir_ciface_fillResource1DRandomBF16(&views[0]->u, lo, hi, ints);
+        else die(where + c + " of " + elt(0));
+      } else if (c.rfind("@fillResource1D", 0) == 0) {
+        if (views.size() != 1 || scalars.size() != 1) die(where + c + " takes a memref and a value");
+        const float val = static_cast<float>(scalars[0]);
+        if (elt(0) == "f32") _mlir_ciface_fillResource1DF32(&views[0]->u, val);
+        else if (elt(0) == "f16") _mlir_ciface_fillResource1DF16(&views[0]->u, val);
+        else if (elt(0) == "bf16") _mlir_ciface_fillResource1DBF16(&views[0]->u, val);
+        else die(where + c + " of " + elt(0));
+      } else {
+        if (views.size() != 3) die(where + c + " takes three memrefs");
+        if (c == "@gemmF16F16F32") _mlir_ciface_gemmF16F16F32(&views[0]->u, &views[1]->u, &views[2]->u);
+        else if (c == "@gemmF16F16F16") _mlir_ciface_gemmF16F16F16(&views[0]->u, &views[1]->u, &views[2]->u);
+        else if (c == "@gemmBF16BF16F32") _mlir_ciface_gemmBF16BF16F32(&views[0]->u, &views[1]->u, &views[2]->u);
+        else die(where + "unknown host GEMM " + c);
+      }
+      for (auto &h : views)  // the functions write their first (fill) or last (gemm) memref
+        if (!h->copy.empty() && h->v->buf->bytes) gpuMemCopy(stream, h->v->buf->ptr, h->copy.data(), h->v->buf->bytes);
+      return;
+    }
     if (c.rfind("@printAllclose", 0) == 0 || c.rfind("@printMaxError", 0) == 0) {
       // the reference's result checks (lib/ExecutionEngine/ImexRunnerUtils.cpp:185-255): both
       // tensors come back to the host and go to the runner-utils function of that name

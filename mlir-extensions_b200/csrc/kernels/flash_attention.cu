@@ -171,7 +171,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_v) : "memory");
       mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_2d(q_smem, &tmap_q, 0, head_row0 + q0, q_full);
+      tma_load_3d(q_smem, &tmap_q, 0, q0, head, q_full);
       int filled = 0;
       for (int j = 0; j < num_blocks; ++j) {
         const int s = j % KV_STAGES;
@@ -180,8 +180,8 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
           break;
         }
         mbar_expect_tx(kv_full(s), 2 * TILE_BYTES);
-        tma_load_2d(k_smem(s), &tmap_k, 0, head_row0 + j * BKV, kv_full(s));
-        tma_load_2d(v_smem(s), &tmap_v, 0, head_row0 + j * BKV, kv_full(s));
+        tma_load_3d(k_smem(s), &tmap_k, 0, j * BKV, head, kv_full(s));
+        tma_load_3d(v_smem(s), &tmap_v, 0, j * BKV, head, kv_full(s));
         filled = j + 1;
       }
       // every tile this thread asked for has been consumed before the CTA may go
@@ -442,10 +442,12 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
     attr_err = e2 != cudaSuccess ? e2 : e4 != cudaSuccess ? e4 : e5;
   });
   if (attr_err != cudaSuccess) return attr_err;
-  const int64_t rows = heads * n_ctx;
+  // heads are a dimension of the tensor maps: a tile that runs past the last key (or query) of
+  // its head is filled with zeros, not with the next head's first rows (whose values, were they
+  // Inf or NaN, would reach this head's output through 0 x V)
   CUtensorMap tq, tk, tv;
-  if (!make_map(&tq, q, dtype, DH, rows, BQ) || !make_map(&tk, k, dtype, DH, rows, BKV) ||
-      !make_map(&tv, v, dtype, DH, rows, BKV))
+  if (!make_map_batched(&tq, q, dtype, n_ctx, heads, BQ) || !make_map_batched(&tk, k, dtype, n_ctx, heads, BKV) ||
+      !make_map_batched(&tv, v, dtype, n_ctx, heads, BKV))
     return cudaErrorNotSupported;
   AttnParams p;
   p.O = o;

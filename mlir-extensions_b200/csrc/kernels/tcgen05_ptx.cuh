@@ -71,6 +71,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// The same for a 3-D tensor (x innermost); coordinates beyond an extent read the fill value.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
 // Ask L2 to fetch a tile ahead of the load that will need it (no smem, no barrier).
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x),

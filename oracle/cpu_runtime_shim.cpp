@@ -135,6 +135,48 @@ RunFn compile(const std::string &source) {
   return fn;
 }
 
+// IMEX_OP_GEMM on the host, the way the reference's CPU pipeline computes a matmul: per output
+// element, k ascending, multiply then add in f32 with separate roundings (16-bit inputs
+// extended first), then + bias, then one rounding to a 16-bit result type.  Reached by the
+// gpu.func kernels the front end recognises as GEMMs (no epilogue there).
+float elt_to_f32(const void *p, int64_t i, uint32_t dt) {
+  if (dt == IMEX_F32) return static_cast<const float *>(p)[i];
+  const uint16_t h = static_cast<const uint16_t *>(p)[i];
+  if (dt == IMEX_BF16) { uint32_t u = static_cast<uint32_t>(h) << 16; float f; memcpy(&f, &u, 4); return f; }
+  _Float16 x; memcpy(&x, &h, 2); return static_cast<float>(x);
+}
+void host_gemm(const ImexKernelDesc &d, const std::vector<void *> &ptrs) {
+  const bool bias = d.flags & IMEX_FLAG_BIAS, acc = d.flags & IMEX_FLAG_ACCUMULATE;
+  const bool ta = d.flags & IMEX_FLAG_TRANS_A, tb = d.flags & IMEX_FLAG_TRANS_B;
+  if (ptrs.size() < (bias ? 4u : 3u)) fail("gpuLaunchKernel: gemm needs A, B, C (and bias)");
+  if (d.epilogue != IMEX_EPI_NONE || d.dims[3] || d.dims[4] || d.dims[5]) fail("host gemm: epilogues and pitches are not served here");
+  const int64_t M = d.dims[0], N = d.dims[1], K = d.dims[2];
+  const void *A = ptrs[0], *B = ptrs[1];
+  const float *bv = bias ? static_cast<const float *>(ptrs[3]) : nullptr;
+  std::vector<float> row(static_cast<size_t>(N));
+  for (int64_t i = 0; i < M; ++i) {
+    for (int64_t j = 0; j < N; ++j) row[j] = acc ? elt_to_f32(ptrs[2], i * N + j, d.out_dtype) : 0.0f;
+    for (int64_t k = 0; k < K; ++k) {
+      const float a = elt_to_f32(A, ta ? k * M + i : i * K + k, d.in_dtype);
+      for (int64_t j = 0; j < N; ++j) {
+        const float p = a * elt_to_f32(B, tb ? j * K + k : k * N + j, d.in_dtype);
+        row[j] = row[j] + p;
+      }
+    }
+    for (int64_t j = 0; j < N; ++j) {
+      float v = row[j];
+      if (bv) v = v + bv[j];
+      if (d.out_dtype == IMEX_F32) static_cast<float *>(ptrs[2])[i * N + j] = v;
+      else if (d.out_dtype == IMEX_F16) { _Float16 x = static_cast<_Float16>(v); memcpy(static_cast<uint16_t *>(ptrs[2]) + i * N + j, &x, 2); }
+      else {
+        uint32_t u; memcpy(&u, &v, 4);
+        u += 0x7fffu + ((u >> 16) & 1u);
+        static_cast<uint16_t *>(ptrs[2])[i * N + j] = static_cast<uint16_t>(u >> 16);
+      }
+    }
+  }
+}
+
 } // namespace
 
 extern "C" {
@@ -163,6 +205,7 @@ void *gpuModuleLoad(void *, const void *data, size_t size) {
   memcpy(m->kernels.data(), static_cast<const char *>(data) + sizeof h, h.num_kernels * sizeof(ImexKernelDesc));
   for (size_t i = 0; i < m->kernels.size(); ++i) {
     const ImexKernelDesc &k = m->kernels[i];
+    if (k.op == IMEX_OP_GEMM) continue;  // served by host_gemm below (GPU-dialect kernels recognised as GEMMs)
     if (k.op != IMEX_OP_LOOPNEST)
       fail("the CPU checker runs loop nests only (start the runner with --all-loopnests); got op " + std::to_string(k.op));
     if (k.dims[1] < 0 || k.dims[2] <= 0 || static_cast<size_t>(k.dims[1] + k.dims[2]) > size)
@@ -195,6 +238,10 @@ void *gpuLaunchKernel(void *, void *kernel, size_t, size_t, size_t, size_t, size
     void *v;
     memcpy(&v, p[i].data, sizeof v);
     ptrs.push_back(v);
+  }
+  if (k->desc.op == IMEX_OP_GEMM) {
+    host_gemm(k->desc, ptrs);
+    return nullptr;
   }
   if (static_cast<int64_t>(ptrs.size()) < k->desc.dims[3]) fail("gpuLaunchKernel: too few pointer arguments");
   compile(k->source)(ptrs.data(), k->desc.dims[0]);

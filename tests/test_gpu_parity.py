@@ -869,6 +869,24 @@ def test_attention_forward_matches_the_reference_cpu_check(pkg, sess, kind, head
     assert np.all(np.abs(got - ref) <= atol + rtol * np.abs(ref))
 
 
+@pytest.mark.parametrize("n_ctx", [200, 72])
+def test_attention_heads_do_not_see_each_other_in_a_ragged_last_tile(pkg, sess, n_ctx):
+    """n_ctx is not a multiple of the 128-key tile: the last K/V tile of a head must be padded
+    with zeros, not with the first rows of the next head.  With NaN and Inf in head 1's first K
+    and V rows, head 0 must come out finite and equal to head 0 computed alone."""
+    B = pkg.blob
+    q, k, v = _attention_inputs(2, n_ctx, "f16", 43)
+    k2, v2 = k.copy(), v.copy()
+    v2[n_ctx:n_ctx + 64] = 0x7E00          # NaN in the rows behind head 0's last key
+    k2[n_ctx:n_ctx + 64] = 0x7C00          # +Inf
+    dq, dk, dv, do = sess.upload(q), sess.upload(k2), sess.upload(v2), sess.alloc(q.nbytes)
+    sess.run(B.attention_fwd("attn", 2, n_ctx, 64, B.F16, 0.5), [dq, dk, dv, do])
+    got = oracle.f16_bits_to_f32(sess.download(do, q.shape, np.uint16))[:n_ctx]
+    ref = oracle.f16_bits_to_f32(oracle.attention_fwd(q[:n_ctx], k[:n_ctx], v[:n_ctx], 1, 0.5, False))
+    assert np.isfinite(got).all()
+    assert oracle.rel_frobenius(got, ref) <= 1e-3
+
+
 def test_attention_forward_at_the_reference_size(pkg, sess):
     """Z = 2, H = 2, N_CTX = 4096, D_HEAD = 64, sm_scale 0.5
     (flash_attention_fwd.mlir:452-456): sampled heads' rows against the oracle, every row
