@@ -14,9 +14,14 @@
  * Parity pins: tests/golden/reference_vectors.json (values transcribed from
  * the CHECK lines of the reference's own tests) and oracle/_ref (the
  * reference's in-tree CPU GEMM compiled from its own source file).
- * PARITY UNPINNED (no golden values exist in the reference): silu, the
- * one-generic-at-a-time functions in 16-bit element types (oracle_unary /
- * oracle_binary / oracle_reduce_leading_as) and oracle_attention_fwd_x16.
+ * silu and the one-generic-at-a-time functions in 16-bit element types
+ * (oracle_unary / oracle_binary / oracle_reduce_leading_as) are pinned through
+ * the reference's generated tests (test/Gen/PlaidML templates and the
+ * benchmark templates with their printed CHECK values): tests/test_oracle_pins.py
+ * runs the same programs through these functions and through the loop-nest
+ * checker that reproduces those CHECK lines.
+ * PARITY UNPINNED (the reference prints no values for it):
+ * oracle_attention_fwd_x16.
  *
  * Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may
  * load this library.  The product never does.
