@@ -203,13 +203,20 @@ def graph_back_to_back(torch, stream, sess, kernel, ptr_sets, rounds=9):
     replayed `rounds` times with an event pair around each replay.  A Python-side launch
     costs ~10 us of host time, more than these kernels run, so without the graph a loop of
     launches measures the host.  Returns (median ms per launch, min ms per launch)."""
-    for ptrs in ptr_sets[:2]:
-        sess.launch(kernel, ptrs, wait=False)      # everything lazy happens before the capture
+    return graph_replay_ms(torch, stream, sess, [lambda ptrs=ptrs: sess.launch(kernel, ptrs, wait=False)
+                                                 for ptrs in ptr_sets], rounds)
+
+
+def graph_replay_ms(torch, stream, sess, launches, rounds=9):
+    """The same timing for any list of enqueue functions (one graph node each)."""
+    ptr_sets = launches
+    for fn in launches[:2]:
+        fn()                                       # everything lazy happens before the capture
     sess.wait()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=stream):
-        for ptrs in ptr_sets:
-            sess.launch(kernel, ptrs, wait=False)
+        for fn in launches:
+            fn()
     per = []
     for i in range(rounds + 2):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -770,7 +777,7 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
                 ms.append(a.elapsed_time(b))
         return float(np.median(ms))
 
-    def hbm_entry(name, key, nbytes, kernel, ptrs, note, ptr_sets=None):
+    def hbm_entry(name, key, nbytes, kernel, ptrs, note, ptr_sets=None, tensor_pairs=None):
         med, mn = timed(kernel, ptrs, cold=True)
         wmed, _ = timed(kernel, ptrs, cold=False)
         ach = nbytes / (med * 1e-3) / 1e9
@@ -795,6 +802,15 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
             ach2 = nbytes / (b2b * 1e-3) / 1e9
             out[name].update(ms_back_to_back=b2b, ms_back_to_back_min=b2b_min, gbs_flushed_single_launch=ach,
                              roofline_ms=b2b)
+            if tensor_pairs:
+                # the yardstick at this size: plain device copies of the same buffers (the same
+                # bytes read and written), one graph node each, timed the same way
+                try:
+                    cp, _ = graph_replay_ms(torch, stream, sess,
+                                            [lambda a=a, b=b: b.copy_(a) for a, b in tensor_pairs])
+                    out[name].update(ms_copy_back_to_back=cp, speed_vs_copy_back_to_back=cp / b2b)
+                except Exception as e:  # noqa: BLE001
+                    out[name]["copy_graph_timing_error"] = repr(e)[:200]
             out[name]["roofline"].update(achieved=ach2, frac=ach2 / hbm, frac_of_nominal_8000=ach2 / 8000.0,
                                          timing="%d launches on %d distinct buffer pairs (%d MiB in all, larger "
                                                 "than L2) replayed as one CUDA graph, one event pair around the "
@@ -810,7 +826,7 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
     hbm_entry("softmax_4096x1024", "softmax", 2 * X.numel() * 4,
               sess.kernel(B.softmax("softmax", 4096, 1024)), [X.data_ptr(), Y.data_ptr()],
               "config 2; 32 MiB moved, fits L2: cold = flushed before each launch",
-              ptr_sets=[[a.data_ptr(), b.data_ptr()] for a, b in pairs])
+              ptr_sets=[[a.data_ptr(), b.data_ptr()] for a, b in pairs], tensor_pairs=pairs)
     del pairs
     # config 4a: row reduce 32768 x 8192
     R = torch.empty((32768, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)

@@ -32,6 +32,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <string>
 
 namespace imex {
 namespace {
@@ -47,8 +48,9 @@ constexpr int TILE_BYTES = 128 * DH * 2;        // 16 KB: any of the Q / K / V t
 constexpr int P_BYTES = BQ * BKV * 2;           // 32 KB: two 128 x 64-key boxes; two such buffers
 // threads: producer warp, MMA warp, 4 * SPLIT softmax warps (SPLIT threads per query row)
 constexpr int num_threads(int split) { return 64 + 128 * split; }
-constexpr int TMEM_COLS = 512;                  // S0 [0,128) S1 [128,256) PV0 [256,320) PV1 [320,384)
+constexpr int TMEM_COLS = 512;  // S0 [0,128) S1 [128,256) PV0 [256,320) PV1 [320,384) P0 [384,448) P1 [448,512)
 constexpr int PV_COL = 256;
+constexpr int P_COL = 384;      // P as the A operand of P.V: 128 keys = 64 columns of two 16-bit values
 constexpr int XCH_BYTES = 2 * 4 * BQ * 4;           // partial row maxima / sums of the threads of a row
 constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 1024 + 256 + XCH_BYTES;
 
@@ -76,6 +78,49 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16) {
   else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));
   return w;
 }
+// ---- packed arithmetic of sm_100: two f32 per 64-bit register, two f16 per 32-bit register
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t w;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(w) : "f"(lo), "f"(hi));
+  return w;
+}
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t w;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(w) : "r"(lo), "r"(hi));
+  return w;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t w, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(w));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x of two f16 values at once: one trip through the special-function unit for two keys, and
+// the result is already the packed 16-bit pair the P tile holds
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
+  uint32_t y;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+  return y;
+}
+__device__ __forceinline__ float sum_halves_f16x2(uint32_t w) {
+  float lo, hi;
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(w));
+  return lo + hi;
+}
 __device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
@@ -87,6 +132,27 @@ __device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
 
 __device__ __forceinline__ void st_shared_v4_u32(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st_16cols(uint32_t taddr, const uint32_t *r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D (TMEM) (+)= A (TMEM: row = lane, two 16-bit values of consecutive k per column) . B (shared memory)
+__device__ __forceinline__ void tcgen05_mma_f16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]);
@@ -103,7 +169,12 @@ template <> __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uin
       : "memory");
 }
 
-template <int SPLIT, bool STATS>
+// FAST16 (f16 only): the exponentials run as ex2.approx.f16x2 on the 16-bit rounded exponent
+// (x = s' - m <= 0, so its absolute rounding error is largest where 2^x is smallest) and the
+// row sums are added up from the packed P values themselves.
+// PTMEM: P goes from the softmax threads' registers into TMEM (tcgen05.st) and the second MMA
+// takes it from there; otherwise through the swizzled shared-memory tile.
+template <int SPLIT, bool STATS, bool FAST16, bool PTMEM>
 __global__ void __launch_bounds__(num_threads(SPLIT), 1)
 flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -122,12 +193,12 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   auto p_full = [&](int b) { return bars + 8u * (5 + 2 * KV_STAGES + b); };
   auto pv_full = [&](int b) { return bars + 8u * (7 + 2 * KV_STAGES + b); };
   auto pv_empty = [&](int b) { return bars + 8u * (9 + 2 * KV_STAGES + b); };
-  const uint32_t xch_bar = bars + 8u * (11 + 2 * KV_STAGES);
-  const uint32_t tmem_slot = bars + 8u * (12 + 2 * KV_STAGES);
+  auto xch_bar_of = [&](int g) { return bars + 8u * (11 + 2 * KV_STAGES + g); };   // one per lane group
+  const uint32_t tmem_slot = bars + 8u * (15 + 2 * KV_STAGES);
   const uint32_t xch = bars + 256;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(
-      smem_aligned + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 8 * (12 + 2 * KV_STAGES));
+      smem_aligned + TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 2 * P_BYTES + 8 * (15 + 2 * KV_STAGES));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -149,7 +220,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       mbar_init(pv_full(b), 1);
       mbar_init(pv_empty(b), 4 * SPLIT);
     }
-    mbar_init(xch_bar, 4 * SPLIT);
+    for (int g = 0; g < 4; ++g) mbar_init(xch_bar_of(g), SPLIT);   // the SPLIT warps that share rows
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -196,6 +267,8 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       const long long t_begin = STATS ? clock64() : 0;
       bool ok = mbar_wait(q_full, 0);
       if (!ok) report(p.status, kStatusMmaWaitTimeout);
+      const uint64_t q_desc = make_smem_desc(q_smem, 16, 1024);
+      const uint64_t p_desc = make_smem_desc(p_smem(0), 16, 1024);
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES, b = j & 1;
         long long t0 = STATS ? clock64() : 0;
@@ -204,10 +277,11 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         if (!mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1u)) return false;
         if (STATS) w_se += clock64() - t0;
         tcgen05_fence_after();
+        // a step of 16 along d is 32 bytes inside the swizzled rows: +2 in the address field
+        const uint64_t kd = make_smem_desc(k_smem(s), 16, 1024);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          tcgen05_mma_f16(tmem_base + b * BKV, make_smem_desc(q_smem + k * 32, 16, 1024),
-                          make_smem_desc(k_smem(s) + k * 32, 16, 1024), p.idesc_s, k ? 1u : 0u);
+          tcgen05_mma_f16(tmem_base + b * BKV, q_desc + 2 * k, kd + 2 * k, p.idesc_s, k ? 1u : 0u);
         tcgen05_commit(s_full(b));
         return true;
       };
@@ -219,11 +293,19 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         if (!mbar_wait(pv_empty(b), ((j >> 1) & 1) ^ 1u)) return false;
         if (STATS) w_pe += clock64() - t0;
         tcgen05_fence_after();
+        // P: 16 keys are 32 bytes (+2) inside a box of 64 keys, the second box 16 KB on (+1024);
+        // V: 16 keys are 16 rows of 128 bytes (+128)
+        const uint64_t pd = p_desc + static_cast<uint64_t>(b) * (P_BYTES >> 4);
+        const uint64_t vd = make_smem_desc(v_smem(s), TILE_BYTES, 1024);
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k)
-          tcgen05_mma_f16(tmem_base + PV_COL + b * DH,
-                          make_smem_desc(p_smem(b) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024),
-                          make_smem_desc(v_smem(s) + k * 2048, TILE_BYTES, 1024), p.idesc_pv, k ? 1u : 0u);
+        for (int k = 0; k < BKV / 16; ++k) {
+          if constexpr (PTMEM)
+            tcgen05_mma_f16_a_tmem(tmem_base + PV_COL + b * DH, tmem_base + P_COL + b * (BKV / 2) + k * 8,
+                                   vd + k * 128, p.idesc_pv, k ? 1u : 0u);
+          else
+            tcgen05_mma_f16(tmem_base + PV_COL + b * DH, pd + (k >> 2) * (TILE_BYTES >> 4) + (k & 3) * 2,
+                            vd + k * 128, p.idesc_pv, k ? 1u : 0u);
+        }
         tcgen05_commit(pv_full(b));   // PV_j is complete: P buffer b and this K/V stage are free again
         tcgen05_commit(kv_empty(s));
         return true;
@@ -260,9 +342,10 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     const uint32_t p_row_off = ((part * HC) >> 6) * TILE_BYTES + r * 128;
     const uint32_t chunk0 = static_cast<uint32_t>(((part * HC) & 63) >> 3);
     const uint32_t swz = static_cast<uint32_t>(r & 7);
-    float o[HO];
+    const uint32_t xch_bar = xch_bar_of(lane_group);
+    uint64_t o2[HO / 2];   // output accumulators, two f32 per register (fma.rn.f32x2)
 #pragma unroll
-    for (int i = 0; i < HO; ++i) o[i] = 0.0f;
+    for (int i = 0; i < HO / 2; ++i) o2[i] = 0ull;
     float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
     const float neg_inf = -INFINITY;
     bool ok = true;
@@ -293,8 +376,9 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       uint32_t v[HO];
       tmem_ld_cols<HO>(t_row + PV_COL + (j & 1) * DH + part * HO, v);
       tmem_ld_wait();
+      const uint64_t alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll
-      for (int i = 0; i < HO; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(v[i]));
+      for (int i = 0; i < HO / 2; ++i) o2[i] = fma_f32x2(o2[i], alpha2, pack_u32x2(v[2 * i], v[2 * i + 1]));
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pv_empty(j & 1));
@@ -333,7 +417,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       float mx = neg_inf;   // in units of log2: s * sm_scale * log2 e
       if (plain) {
 #pragma unroll
-        for (int i = 0; i < HC; ++i) mx = fmaxf(mx, __uint_as_float(sc[i]));
+        for (int i = 0; i < HC; i += 2) mx = max3(mx, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
         mx *= p.scale_log2e;
       } else {
 #pragma unroll
@@ -348,25 +432,57 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       const uint32_t p_row = p_smem(b) + p_row_off;
       float rowsum = 0.0f;
       const float neg_m = -m_new;
+      uint32_t pw[HC / 2];   // this thread's keys of P, two 16-bit values per word
+      if (FAST16 && plain) {
+        const uint64_t scale2 = pack_f32x2(p.scale_log2e, p.scale_log2e);
+        const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
 #pragma unroll
-      for (int q = 0; q < HC / 8; ++q) {  // 16-byte chunks of 8 keys
-        float e[8];
-        if (plain) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) e[i] = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, neg_m));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float pe = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, neg_m));
-            e[i] = (8 * q + i < valid) ? pe : 0.0f;
-          }
+        for (int i = 0; i < HC / 2; ++i) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_u32x2(sc[2 * i], sc[2 * i + 1]), scale2, neg_m2), x0, x1);
+          pw[i] = ex2_f16x2(pack2(x0, x1, 0));
         }
-        rowsum += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
-        st_shared_v4_u32(p_row + (((chunk0 + static_cast<uint32_t>(q)) ^ swz) << 4), pack2(e[0], e[1], p.is_bf16),
-                         pack2(e[2], e[3], p.is_bf16), pack2(e[4], e[5], p.is_bf16),
-                         pack2(e[6], e[7], p.is_bf16));
+        uint32_t acc[HC / 4];
+#pragma unroll
+        for (int i = 0; i < HC / 4; ++i) acc[i] = add_f16x2(pw[2 * i], pw[2 * i + 1]);
+#pragma unroll
+        for (int n = HC / 4; n > 1; n >>= 1)
+#pragma unroll
+          for (int q = 0; q < n / 2; ++q) acc[q] = add_f16x2(acc[q], acc[q + n / 2]);
+        rowsum = sum_halves_f16x2(acc[0]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < HC / 8; ++q) {  // 8 keys at a time
+          float e[8];
+          if (plain) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, neg_m));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float pe = ex2(fmaf(__uint_as_float(sc[8 * q + i]), p.scale_log2e, neg_m));
+              e[i] = (8 * q + i < valid) ? pe : 0.0f;
+            }
+          }
+          rowsum += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) pw[4 * q + i] = pack2(e[2 * i], e[2 * i + 1], p.is_bf16);
+        }
       }
-      fence_async_smem();  // P (generic-proxy stores) visible to the tensor core's reads
+      if constexpr (PTMEM) {
+        // buffer b was last read by PV_{j-2}, whose completion this thread saw when it folded it in
+#pragma unroll
+        for (int c = 0; c < HC / 2; c += 16)
+          tmem_st_16cols(t_row + P_COL + b * (BKV / 2) + part * (HC / 2) + c, pw + c);
+        tmem_st_wait();
+        tcgen05_fence_before();
+      } else {
+#pragma unroll
+        for (int q = 0; q < HC / 8; ++q)
+          st_shared_v4_u32(p_row + (((chunk0 + static_cast<uint32_t>(q)) ^ swz) << 4), pw[4 * q], pw[4 * q + 1],
+                           pw[4 * q + 2], pw[4 * q + 3]);
+        fence_async_smem();  // P (generic-proxy stores) visible to the tensor core's reads
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(b));
       l = fmaf(l, alpha, rowsum);
@@ -389,6 +505,9 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       if (lane == 0) report(p.status, kStatusEpiWaitTimeout);
     } else if (q0 + r < p.n_ctx) {
       const float inv = 1.0f / l_row;
+      float o[HO];
+#pragma unroll
+      for (int i = 0; i < HO / 2; ++i) unpack_f32x2(o2[i], o[2 * i], o[2 * i + 1]);
       uint16_t *orow = static_cast<uint16_t *>(p.O) + static_cast<size_t>(head_row0 + q0 + r) * DH + part * HO;
 #pragma unroll
       for (int c = 0; c < HO; c += 8) {
@@ -428,18 +547,23 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
   if (!flash_attention_supported(heads, n_ctx, d_head, dtype, q, k, v, o)) return cudaErrorNotSupported;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  static int split = 4;  // threads per query row (IMEX_ATTN_SPLIT=2 for the two-thread form)
-  static bool with_stats = false;
+  static bool with_stats = false, exp_f32 = false, p_smem = false;
+  using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
+  // [stats][fast16][p in TMEM]
+  static const Kernel kernels[2][2][2] = {
+      {{flash_attention_fwd_kernel<4, false, false, false>, flash_attention_fwd_kernel<4, false, false, true>},
+       {flash_attention_fwd_kernel<4, false, true, false>, flash_attention_fwd_kernel<4, false, true, true>}},
+      {{flash_attention_fwd_kernel<4, true, false, false>, flash_attention_fwd_kernel<4, true, false, true>},
+       {flash_attention_fwd_kernel<4, true, true, false>, flash_attention_fwd_kernel<4, true, true, true>}}};
   std::call_once(once, [] {
-    if (const char *e = getenv("IMEX_ATTN_SPLIT")) split = atoi(e) == 2 ? 2 : 4;
     with_stats = getenv("IMEX_ATTN_STATS") != nullptr;  // development aid: where the roles wait
-    cudaError_t e2 = cudaFuncSetAttribute(flash_attention_fwd_kernel<2, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaError_t e4 = cudaFuncSetAttribute(flash_attention_fwd_kernel<4, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaError_t e5 = cudaFuncSetAttribute(flash_attention_fwd_kernel<4, true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    attr_err = e2 != cudaSuccess ? e2 : e4 != cudaSuccess ? e4 : e5;
+    if (const char *e = getenv("IMEX_ATTN_EXP")) exp_f32 = std::string(e) == "f32";  // f16: every exponential in f32
+    if (const char *e = getenv("IMEX_ATTN_P")) p_smem = std::string(e) == "smem";   // P through shared memory
+    for (int i = 0; i < 8; ++i) {
+      cudaError_t x = cudaFuncSetAttribute(kernels[i >> 2][(i >> 1) & 1][i & 1],
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      if (x != cudaSuccess) attr_err = x;
+    }
   });
   if (attr_err != cudaSuccess) return attr_err;
   // heads are a dimension of the tensor maps: a tile that runs past the last key (or query) of
@@ -470,12 +594,8 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
     if (!stats_buf) cudaMallocManaged(&stats_buf, 8 * 4096 * sizeof(long long));
     p.stats = stats_buf;
   }
-  if (p.stats)
-    flash_attention_fwd_kernel<4, true><<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
-  else if (split == 2)
-    flash_attention_fwd_kernel<2, false><<<grid, num_threads(2), SMEM_BYTES, stream>>>(tq, tk, tv, p);
-  else
-    flash_attention_fwd_kernel<4, false><<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  const bool fast16 = dtype == kF16 && !exp_f32;
+  kernels[p.stats ? 1 : 0][fast16 ? 1 : 0][p_smem ? 0 : 1]<<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
   if (p.stats) {
     cudaStreamSynchronize(stream);
     double a[8] = {0};

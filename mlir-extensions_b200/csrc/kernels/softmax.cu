@@ -135,6 +135,12 @@ template <int V, int MAXW>
 __global__ void __launch_bounds__(32 * MAXW)
 softmax_warp_balanced_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int cols,
                              float max_init) {
+  // Launched with programmatic stream serialisation: this grid may be set up on the SMs while
+  // the launch before it in the stream is still running.  Nothing is read or written before
+  // the wait, which returns once that launch has completed and its writes are visible; the
+  // launch after this one is allowed to be set up from here on.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int nvec = cols >> 2;
@@ -270,8 +276,19 @@ cudaError_t launch_warp(const float *x, float *y, int64_t rows, int cols, float 
     const int64_t rounds = (per_sm + MAXW - 1) / MAXW;        // rows a warp walks
     const int warps_cta = static_cast<int>((per_sm + rounds - 1) / rounds);
     const unsigned grid = static_cast<unsigned>(rows < sms ? rows : sms);
-    softmax_warp_balanced_kernel<V, MAXW><<<grid, 32 * warps_cta, 0, stream>>>(x, y, rows, cols, max_init);
-    return cudaGetLastError();
+    // a launch of a few microseconds: let its set-up overlap the end of the launch before it
+    // (IMEX_SOFTMAX_PDL=0: plain stream order)
+    static const bool pdl = !(getenv("IMEX_SOFTMAX_PDL") && atoi(getenv("IMEX_SOFTMAX_PDL")) == 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(32 * warps_cta);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, softmax_warp_balanced_kernel<V, MAXW>, x, y, rows, cols, max_init);
   }
   const int warps = 8;
   unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
