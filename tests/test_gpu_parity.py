@@ -887,6 +887,28 @@ def test_attention_heads_do_not_see_each_other_in_a_ragged_last_tile(pkg, sess, 
     assert oracle.rel_frobenius(got, ref) <= 1e-3
 
 
+@pytest.mark.parametrize("kind,heads,n_ctx,tol", [("f16", 2, 2048, 1e-3), ("bf16", 2, 1000, 2.0 ** -8)])
+def test_attention_with_row_maxima_that_keep_growing(pkg, sess, kind, heads, n_ctx, tol):
+    """The kernel keeps a reference maximum per row and rescales O and the running sum only when
+    a block's maximum outgrows it by more than 2^8.  Keys that grow along the sequence (by 8x
+    in all, with one block that jumps by another 2x) make that happen again and again; the
+    result must not depend on it."""
+    B = pkg.blob
+    q, k, v = _attention_inputs(heads, n_ctx, kind, 77)
+    conv = oracle.bf16_bits_to_f32 if kind == "bf16" else oracle.f16_bits_to_f32
+    back = oracle.to_bf16_bits if kind == "bf16" else oracle.to_f16_bits
+    kf = conv(k).reshape(heads, n_ctx, 64)
+    kf = kf * (1.0 + 7.0 * np.arange(n_ctx, dtype=np.float32) / n_ctx).reshape(1, n_ctx, 1)
+    kf[1, n_ctx // 2: n_ctx // 2 + 128] *= 2.0
+    k = back(kf.reshape(heads * n_ctx, 64).astype(np.float32))
+    dq, dk, dv, do = sess.upload(q), sess.upload(k), sess.upload(v), sess.alloc(q.nbytes)
+    sess.run(B.attention_fwd("attn", heads, n_ctx, 64, B.BF16 if kind == "bf16" else B.F16, 0.5), [dq, dk, dv, do])
+    got = conv(sess.download(do, q.shape, np.uint16))
+    ref = conv(oracle.attention_fwd(q, k, v, heads, 0.5, kind == "bf16"))
+    assert np.isfinite(got).all()
+    assert oracle.rel_frobenius(got, ref) <= tol
+
+
 def test_attention_forward_at_the_reference_size(pkg, sess):
     """Z = 2, H = 2, N_CTX = 4096, D_HEAD = 64, sm_scale 0.5
     (flash_attention_fwd.mlir:452-456): sampled heads' rows against the oracle, every row
