@@ -193,6 +193,7 @@ bool single_mode(const unsigned char *code, int ncode) {
   return true;
 }
 
+// reduce with vec == -1: the "tall" form of the leading-dim reduce (many rows, few columns)
 std::string generate(const unsigned char *code, int ncode, int n_inputs, int dtype, int out_dtype,
                      bool reduce, int vec) {
   const TypeInfo in = type_info(dtype), out = type_info(reduce ? dtype : out_dtype);
@@ -206,6 +207,38 @@ std::string generate(const unsigned char *code, int ncode, int n_inputs, int dty
   auto load = [&](int k, const std::string &idx) {
     return std::string(in.load) + "(p" + std::to_string(k) + "[" + idx + "])";
   };
+  if (reduce && vec == -1) {
+    // Few columns, many rows (the reference's kInputFusion: 512 x 1024): one thread per column
+    // would walk the rows alone, evaluating the chain's transcendental functions one after the
+    // other.  Here a CTA takes 16 columns; all 256 threads evaluate the chain for a tile of 128
+    // rows into shared memory, then one thread per column adds the tile's values in row
+    // order: the rounded adds keep the loop nest's order, the rest runs in parallel.
+    os << "  __shared__ float vals[128][17];\n"
+       << "  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;\n"
+       << "  const long long col = blockIdx.x * 16LL + tx;\n"
+       << "  const bool live = col < cols;\n"
+       << "  float acc = (live && ty == 0 && accumulate) ? " << in.load << "(y[col]) : 0.0f;\n"
+       << "  for (long long r0 = 0; r0 < rows; r0 += 128) {\n"
+       << "#pragma unroll\n"   // all eight passes at once: their loads are in flight together
+       << "    for (int i = 0; i < 8; ++i) {\n"
+       << "      const long long row = r0 + ty + 16 * i;\n"
+       << "      if (live && row < rows) {\n";
+    for (int k = 0; k < n_inputs; ++k)
+      if (sh.mode[k] >= 0)
+        os << "    const float x" << k << " = "
+           << load(k, sh.mode[k] == 0 ? "row * cols + col" : sh.mode[k] == 1 ? "col" : "row") << ";\n";
+    const std::string r = emit_body(code, ncode, in.round, os);
+    os << "        vals[ty + 16 * i][tx] = " << r << ";\n      }\n    }\n"
+       << "    __syncthreads();\n"
+       << "    if (live && ty == 0) {\n"
+       << "      const int n = rows - r0 < 128 ? (int)(rows - r0) : 128;\n"
+       << "#pragma unroll 8\n"
+       << "      for (int k = 0; k < n; ++k) acc = "
+       << (in.round[0] ? std::string(in.round) + "(__fadd_rn(acc, vals[k][tx]))" : "__fadd_rn(acc, vals[k][tx])") << ";\n"
+       << "    }\n    __syncthreads();\n  }\n"
+       << "  if (live && ty == 0) y[col] = " << out.store << "(acc);\n}\n";
+    return os.str();
+  }
   if (reduce) {
     os << "  const long long col = blockIdx.x * (long long)blockDim.x + threadIdx.x;\n"
        << "  if (col >= cols) return;\n"
@@ -305,6 +338,8 @@ cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, 
   // elements per thread: 16 bytes of the narrower of input and output type, when the
   // row length and the alignment allow it
   int vec = 1;
+  // too few columns to fill the GPU with one thread each, and enough rows to share out
+  if (reduce_leading && rows >= 64 && cols < 148LL * 256) vec = -1;
   if (!reduce_leading) {
     bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int i = 0; i < n_inputs; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(inputs[i]) & 15) == 0;
@@ -342,7 +377,7 @@ cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, 
   args.push_back(&acc);
   unsigned blocks;
   if (reduce_leading) {
-    blocks = static_cast<unsigned>((cols + 255) / 256);
+    blocks = static_cast<unsigned>(vec == -1 ? (cols + 15) / 16 : (cols + 255) / 256);
   } else {
     const long long groups = rows * (cols / vec);
     long long b = (groups + 255) / 256;

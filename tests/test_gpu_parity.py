@@ -791,13 +791,14 @@ def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind, expr_path
         assert sess.download(dy32, (rows, cols), np.float32).tobytes() == ref.tobytes()
 
 
+@pytest.mark.parametrize("shape", [(512, 1024), (200, 70), (40, 300)])
 @pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
-def test_fused_chain_into_column_reduce(pkg, sess, kind, expr_path):
+def test_fused_chain_into_column_reduce(pkg, sess, kind, expr_path, shape):
     """|x0| + x1 summed over the rows, ascending, every step in the element type: the shape of
     benchmarks/kInputFusion/kInputFusion.mlir.in:6-41 with exact operations -> bit-exact;
     then the benchmark's own chain (with log) within a last-bit budget."""
     B = pkg.blob
-    rows, cols = 512, 1024
+    rows, cols = shape   # (200, 70): ragged tiles of the many-rows form; (40, 300): one thread per column
     bdt, odt, x0_dev, x0 = _typed(pkg, kind, oracle.fill_uniform((rows, cols), 37, -1.0, 1.0))
     _, _, x1_dev, x1 = _typed(pkg, kind, oracle.fill_uniform((rows, cols), 38, 0.5, 2.0))
     d0, d1 = sess.upload(x0_dev), sess.upload(x1_dev)
