@@ -239,6 +239,43 @@ std::string generate(const unsigned char *code, int ncode, int n_inputs, int dty
        << "  if (live && ty == 0) y[col] = " << out.store << "(acc);\n}\n";
     return os.str();
   }
+  auto vec_type = [](int bytes) { return bytes == 16 ? "uint4" : bytes == 8 ? "uint2" : bytes == 4 ? "unsigned" : "u16"; };
+  if (reduce && vec >= 2) {
+    // Many columns: `vec` adjacent columns per thread (16-byte loads), one running sum per
+    // column, each added to in row order.
+    const int in_bytes = dtype == kF32 ? 4 : 2;
+    const std::string vt = vec_type(vec * in_bytes);
+    os << "  const long long col = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * " << vec << ";\n"
+       << "  if (col >= cols) return;\n"
+       << "  float acc[" << vec << "];\n"
+       << "  __align__(16) " << in.ctype << " yv[" << vec << "];\n"
+       << "  if (accumulate) *reinterpret_cast<" << vt << " *>(yv) = *reinterpret_cast<const " << vt << " *>(y + col);\n"
+       << "#pragma unroll\n  for (int e = 0; e < " << vec << "; ++e) acc[e] = accumulate ? " << in.load << "(yv[e]) : 0.0f;\n"
+       << "#pragma unroll 4\n  for (long long row = 0; row < rows; ++row) {\n";
+    for (int k = 0; k < n_inputs; ++k) {
+      if (sh.mode[k] < 0) continue;
+      if (sh.mode[k] == 2) {
+        os << "    const float s" << k << " = " << load(k, "row") << ";\n";
+        continue;
+      }
+      os << "    __align__(16) " << in.ctype << " v" << k << "[" << vec << "];\n"
+         << "    *reinterpret_cast<" << vt << " *>(v" << k << ") = *reinterpret_cast<const " << vt << " *>(p" << k
+         << " + " << (sh.mode[k] == 0 ? "row * cols + col" : "col") << ");\n";
+    }
+    os << "#pragma unroll\n    for (int e = 0; e < " << vec << "; ++e) {\n";
+    for (int k = 0; k < n_inputs; ++k) {
+      if (sh.mode[k] < 0) continue;
+      if (sh.mode[k] == 2) os << "    const float x" << k << " = s" << k << ";\n";
+      else os << "    const float x" << k << " = " << in.load << "(v" << k << "[e]);\n";
+    }
+    const std::string r = emit_body(code, ncode, in.round, os);
+    os << "      acc[e] = "
+       << (in.round[0] ? std::string(in.round) + "(__fadd_rn(acc[e], " + r + "))" : "__fadd_rn(acc[e], " + r + ")")
+       << ";\n    }\n  }\n"
+       << "#pragma unroll\n  for (int e = 0; e < " << vec << "; ++e) yv[e] = " << out.store << "(acc[e]);\n"
+       << "  *reinterpret_cast<" << vt << " *>(y + col) = *reinterpret_cast<const " << vt << " *>(yv);\n}\n";
+    return os.str();
+  }
   if (reduce) {
     os << "  const long long col = blockIdx.x * (long long)blockDim.x + threadIdx.x;\n"
        << "  if (col >= cols) return;\n"
@@ -261,7 +298,6 @@ std::string generate(const unsigned char *code, int ncode, int n_inputs, int dty
      << "    const long long row = g / groups_per_row, col = (g % groups_per_row) * " << vec << ";\n"
      << "    const long long base = row * cols + col;\n";
   const int in_bytes = dtype == kF32 ? 4 : 2, out_bytes = (out_dtype == kF32 ? 4 : 2);
-  auto vec_type = [](int bytes) { return bytes == 16 ? "uint4" : bytes == 8 ? "uint2" : bytes == 4 ? "unsigned" : "u16"; };
   // packed loads of the full-tensor and row-vector inputs
   for (int k = 0; k < n_inputs; ++k) {
     if (sh.mode[k] < 0) continue;
@@ -340,6 +376,13 @@ cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, 
   int vec = 1;
   // too few columns to fill the GPU with one thread each, and enough rows to share out
   if (reduce_leading && rows >= 64 && cols < 148LL * 256) vec = -1;
+  if (reduce_leading && vec == 1) {
+    // enough columns to fill the GPU with several per thread, and 16-byte alignment throughout
+    const int want = dtype == kF32 ? 4 : 8;
+    bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && cols % want == 0;
+    for (int i = 0; i < n_inputs; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(inputs[i]) & 15) == 0;
+    if (aligned && cols / want >= 148LL * 512) vec = want;
+  }
   if (!reduce_leading) {
     bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int i = 0; i < n_inputs; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(inputs[i]) & 15) == 0;
@@ -377,7 +420,7 @@ cudaError_t launch_expr_jit(const void *const *inputs, int n_inputs, void *out, 
   args.push_back(&acc);
   unsigned blocks;
   if (reduce_leading) {
-    blocks = static_cast<unsigned>(vec == -1 ? (cols + 15) / 16 : (cols + 255) / 256);
+    blocks = static_cast<unsigned>(vec == -1 ? (cols + 15) / 16 : vec > 1 ? (cols / vec + 255) / 256 : (cols + 255) / 256);
   } else {
     const long long groups = rows * (cols / vec);
     long long b = (groups + 255) / 256;
