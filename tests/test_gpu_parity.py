@@ -824,8 +824,8 @@ def test_fused_chain_into_column_reduce(pkg, sess, kind, expr_path, shape):
     ref3 = oracle.reduce_leading_as(oracle.binary("addf", oracle.unary("log", x1, odt),
                                                   oracle.unary("absf", x0, odt), odt), odt)
     # logf differs by the last bit between CUDA's and glibc's libm; a sum of log(x1) < 0 and |x0| can
-    # cancel, and among 600 thousand columns of 6 rows some do: the budget is relative to the
-    # sum of the terms' magnitudes there
+    # cancel, and among 600 thousand columns of 6 rows some nearly do (measured 3e-5): a wider
+    # budget there
     tol = {"f32": 1e-5 if cols < 100000 else 1e-4, "f16": 2.0 ** -8, "bf16": 2.0 ** -5}[kind]
     assert oracle.max_rel_err(got3, ref3, 1e-3) <= tol
 
