@@ -8,7 +8,7 @@
 // algorithmic traffic = 2 * rows * cols * 4 bytes.
 //
 // Arithmetic per element is the reference's: t = x - max (exact max),
-// e = exp(t) (see exp_neg: within ~3e-7 of libm's expf), y = e / sum with IEEE division.  Only the order of the adds in
+// e = exp(t) (see exp_neg: within ~3e-7 of libm's expf), y = e / sum correctly rounded (see div_by).  Only the order of the adds in
 // `sum` differs from the sequential loop (per-lane partial sums + shuffle
 // tree), which is where the <= 1e-5 relative tolerance goes.
 #include "kernels.h"
@@ -57,9 +57,25 @@ __device__ __forceinline__ float exp_neg(float t) {
 // fmaxf drops NaNs where arith.maximumf keeps them; a NaN element still turns
 // the whole row into NaN through exp -> sum -> divide, as in the reference.
 
+__device__ __forceinline__ float4 ldg_stream4(const float4 *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+// e / s by one correctly rounded reciprocal per row (rc = rn(1 / s)) and one residual step per
+// element (q = e * rc; q += (e - q * s) * rc): the correctly rounded quotient for every normal
+// result (Markstein), at 3 instructions per element instead of the ~10 of a full IEEE
+// division sequence.
+__device__ __forceinline__ float div_by(float e, float s, float rc) {
+  const float q = __fmul_rn(e, rc);
+  return __fmaf_rn(__fmaf_rn(-q, s, e), rc, q);
+}
+
 // One warp per row, the whole row in registers: cols == 4 * 32 * V exactly or
 // ragged (guarded), cols <= 128 * V.
-template <int V>
+template <int V, bool FULL>
 __global__ void __launch_bounds__(256)
 softmax_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int cols,
                     float max_init) {
@@ -73,8 +89,8 @@ softmax_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t 
   float4 v[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) {
-    int idx = lane + 32 * i;
-    v[i] = (idx < nvec) ? __ldg(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    const int idx = lane + 32 * i;
+    v[i] = (FULL || idx < nvec) ? __ldg(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
   }
   float m = max_init;
 #pragma unroll
@@ -84,26 +100,32 @@ softmax_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t 
   float s = 0.0f;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
-    int idx = lane + 32 * i;
-    if (idx < nvec) {
-      v[i].x = exp_neg(v[i].x - m);
-      v[i].y = exp_neg(v[i].y - m);
-      v[i].z = exp_neg(v[i].z - m);
-      v[i].w = exp_neg(v[i].w - m);
-      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-    }
+    // a lane past the end of the row holds -inf: exp gives 0, which adds nothing
+    v[i].x = exp_neg(v[i].x - m);
+    v[i].y = exp_neg(v[i].y - m);
+    v[i].z = exp_neg(v[i].z - m);
+    v[i].w = exp_neg(v[i].w - m);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
   }
   s = warp_sum(s);
+  // division by one correctly rounded reciprocal and a residual step per element (div_by);
+  // a sum that is not a finite normal number >= 1 (NaN row, overflow) takes the full division
+  if (s >= 1.0f && s < 3.0e38f) {
+    const float rc = __frcp_rn(s);
 #pragma unroll
-  for (int i = 0; i < V; ++i) {
-    int idx = lane + 32 * i;
-    if (idx < nvec) {
-      float4 o;
-      o.x = __fdiv_rn(v[i].x, s);
-      o.y = __fdiv_rn(v[i].y, s);
-      o.z = __fdiv_rn(v[i].z, s);
-      o.w = __fdiv_rn(v[i].w, s);
-      yr[idx] = o;
+    for (int i = 0; i < V; ++i) {
+      const int idx = lane + 32 * i;
+      if (FULL || idx < nvec)
+        yr[idx] = make_float4(div_by(v[i].x, s, rc), div_by(v[i].y, s, rc), div_by(v[i].z, s, rc),
+                              div_by(v[i].w, s, rc));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int idx = lane + 32 * i;
+      if (FULL || idx < nvec)
+        yr[idx] = make_float4(__fdiv_rn(v[i].x, s), __fdiv_rn(v[i].y, s), __fdiv_rn(v[i].z, s),
+                              __fdiv_rn(v[i].w, s));
     }
   }
 }
@@ -115,23 +137,9 @@ softmax_warp_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t 
 // share of the rows (up to MAXW), so every SM issues all of its loads in the first
 // microsecond and owns the same number of rows to within one; with more rows than
 // SMs x MAXW a warp walks several rows.  Row r goes to CTA r % gridDim.x.
-// The division is by one correctly rounded reciprocal per row and one residual step per
-// element (q = e * rc; q += (e - q * s) * rc): the correctly rounded quotient e / s for
-// every normal result (Markstein), at 3 instructions per element instead of the ~10 of a
-// full IEEE division sequence.
-__device__ __forceinline__ float4 ldg_stream4(const float4 *p) {
-  float4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p));
-  return v;
-}
-__device__ __forceinline__ float div_by(float e, float s, float rc) {
-  const float q = __fmul_rn(e, rc);
-  return __fmaf_rn(__fmaf_rn(-q, s, e), rc, q);
-}
-
-template <int V, int MAXW>
+// FULL: cols == 4 * 32 * V exactly, so no lane is ever past the end of its row and the loop
+// bodies carry no predicates (the benchmark's 1024 columns with V = 8).
+template <int V, int MAXW, bool FULL>
 __global__ void __launch_bounds__(32 * MAXW)
 softmax_warp_balanced_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int cols,
                              float max_init) {
@@ -152,7 +160,7 @@ softmax_warp_balanced_kernel(const float *__restrict__ x, float *__restrict__ y,
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const int idx = lane + 32 * i;
-      v[i] = (idx < nvec) ? ldg_stream4(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      v[i] = (FULL || idx < nvec) ? ldg_stream4(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
     }
     float m = max_init;
 #pragma unroll
@@ -161,31 +169,31 @@ softmax_warp_balanced_kernel(const float *__restrict__ x, float *__restrict__ y,
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-      if (lane + 32 * i < nvec) {
-        v[i].x = exp_neg(v[i].x - m);
-        v[i].y = exp_neg(v[i].y - m);
-        v[i].z = exp_neg(v[i].z - m);
-        v[i].w = exp_neg(v[i].w - m);
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-      }
+      // a lane past the end of the row holds -inf: exp gives 0, which adds nothing
+      v[i].x = exp_neg(v[i].x - m);
+      v[i].y = exp_neg(v[i].y - m);
+      v[i].z = exp_neg(v[i].z - m);
+      v[i].w = exp_neg(v[i].w - m);
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
     s = warp_sum(s);
-    const float rc = __frcp_rn(s);
-    // a sum that is not a finite normal number (NaN row, overflow) takes the full division
-    const bool plain = !(s >= 1.0f && s < 3.0e38f);
+    // a sum that is not a finite normal number >= 1 (NaN row, overflow) takes the full division
+    if (s >= 1.0f && s < 3.0e38f) {
+      const float rc = __frcp_rn(s);
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < nvec) {
-        float4 o;
-        if (plain) {
-          o.x = __fdiv_rn(v[i].x, s); o.y = __fdiv_rn(v[i].y, s);
-          o.z = __fdiv_rn(v[i].z, s); o.w = __fdiv_rn(v[i].w, s);
-        } else {
-          o.x = div_by(v[i].x, s, rc); o.y = div_by(v[i].y, s, rc);
-          o.z = div_by(v[i].z, s, rc); o.w = div_by(v[i].w, s, rc);
-        }
-        yr[idx] = o;
+      for (int i = 0; i < V; ++i) {
+        const int idx = lane + 32 * i;
+        if (FULL || idx < nvec)
+          yr[idx] = make_float4(div_by(v[i].x, s, rc), div_by(v[i].y, s, rc), div_by(v[i].z, s, rc),
+                                div_by(v[i].w, s, rc));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const int idx = lane + 32 * i;
+        if (FULL || idx < nvec)
+          yr[idx] = make_float4(__fdiv_rn(v[i].x, s), __fdiv_rn(v[i].y, s), __fdiv_rn(v[i].z, s),
+                                __fdiv_rn(v[i].w, s));
       }
     }
   }
@@ -288,11 +296,14 @@ cudaError_t launch_warp(const float *x, float *y, int64_t rows, int cols, float 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, softmax_warp_balanced_kernel<V, MAXW>, x, y, rows, cols, max_init);
+    if (cols == 4 * 32 * V)
+      return cudaLaunchKernelEx(&cfg, softmax_warp_balanced_kernel<V, MAXW, true>, x, y, rows, cols, max_init);
+    return cudaLaunchKernelEx(&cfg, softmax_warp_balanced_kernel<V, MAXW, false>, x, y, rows, cols, max_init);
   }
   const int warps = 8;
   unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
-  softmax_warp_kernel<V><<<grid, warps * 32, 0, stream>>>(x, y, rows, cols, max_init);
+  if (cols == 4 * 32 * V) softmax_warp_kernel<V, true><<<grid, warps * 32, 0, stream>>>(x, y, rows, cols, max_init);
+  else softmax_warp_kernel<V, false><<<grid, warps * 32, 0, stream>>>(x, y, rows, cols, max_init);
   return cudaGetLastError();
 }
 

@@ -55,8 +55,15 @@ struct Allocation {
   int device;
 };
 
+struct Stream;
 struct Event {
   cudaEvent_t ev = nullptr;
+  // Set instead of recording `ev` when the launch was issued while its stream was being
+  // captured into a CUDA graph: an event record would become a graph node of its own between
+  // the kernel nodes (about a microsecond each, and it cuts the programmatic edge that lets
+  // consecutive launches overlap).  Such a handle orders only work on the same stream, which
+  // stream order gives anyway.
+  Stream *ordered_on = nullptr;
 };
 
 // Launch-completion events come from a ring of kEventSlots per stream, created on first
@@ -601,12 +608,27 @@ Event *launch(Stream *s, Kernel *k, size_t sharedMemBytes, ImexParamDesc *params
     }
   }
   if (deps)
-    for (size_t i = 0; deps[i].event; ++i)
-      CHECK_CUDA(cudaStreamWaitEvent(s->stream, static_cast<Event *>(deps[i].event)->ev, 0));
+    for (size_t i = 0; deps[i].event; ++i) {
+      auto *dep = static_cast<Event *>(deps[i].event);
+      if (dep->ordered_on) {
+        if (dep->ordered_on != s)
+          throw std::runtime_error("gpuLaunchKernel: a launch captured into a CUDA graph cannot be waited for from "
+                                   "another stream");
+        continue;   // same stream: already ordered
+      }
+      CHECK_CUDA(cudaStreamWaitEvent(s->stream, dep->ev, 0));
+    }
   for (void *p : ptrs) prefetch_managed(s, p);
   if (getenv("IMEX_ENABLE_PROFILING")) profile(s, k->desc, ptrs.data(), ptrs.size(), k->source);
   enqueue(s, k->desc, ptrs.data(), ptrs.size(), k->source);
   Event *ev = &s->events[s->next_event++ % kEventSlots];
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  CHECK_CUDA(cudaStreamIsCapturing(s->stream, &capturing));
+  if (capturing == cudaStreamCaptureStatusActive) {
+    ev->ordered_on = s;
+    return ev;
+  }
+  ev->ordered_on = nullptr;
   if (!ev->ev) CHECK_CUDA(cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming));
   CHECK_CUDA(cudaEventRecord(ev->ev, s->stream));
   return ev;
