@@ -807,9 +807,10 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
                                   "frac_of_nominal_8000": ach / 8000.0},
                      "roofline_ms": med, "note": note}
         if ptr_sets:
-            # a problem this small is timed mostly by the event pair around ONE launch (a plain
-            # copy of the same bytes takes as long); the launch duration proper shows when
-            # launches follow each other inside one CUDA graph
+            # an event pair around ONE launch adds 5-10 us (all of a 32 MiB problem's time, a tenth
+            # of a 512 MiB problem's; a plain copy timed that way loses as much); the launch
+            # duration proper shows when launches on distinct buffers follow each other inside
+            # one CUDA graph, which is also how a streaming peak is measured
             try:
                 b2b, b2b_min = graph_back_to_back(torch, stream, sess, kernel, ptr_sets)
             except Exception as e:  # noqa: BLE001 - reported, the flushed figure stays
@@ -828,7 +829,7 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
                 except Exception as e:  # noqa: BLE001
                     out[name]["copy_graph_timing_error"] = repr(e)[:200]
             out[name]["roofline"].update(achieved=ach2, frac=ach2 / hbm, frac_of_nominal_8000=ach2 / 8000.0,
-                                         timing="%d launches on %d distinct buffer pairs (%d MiB in all, larger "
+                                         timing="%d launches on %d distinct buffer sets (%d MiB in all, larger "
                                                 "than L2) replayed as one CUDA graph, one event pair around the "
                                                 "replay; the flushed single-launch figure is "
                                                 "gbs_flushed_single_launch"
@@ -847,17 +848,19 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
     # config 4a: row reduce 32768 x 8192
     R = torch.empty((32768, 8192), dtype=torch.float32, device=dev).uniform_(0.0, 1.0)
     S = torch.empty(32768, dtype=torch.float32, device=dev)
+    more = [(torch.empty_like(R).uniform_(0.0, 1.0), torch.empty_like(S)) for _ in range(2)]
     hbm_entry("reduce_rows_32768x8192", "reduce_rows", R.numel() * 4 + S.numel() * 4,
               sess.kernel(B.reduce_rows("reduce", 32768, 8192)), [R.data_ptr(), S.data_ptr()],
-              "config 4a")
-    del R, S
+              "config 4a", ptr_sets=[[a.data_ptr(), b.data_ptr()] for a, b in more])
+    del R, S, more
     # config 4b: transpose 8192 x 8192
     T = torch.empty((8192, 8192), dtype=torch.float32, device=dev).uniform_(-1.0, 1.0)
     U = torch.empty_like(T)
+    more = [(torch.empty_like(T).uniform_(-1.0, 1.0), torch.empty_like(U)) for _ in range(3)]
     hbm_entry("transpose_8192x8192", "transpose2d", 2 * T.numel() * 4,
               sess.kernel(B.transpose2d("transpose", 8192, 8192)), [T.data_ptr(), U.data_ptr()],
-              "config 4b")
-    del T, U
+              "config 4b", ptr_sets=[[a.data_ptr(), b.data_ptr()] for a, b in more], tensor_pairs=more)
+    del T, U, more
     # the reference's fusion benchmark chain (log, absf, addf, subf: kLoopFusion), scaled up to
     # 8192 x 8192 so that it streams from HBM; its own 512 x 1024 shape moves 6 MiB
     for tag, tdt, bdt, esz in (("f32", torch.float32, B.F32, 4), ("f16", torch.float16, B.F16, 2),
