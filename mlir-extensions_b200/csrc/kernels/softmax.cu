@@ -12,6 +12,7 @@
 // `sum` differs from the sequential loop (per-lane partial sums + shuffle
 // tree), which is where the <= 1e-5 relative tolerance goes.
 #include "kernels.h"
+#include "epilogue.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -30,28 +31,6 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
-}
-
-// exp(t) for t <= 0 in a handful of instructions: 2^(t*log2e) through the
-// hardware ex2 unit, with the rounding error of the product t*log2e (which
-// alone would cost 1.5e-6 relative at t = -26) fed back as a first-order
-// correction.  y + r is t*log2e to ~2^-48 relative (log2e split in hi + lo, the
-// product's residual recovered with an FMA); ex2.approx is good to 2 ulp, so the
-// result is within ~3e-7 of libm's expf, which the CPU pipeline calls
-// (convert-math-to-libm).  libm's expf costs ~25 instructions per element and,
-// with every warp of the single wave in the same phase, was a third of the
-// 4096x1024 kernel's time.  NaN and -inf pass through (ex2(-inf) = 0).
-__device__ __forceinline__ float exp_neg(float t) {
-  const float L2E_HI = 1.44269502162933349609375f;   // float(log2(e))
-  const float L2E_LO = 1.92596299112661746e-8f;      // log2(e) - L2E_HI
-  const float LN2 = 0.693147182464599609375f;
-  const float y = __fmul_rn(t, L2E_HI);
-  float r = __fmaf_rn(t, L2E_HI, -y);                // exact residual of the product
-  r = __fmaf_rn(t, L2E_LO, r);
-  float e;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(y));
-  // 2^(y + r) = 2^y * (1 + r ln2 + ...);  |r| < 2^-18, the next term is below 2^-38
-  return isfinite(r) ? __fmaf_rn(e, __fmul_rn(r, LN2), e) : e;
 }
 
 // fmaxf drops NaNs where arith.maximumf keeps them; a NaN element still turns
