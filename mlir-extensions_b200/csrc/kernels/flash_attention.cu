@@ -163,7 +163,7 @@ template <> __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uin
 
 // P goes from the softmax threads' registers into TMEM (tcgen05.st) and the second MMA takes its
 // A operand from there; O accumulates in TMEM.
-template <int SPLIT, bool STATS>
+template <int SPLIT, bool STATS, bool BF16>
 __global__ void __launch_bounds__(num_threads(SPLIT), 1)
 flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -388,10 +388,12 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     };
     // P values of keys [8 * q0, 8 * q1) of block j from the scores: p = 2^(s' - m), rounded
     // to 16 bits, two per word; their f32 sum goes into sum2 (two partial sums side by side).
-    auto exp_keys = [&](const uint32_t (&sc)[HC], uint32_t (&pw)[HC / 2], int q0, int q1, int j, float neg_m,
-                        uint64_t &sum2) __attribute__((always_inline)) {
+    // `plain` (a literal at every call, folded when the lambda is inlined: the choice is made once
+    // per block, outside) says that all 32 keys exist, so nothing is masked and the whole half
+    // is one straight line of code.
+    auto exp_keys = [&](const bool plain, const uint32_t (&sc)[HC], uint32_t (&pw)[HC / 2], int q0, int q1, int j,
+                        float neg_m, uint64_t &sum2) __attribute__((always_inline)) {
       const int valid = valid_keys(j);
-      const bool plain = valid >= HC && p.scale_log2e > 0.0f;
       const uint64_t scale2 = pack_f32x2(p.scale_log2e, p.scale_log2e);
       const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
 #pragma unroll
@@ -411,7 +413,7 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           sum2 = add_f32x2(sum2, pack_f32x2(e[2 * i], e[2 * i + 1]));
-          pw[4 * q + i] = pack2(e[2 * i], e[2 * i + 1], p.is_bf16);
+          pw[4 * q + i] = pack2(e[2 * i], e[2 * i + 1], BF16);
         }
       }
     };
@@ -448,7 +450,9 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       uint64_t sum2 = 0ull;
       const float neg_m = -m;
       const uint32_t p_addr = t_row + P_COL + b * (BKV / 2) + part * (HC / 2);
-      exp_keys(cur, pw, 0, HC / 16, j, neg_m, sum2);            // first half of the exponentials
+      const bool plain = valid_keys(j) >= HC;
+      if (plain) exp_keys(true, cur, pw, 0, HC / 16, j, neg_m, sum2);   // first half of the exponentials
+      else exp_keys(false, cur, pw, 0, HC / 16, j, neg_m, sum2);
       tick(0);
       if (j >= 2) {
         // P buffer b was read by PV_{j-2}: finished long ago, but the order must be seen
@@ -469,7 +473,8 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         tmem_ld_cols<HC>(t_row + (b ^ 1) * BKV + part * HC, nxt);   // lands while the second half runs
       }
       tick(1);
-      exp_keys(cur, pw, HC / 16, HC / 8, j, neg_m, sum2);       // second half
+      if (plain) exp_keys(true, cur, pw, HC / 16, HC / 8, j, neg_m, sum2);   // second half
+      else exp_keys(false, cur, pw, HC / 16, HC / 8, j, neg_m, sum2);
       tick(2);
       tmem_st_8cols(p_addr + 8, pw + 8);
       if (have_next) tmem_ld_wait();
@@ -555,8 +560,8 @@ flash_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         uint16_t *orow = static_cast<uint16_t *>(p.O) + static_cast<size_t>(head_row0 + q0 + r) * DH + part * HO;
 #pragma unroll
         for (int c = 0; c < HO; c += 8) {
-          const uint4 out = make_uint4(pack2(o[c], o[c + 1], p.is_bf16), pack2(o[c + 2], o[c + 3], p.is_bf16),
-                                       pack2(o[c + 4], o[c + 5], p.is_bf16), pack2(o[c + 6], o[c + 7], p.is_bf16));
+          const uint4 out = make_uint4(pack2(o[c], o[c + 1], BF16), pack2(o[c + 2], o[c + 3], BF16),
+                                       pack2(o[c + 4], o[c + 5], BF16), pack2(o[c + 6], o[c + 7], BF16));
           *reinterpret_cast<uint4 *>(orow + c) = out;
         }
       }
@@ -592,11 +597,15 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
   static cudaError_t attr_err = cudaSuccess;
   static bool with_stats = false;
   using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-  static const Kernel kernels[2] = {flash_attention_fwd_kernel<4, false>, flash_attention_fwd_kernel<4, true>};
+  // [stats][bf16]
+  static const Kernel kernels[2][2] = {
+      {flash_attention_fwd_kernel<4, false, false>, flash_attention_fwd_kernel<4, false, true>},
+      {flash_attention_fwd_kernel<4, true, false>, flash_attention_fwd_kernel<4, true, true>}};
   std::call_once(once, [] {
     with_stats = getenv("IMEX_ATTN_STATS") != nullptr;  // development aid: where the roles wait
-    for (int i = 0; i < 2; ++i) {
-      cudaError_t x = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    for (int i = 0; i < 4; ++i) {
+      cudaError_t x = cudaFuncSetAttribute(kernels[i >> 1][i & 1], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_BYTES);
       if (x != cudaSuccess) attr_err = x;
     }
   });
@@ -629,7 +638,7 @@ cudaError_t launch_flash_attention_fwd(const void *q, const void *k, const void 
     if (!stats_buf) cudaMallocManaged(&stats_buf, 24 * 4096 * sizeof(long long));
     p.stats = stats_buf;
   }
-  kernels[p.stats ? 1 : 0]<<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  kernels[p.stats ? 1 : 0][dtype == kBF16 ? 1 : 0]<<<grid, num_threads(4), SMEM_BYTES, stream>>>(tq, tk, tv, p);
   if (p.stats) {
     cudaStreamSynchronize(stream);
     double a[24] = {0};
