@@ -485,6 +485,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // parts added in order).  One block per 8 rows of a split tile.
 __global__ void __launch_bounds__(256)
 gemm_splitk_fixup_kernel(const PairParams p) {
+  // launched with programmatic stream serialisation: its blocks are set up while the GEMM's last
+  // CTAs drain; nothing is read before the GEMM has completed and its writes are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int t = blockIdx.x / (PAIR_M / 8);          // which split tile
   const int strip = blockIdx.x % (PAIR_M / 8);      // which 8 rows of it
   int mb, nb;
@@ -683,7 +686,17 @@ cudaError_t launch_gemm_tcgen05_2cta(const GemmProblem &g, unsigned *status, cud
   if (p.split_tiles) {
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return le;
-    gemm_splitk_fixup_kernel<<<p.split_tiles * (PAIR_M / 8), 256, 0, stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.split_tiles * (PAIR_M / 8));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    le = cudaLaunchKernelEx(&cfg, gemm_splitk_fixup_kernel, p);
+    if (le != cudaSuccess) return le;
   }
   if (g.launched) *g.launched = p.split_tiles ? 2 : 1;
   if (want_stats && stats_buf) {
