@@ -89,7 +89,9 @@ def check_rows(text):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("IMEX_REFERENCE_DIR"),
+                    required="IMEX_REFERENCE_DIR" not in os.environ,
+                    help="checkout of intel/mlir-extensions (default: $IMEX_REFERENCE_DIR)")
     ap.add_argument("--out", default=os.path.join(HERE, "reference_vectors.json"))
     args = ap.parse_args()
 
