@@ -889,7 +889,26 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
         "roofline": {"bound": "tensor", "achieved": aflops / (med * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": aflops / (med * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None},
         "note": "the reference's flash-attention test shape; 128 CTAs of 128 query rows, 17 GFLOP in all"}
-    del Q, Kt, Vt, Ot
+
+    def tensor_graph_timing(name, kernel, ptr_sets, flops, what):
+        """The launch duration proper of a 40-100 us kernel: launches on distinct buffer sets
+        (together larger than L2) replayed as one CUDA graph; an event pair around one launch
+        adds 5-10 us.  The flushed single-launch figure stays in ms_cold_median."""
+        try:
+            b2b, b2b_min = graph_back_to_back(torch, stream, sess, kernel, ptr_sets)
+        except Exception as e:  # noqa: BLE001 - reported, the flushed figure stays
+            out[name]["graph_timing_error"] = repr(e)[:200]
+            return
+        ach = flops / (b2b * 1e-3) / 1e12
+        out[name].update(ms_back_to_back=b2b, ms_back_to_back_min=b2b_min, roofline_ms=b2b,
+                         tflops_flushed_single_launch=out[name]["value"], value=ach)
+        out[name]["roofline"].update(achieved=ach, frac=ach / peaks["bf16_tflops"], timing=what)
+
+    asets = [[(torch.rand((heads * n_ctx, 64), device=dev) * 2 - 1).to(torch.float16) for _ in range(3)]
+             + [torch.empty_like(Q)] for _ in range(32)]
+    tensor_graph_timing("attention_fwd_4x4096x64", ak, [[t.data_ptr() for t in ts] for ts in asets], aflops,
+                        "32 launches on 32 distinct sets of Q, K, V, O (256 MiB in all) replayed as one CUDA graph")
+    del Q, Kt, Vt, Ot, asets
     # config 3: GEMM 4096^3 + relu
     n = 4096
     A = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
@@ -911,6 +930,16 @@ def bench_kernels(torch, pkg, sess, dev, peaks, stream, iters=30):
                      "peak_source": peaks["source"] + " (cuBLAS bf16 burst)",
                      "frac_of_nominal_2250": ach / 2250.0},
         "note": "config 3"}
+    gsets = []
+    for i in range(2):   # with the first set: 3 x (32 + 32 + 64 MiB), larger than L2
+        a2, b2 = torch.empty_like(A), torch.empty_like(Bm)
+        sess.run(B.fill_uniform("cfg3_a%d" % i, n * n, B.BF16, 13 + 2 * i, -1.0, 1.0), [a2.data_ptr()])
+        sess.run(B.fill_uniform("cfg3_b%d" % i, n * n, B.BF16, 14 + 2 * i, -1.0, 1.0), [b2.data_ptr()])
+        gsets.append((a2, b2, torch.empty_like(Cm)))
+    gsets.append((A, Bm, Cm))
+    tensor_graph_timing("gemm_4096_relu", k, [[t.data_ptr() for t in ts] for ts in gsets], fl,
+                        "3 launches on 3 distinct sets of A, B, C (384 MiB in all) replayed as one CUDA graph")
+    out["gemm_4096_relu"]["roofline"]["frac_of_nominal_2250"] = out["gemm_4096_relu"]["value"] / 2250.0
     return out
 
 
