@@ -125,3 +125,37 @@ def test_launch_events_come_from_a_ring_and_stay_usable(pkg):
         s.launch(relu, [dy, dz], wait=False, deps=[events[-1]])
         s.wait()
         assert np.array_equal(s.download(dz, X.shape, np.float32), oracle.relu(X))
+
+
+def test_launches_captured_into_a_cuda_graph_replay_with_the_same_results(pkg):
+    """gpuLaunchKernel on a stream that is being captured: the launches become graph nodes (no
+    event record between them; the softmax of a few rows per SM is launched with programmatic
+    stream serialisation, the second launch reads what the first wrote), and a replay gives the
+    bits of the direct launches.  A handle returned under capture may be passed as a dependency
+    on the same stream."""
+    import torch
+    B = pkg.blob
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    sess = pkg.Session(device=0, adopt_stream=stream.cuda_stream)
+    x = torch.empty((4096, 1024), dtype=torch.float32, device=dev).normal_(0.0, 3.0)
+    y1, y2 = torch.empty_like(x), torch.empty_like(x)
+    k = sess.kernel(B.softmax("sm", 4096, 1024))
+    sess.launch(k, [x.data_ptr(), y1.data_ptr()], wait=False)   # everything lazy happens before the capture
+    sess.launch(k, [y1.data_ptr(), y2.data_ptr()], wait=True)
+    want1, want2 = y1.clone(), y2.clone()
+    y1.zero_()
+    y2.zero_()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        first = sess.launch(k, [x.data_ptr(), y1.data_ptr()], wait=False)
+        sess.launch(k, [y1.data_ptr(), y2.data_ptr()], wait=False, deps=(first,))
+    assert float(y2.abs().sum()) == 0.0          # captured, not run
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y1, want1) and torch.equal(y2, want2)
+    torch.cuda.set_stream(torch.cuda.default_stream(dev))
+    sess.close()
