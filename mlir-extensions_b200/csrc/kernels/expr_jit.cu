@@ -37,6 +37,16 @@ __device__ __forceinline__ u16 f2b(float f) { u16 h; asm("cvt.rn.bf16.f32 %0, %1
 __device__ __forceinline__ float maximumf(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
 __device__ __forceinline__ float minimumf(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 __device__ __forceinline__ float relu_ugt(float x) { return !(x <= 0.0f) ? x : 0.0f; }
+// exp for results that are rounded to 16 bits: 2^(t log2 e) on the hardware unit with the rounding
+// error of the product fed back (within 3e-7 of libm's expf, a thousandth of a 16-bit half-ulp)
+__device__ __forceinline__ float exp_c(float t) {
+  const float y = __fmul_rn(t, 1.44269502162933349609375f);
+  float r = __fmaf_rn(t, 1.44269502162933349609375f, -y);
+  r = __fmaf_rn(t, 1.92596299112661746e-8f, r);
+  float e;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(y));
+  return isfinite(r) ? __fmaf_rn(e, __fmul_rn(r, 0.693147182464599609375f), e) : e;
+}
 // two 16-bit values in one register (element 0 in the low half)
 __device__ __forceinline__ unsigned pack_h(float lo, float hi) { unsigned d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
 __device__ __forceinline__ unsigned pack_b(float lo, float hi) { unsigned d; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
@@ -145,7 +155,7 @@ std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, st
       auto f = [&](const std::string &x) -> std::string {
         switch (op) {
         case 34: return "logf(" + x + ")";
-        case 35: return "expf(" + x + ")";
+        case 35: return "exp_c(" + x + ")";
         case 36: return "__fsqrt_rn(" + x + ")";
         case 37: return "__fdiv_rn(1.0f, __fsqrt_rn(" + x + "))";
         case 38: return "tanhf(" + x + ")";
@@ -297,13 +307,13 @@ std::string generate(const unsigned char *code, int ncode, int n_inputs, int dty
        << "  y[col] = " << out.store << "(acc);\n}\n";
     return os.str();
   }
-  // elementwise: `vec` consecutive columns of one row per thread and group.  In f32 a thread
-  // loads the inputs of four groups before it computes the first: with one group in flight
-  // per thread a chain with transcendental functions keeps a warp too long between its loads
-  // to saturate HBM.  The 16-bit chains are bound by instruction issue (8 values per 16
-  // bytes): there the extra registers only cost occupancy (measured 4795 -> 4468 GB/s), so
-  // they keep one group.
-  const int U = dtype == kF32 ? 4 : 1;
+  // elementwise: `vec` consecutive columns of one row per thread and group.  A thread loads the
+  // inputs of several groups before it computes the first: with one group in flight per thread a
+  // chain with transcendental functions keeps a warp too long between its loads to saturate
+  // HBM.  Four groups in f32; two in the 16-bit types, whose chains are bound by instruction
+  // issue (8 values per 16 bytes) and lose occupancy to the extra registers (measured on the
+  // log chain: 4739 / 4911 / 4574 GB/s with 1 / 2 / 4 groups).
+  const int U = dtype == kF32 ? 4 : 2;
   const int in_bytes = dtype == kF32 ? 4 : 2, out_bytes = (out_dtype == kF32 ? 4 : 2);
   os << "  const long long groups_per_row = cols / " << vec << ", total = rows * groups_per_row;\n"
      << "  const long long stride = (long long)gridDim.x * blockDim.x;\n"
