@@ -407,11 +407,20 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
   std::vector<int> par, red;
   for (int d = 0; d < nd; ++d) (op.iterators[d] == "reduction" ? red : par).push_back(d);
   // outputs: indexed by parallel dimensions only, and by all of them
+  // (a dimension moved by a constant, d0 + 2, still addresses every element at most once: the
+  // part of the output the iteration space does not reach keeps its initial value,
+  // test/PlaidML/OpTest.ExplicitPadding.mlir:29-40)
+  std::vector<bool> partial(nOut, false);
   for (size_t k = nIn; k < nIn + nOut; ++k) {
     std::set<int> used;
     for (auto &mr : op.maps[k].results) {
-      if (!mr.simple) { why = "output indexed by a compound expression"; return false; }
-      if (!mr.isConst) used.insert(static_cast<int>(mr.value));
+      if (!mr.simple && mr.shiftDim < 0) { why = "output indexed by a compound expression"; return false; }
+      if (!mr.simple) {
+        used.insert(mr.shiftDim);
+        partial[k - nIn] = true;
+      } else if (!mr.isConst) {
+        used.insert(static_cast<int>(mr.value));
+      }
     }
     for (int d : red)
       if (used.count(d)) { why = "output indexed by a reduction dimension"; return false; }
@@ -443,7 +452,8 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
   for (auto &o : op.body->ops)
     for (auto &v : o->operands) usedNames.insert(v);
   out.readsInit.assign(nOut, false);
-  for (size_t k = 0; k < nOut; ++k) out.readsInit[k] = !red.empty() || usedNames.count(op.body->args[nIn + k]) != 0;
+  for (size_t k = 0; k < nOut; ++k)
+    out.readsInit[k] = !red.empty() || partial[k] || usedNames.count(op.body->args[nIn + k]) != 0;
 
   std::ostringstream os;
   os << "extern \"C\" __global__ void imex_loopnest(";
@@ -537,6 +547,45 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
   std::ostringstream sum;
   sum << "loopnest[" << par.size() << " parallel, " << red.size() << " reduction dims, " << out.threads << " threads]";
   out.summary = sum.str();
+  return true;
+}
+
+bool buildPad(const Type &src, const Type &dst, const std::vector<int64_t> &low, double value,
+              LoopNestKernel &out, std::string &why) {
+  const size_t rank = dst.shape.size();
+  if (!src.isShaped() || !dst.isShaped() || src.shape.size() != rank || low.size() != rank || src.elt != dst.elt) {
+    why = "tensor.pad between arrays of different rank or element type";
+    return false;
+  }
+  if (!storageType(dst.elt)) {
+    why = "element type " + dst.elt + " has no C counterpart";
+    return false;
+  }
+  int64_t n = 1;
+  for (size_t d = 0; d < rank; ++d) {
+    if (dst.shape[d] < 0 || src.shape[d] < 0) { why = "dynamic shape"; return false; }
+    n *= dst.shape[d];
+  }
+  out.threads = n;
+  out.pointerInputs = {0};
+  out.readsInit = {false};
+  std::ostringstream os;
+  const char *st = storageType(dst.elt);
+  os << "extern \"C\" __global__ void imex_loopnest(const " << st << " *__restrict__ in0, " << st
+     << " *__restrict__ out0) {\n"
+     << "  const i64 p = IMX_THREAD_INDEX;\n"
+     << "  if (p >= " << n << "LL) return;\n"
+     << "  i64 q = p, s = 0, stride = 1;\n"
+     << "  bool inside = true;\n";
+  // innermost dimension first: position in the source = position in the result - low
+  for (int d = static_cast<int>(rank) - 1; d >= 0; --d) {
+    os << "  {\n    const i64 c = q % " << dst.shape[d] << "LL - " << low[d] << "LL;\n    q /= " << dst.shape[d] << "LL;\n"
+       << "    inside = inside && c >= 0 && c < " << src.shape[d] << "LL;\n"
+       << "    s += c * stride;\n    stride *= " << src.shape[d] << "LL;\n  }\n";
+  }
+  os << "  out0[p] = inside ? in0[s] : " << storeExpr(dst.elt, literal(dst.elt, value)) << ";\n}\n";
+  out.source = os.str();
+  out.summary = "pad[" + std::to_string(n) + " threads]";
   return true;
 }
 

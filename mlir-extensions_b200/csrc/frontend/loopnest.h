@@ -40,5 +40,11 @@ struct LoopNestKernel {
 bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel &out, std::string &why,
                    const std::vector<Type> *types = nullptr);
 
+// tensor.pad with static amounts and a constant padding value (test/PlaidML/CppEdsl.Convolution.mlir:26-29):
+// one thread per element of the result, which is the source element at (position - low) or
+// the padding value outside the source.
+bool buildPad(const Type &src, const Type &dst, const std::vector<int64_t> &low, double value, LoopNestKernel &out,
+              std::string &why);
+
 } // namespace fe
 } // namespace imex

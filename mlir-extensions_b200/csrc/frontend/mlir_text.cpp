@@ -418,6 +418,8 @@ private:
         } else {
           r.simple = false;
           r.value = -1;
+          r.shiftDim = t.shiftDim;
+          r.shift = t.shift;
         }
         m.results.push_back(r);
       } while (accept(','));
@@ -432,6 +434,8 @@ private:
     enum { Const, Dim, Other } kind = Other;
     int64_t value = 0;
     std::string text;
+    int shiftDim = -1;   // Other of the form dim + constant
+    int64_t shift = 0;
   };
   AffineTerm affineAtom(const std::vector<std::string> &dims) {
     skip();
@@ -499,6 +503,13 @@ private:
       AffineTerm b = affineProduct(dims);
       AffineTerm r;
       r.text = "(" + a.text + " " + op + " " + b.text + ")";
+      if (a.kind == AffineTerm::Dim && b.kind == AffineTerm::Const) {
+        r.shiftDim = static_cast<int>(a.value);
+        r.shift = op == '+' ? b.value : -b.value;
+      } else if (a.kind == AffineTerm::Const && b.kind == AffineTerm::Dim && op == '+') {
+        r.shiftDim = static_cast<int>(b.value);
+        r.shift = a.value;
+      }
       a = r;
     }
     return a;
@@ -815,7 +826,7 @@ private:
         pos += 2;
         op->resultTypes = typeList();
       }
-    } else if (n == "linalg.yield" || n == "scf.yield" || n == "return" || n == "func.return") {
+    } else if (n == "linalg.yield" || n == "scf.yield" || n == "tensor.yield" || n == "return" || n == "func.return") {
       operandList(op->operands);
       if (accept(':')) {
         do {
@@ -881,6 +892,33 @@ private:
     } else if (n == "tensor.from_elements") {
       operandList(op->operands);
       expect(':');
+      op->resultTypes.push_back(type());
+    } else if (n == "tensor.pad") {
+      // %r = tensor.pad %x low[0, 1, 1, 0] high[0, 1, 1, 0] { ^bb0(%i: index, ...): tensor.yield %c : f32 }
+      //        : tensor<..> to tensor<..>      (static amounts only)
+      operandList(op->operands);
+      acceptWord("nofold");
+      for (const char *word : {"low", "high"}) {
+        expectWord(word);
+        expect('[');
+        std::vector<int64_t> amounts;
+        skip();
+        if (peek() != ']') {
+          do {
+            skip();
+            if (peek() == '%') fail("tensor.pad with dynamic amounts is outside the supported subset");
+            amounts.push_back(static_cast<int64_t>(number().value));
+          } while (accept(','));
+        }
+        expect(']');
+        op->reassociation.push_back(amounts);
+      }
+      expect('{');
+      op->body = std::make_unique<Block>();
+      block(*op->body, /*allowLabel=*/true);
+      expect(':');
+      op->operandTypes.push_back(type());
+      expectWord("to");
       op->resultTypes.push_back(type());
     } else if (n == "tensor.expand_shape" || n == "tensor.collapse_shape") {
       operandList(op->operands);

@@ -44,6 +44,8 @@ struct MapResult {
   int64_t value = 0;     // dimension index or the constant; -1 when not simple
   bool simple = true;
   std::string expr;      // C expression over d0.. (always set)
+  int shiftDim = -1;     // "d<shiftDim> + shift" (a dimension moved by a constant): not simple,
+  int64_t shift = 0;     // but still one-to-one
 };
 struct AffineMap {
   int numDims = 0;

@@ -735,6 +735,43 @@ private:
     for (size_t r = 0; r < op.results.size() && r < outs.size(); ++r) fr.vals[op.results[r]] = outs[r];
   }
 
+  // tensor.pad with static amounts and a constant padding value: one launch of a loop-nest kernel.
+  void padOp(const Op &op, Frame &fr, void *stream) {
+    const std::string where = "line " + std::to_string(op.line) + ": ";
+    // the region yields the padding value: a constant of the enclosing function or of the region
+    double value = 0.0;
+    bool known = false;
+    if (op.body && !op.body->ops.empty()) {
+      std::map<std::string, double> local;
+      for (auto &o : op.body->ops) {
+        if (o->name == "arith.constant" && !o->numbers.empty() && !o->results.empty()) local[o->results[0]] = o->numbers[0];
+        if (o->name == "tensor.yield" && o->operands.size() == 1) {
+          auto it = local.find(o->operands[0]);
+          if (it != local.end()) { value = it->second; known = true; }
+          auto jt = fr.constants.find(o->operands[0]);
+          if (!known && jt != fr.constants.end()) { value = jt->second; known = true; }
+        }
+      }
+    }
+    if (!known) die(where + "tensor.pad whose padding value is not a constant is not supported");
+    if (op.reassociation.size() != 2) die(where + "tensor.pad without low / high amounts");
+    Value &src = get(fr, op.operands[0], op);
+    if (src.kind != Value::Tensor) die(where + "tensor.pad of a scalar");
+    LoopNestKernel k;
+    std::string why;
+    if (!buildPad(src.type, op.resultTypes[0], op.reassociation[0], value, k, why)) die(where + "tensor.pad: " + why);
+    for (size_t d = 0; d < op.reassociation[1].size(); ++d)
+      if (src.type.shape[d] + op.reassociation[0][d] + op.reassociation[1][d] != op.resultTypes[0].shape[d])
+        die(where + "tensor.pad: low + extent + high differs from the result's extent");
+    Value out = makeTensorExact(stream, op.resultTypes[0], false);
+    std::vector<void *> ptrs = {src.buf->ptr, out.buf->ptr};
+    ImexKernelDesc d = desc(IMEX_OP_LOOPNEST, 0, 0);
+    d.dims[0] = k.threads;
+    d.dims[3] = 2;
+    launch(stream, d, ptrs, k.summary, k.source);
+    fr.vals[op.results[0]] = out;
+  }
+
   // How often `v` is used by the top-level ops of `b`; fusions that make `v` disappear are
   // only sound when these are ALL its uses (none hidden inside a nested loop body).
   static int visibleUses(const std::string &v, const Block &b) {
@@ -830,6 +867,8 @@ private:
         Value v = get(fr, op.operands[0], op);  // contiguous: only the shape changes
         v.type = op.resultTypes[0];
         fr.vals[op.results[0]] = v;
+      } else if (n == "tensor.pad") {
+        padOp(op, fr, stream);
       } else if (n == "tensor.extract") {
         Value &t = get(fr, op.operands[0], op);
         if (t.type.count() != 1) die("line " + std::to_string(op.line) + ": tensor.extract of a non-scalar tensor");
