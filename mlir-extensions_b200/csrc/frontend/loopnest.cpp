@@ -589,5 +589,50 @@ bool buildPad(const Type &src, const Type &dst, const std::vector<int64_t> &low,
   return true;
 }
 
+bool buildSlice(const Type &src, const Type &dst, const std::vector<int64_t> &offsets,
+                const std::vector<int64_t> &sizes, const std::vector<int64_t> &strides, LoopNestKernel &out,
+                std::string &why) {
+  const size_t rank = src.shape.size();
+  if (!src.isShaped() || !dst.isShaped() || offsets.size() != rank || sizes.size() != rank || strides.size() != rank ||
+      src.elt != dst.elt) {
+    why = "tensor.extract_slice whose lists do not match the source";
+    return false;
+  }
+  if (!storageType(dst.elt)) {
+    why = "element type " + dst.elt + " has no C counterpart";
+    return false;
+  }
+  int64_t n = 1;
+  for (size_t d = 0; d < rank; ++d) {
+    if (src.shape[d] < 0 || sizes[d] <= 0 || offsets[d] < 0 || strides[d] <= 0 ||
+        offsets[d] + (sizes[d] - 1) * strides[d] >= src.shape[d]) {
+      why = "tensor.extract_slice outside its source";
+      return false;
+    }
+    n *= sizes[d];
+  }
+  if (dst.count() != n) {
+    why = "tensor.extract_slice whose result does not hold sizes-many elements";
+    return false;
+  }
+  out.threads = n;
+  out.pointerInputs = {0};
+  out.readsInit = {false};
+  std::ostringstream os;
+  const char *st = storageType(dst.elt);
+  os << "extern \"C\" __global__ void imex_loopnest(const " << st << " *__restrict__ in0, " << st
+     << " *__restrict__ out0) {\n"
+     << "  const i64 p = IMX_THREAD_INDEX;\n"
+     << "  if (p >= " << n << "LL) return;\n"
+     << "  i64 q = p, s = 0, stride = 1;\n";
+  for (int d = static_cast<int>(rank) - 1; d >= 0; --d)
+    os << "  s += (" << offsets[d] << "LL + (q % " << sizes[d] << "LL) * " << strides[d] << "LL) * stride; q /= " << sizes[d]
+       << "LL; stride *= " << src.shape[d] << "LL;\n";
+  os << "  out0[p] = in0[s];\n}\n";
+  out.source = os.str();
+  out.summary = "slice[" + std::to_string(n) + " threads]";
+  return true;
+}
+
 } // namespace fe
 } // namespace imex

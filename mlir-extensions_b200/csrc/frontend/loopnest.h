@@ -46,5 +46,10 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
 bool buildPad(const Type &src, const Type &dst, const std::vector<int64_t> &low, double value, LoopNestKernel &out,
               std::string &why);
 
+// tensor.extract_slice with static offsets, sizes and strides
+// (test/Jax/janet/jit__get_age_weights_from_tables.8_linalg.mlir:60): one thread per element of the result.
+bool buildSlice(const Type &src, const Type &dst, const std::vector<int64_t> &offsets, const std::vector<int64_t> &sizes,
+                const std::vector<int64_t> &strides, LoopNestKernel &out, std::string &why);
+
 } // namespace fe
 } // namespace imex

@@ -787,7 +787,17 @@ private:
       if (startsWith("dense")) {
         denseAttr(*op);
       } else {
+        skip();
+        const bool boolean = startsWith("true") || startsWith("false");
         pushNumber(*op, number());
+        skip();
+        if (boolean && peek() != ':') {   // "arith.constant true": the type i1 goes without saying
+          Type t;
+          t.kind = Type::Scalar;
+          t.elt = "i1";
+          op->resultTypes.push_back(t);
+          return op;
+        }
       }
       expect(':');
       op->resultTypes.push_back(type());
@@ -892,6 +902,28 @@ private:
     } else if (n == "tensor.from_elements") {
       operandList(op->operands);
       expect(':');
+      op->resultTypes.push_back(type());
+    } else if (n == "tensor.extract_slice") {
+      // %r = tensor.extract_slice %x[49999] [1] [1] : tensor<50000xf32> to tensor<1xf32>
+      //      (offsets, sizes, strides; static only; the result may drop unit dimensions)
+      operandList(op->operands);
+      for (int list = 0; list < 3; ++list) {
+        expect('[');
+        std::vector<int64_t> v;
+        skip();
+        if (peek() != ']') {
+          do {
+            skip();
+            if (peek() == '%') fail("tensor.extract_slice with dynamic offsets, sizes or strides is outside the supported subset");
+            v.push_back(static_cast<int64_t>(number().value));
+          } while (accept(','));
+        }
+        expect(']');
+        op->reassociation.push_back(v);
+      }
+      expect(':');
+      op->operandTypes.push_back(type());
+      expectWord("to");
       op->resultTypes.push_back(type());
     } else if (n == "tensor.pad") {
       // %r = tensor.pad %x low[0, 1, 1, 0] high[0, 1, 1, 0] { ^bb0(%i: index, ...): tensor.yield %c : f32 }

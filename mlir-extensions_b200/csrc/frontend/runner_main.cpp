@@ -869,6 +869,21 @@ private:
         fr.vals[op.results[0]] = v;
       } else if (n == "tensor.pad") {
         padOp(op, fr, stream);
+      } else if (n == "tensor.extract_slice") {
+        const std::string where = "line " + std::to_string(op.line) + ": ";
+        Value &src = get(fr, op.operands[0], op);
+        if (src.kind != Value::Tensor || op.reassociation.size() != 3) die(where + "tensor.extract_slice of a scalar");
+        LoopNestKernel k;
+        std::string why;
+        if (!buildSlice(src.type, op.resultTypes[0], op.reassociation[0], op.reassociation[1], op.reassociation[2], k, why))
+          die(where + why);
+        Value out = makeTensorExact(stream, op.resultTypes[0], false);
+        std::vector<void *> ptrs = {src.buf->ptr, out.buf->ptr};
+        ImexKernelDesc d = desc(IMEX_OP_LOOPNEST, 0, 0);
+        d.dims[0] = k.threads;
+        d.dims[3] = 2;
+        launch(stream, d, ptrs, k.summary, k.source);
+        fr.vals[op.results[0]] = out;
       } else if (n == "tensor.extract") {
         Value &t = get(fr, op.operands[0], op);
         if (t.type.count() != 1) die("line " + std::to_string(op.line) + ": tensor.extract of a non-scalar tensor");

@@ -55,6 +55,26 @@ HOT_PATH = [
     "test/PlaidML/OpTest.ExplicitPadding.mlir", "test/PlaidML/OpTest.ExplicitPaddingInf.mlir",
     "test/Jax/qoc/jit__diag.11_linalg.mlir",
 ]
+# the rest of the two folders that the loop-nest lowering carries: bit operations, logical operations
+# on mixed types, layers, dilated convolution, integer GEMVs, gathers (tensor.extract in a body), ...
+OTHER_PROGRAMS = [
+    "test/Jax/gordon/jit__logsm_from_logmhalo_jax_kern_0_before_linalg.mlir",
+    "test/Jax/janet/jit__get_met_weights_singlegal.43_linalg.mlir", "test/Jax/jax_qmc/jit_pionless_2b_lo.41_linalg.mlir",
+    "test/PlaidML/CppEdsl.BitAnd.mlir", "test/PlaidML/CppEdsl.BitAndScalar.mlir", "test/PlaidML/CppEdsl.BitLeft.mlir",
+    "test/PlaidML/CppEdsl.BitNot.mlir", "test/PlaidML/CppEdsl.BitOr.mlir", "test/PlaidML/CppEdsl.BitRightScalar.mlir",
+    "test/PlaidML/CppEdsl.BitRightTensor.mlir", "test/PlaidML/CppEdsl.BitXor.mlir", "test/PlaidML/CppEdsl.BroadcastCmp.mlir",
+    "test/PlaidML/CppEdsl.ConstAdd.mlir", "test/PlaidML/CppEdsl.DupOut.mlir", "test/PlaidML/CppEdsl.EltwiseMod.mlir",
+    "test/PlaidML/OpTest.Conv2DDilated.mlir", "test/PlaidML/OpTest.GEMV_INT64.mlir", "test/PlaidML/OpTest.GEMV_INT8.mlir",
+    "test/PlaidML/OpTest.GEMV_UINT64.mlir", "test/PlaidML/OpTest.HigherPrecisioConstants.mlir",
+    "test/PlaidML/OpTest.LarsMomentum4d.mlir", "test/PlaidML/OpTest.LayerEmbeddedConst.mlir",
+    "test/PlaidML/OpTest.LayerException.mlir", "test/PlaidML/OpTest.LayerMulti.mlir",
+    "test/PlaidML/OpTest.LayerOperandOrder.mlir", "test/PlaidML/OpTest.LayerUnusedOperand.mlir", "test/PlaidML/OpTest.Lens.mlir",
+    "test/PlaidML/OpTest.LogicalAnd_mixed.mlir", "test/PlaidML/OpTest.LogicalAnd_uint64.mlir",
+    "test/PlaidML/OpTest.LogicalNot_float.mlir", "test/PlaidML/OpTest.LogicalNot_int32.mlir",
+    "test/PlaidML/OpTest.LogicalOr_float.mlir", "test/PlaidML/OpTest.LogicalOr_int32.mlir",
+    "test/PlaidML/OpTest.LogicalOr_uint64.mlir", "test/PlaidML/OpTest.ReshapeIntoScalar.mlir", "test/PlaidML/OpTest.Shape.mlir",
+    "test/PlaidML/OpTest.Tan.mlir", "test/PlaidML/OpTest.UniqueNames.mlir",
+]
 # 2048^3 on one host thread: the CPU run takes a minute; the GPU run is instant
 SLOW_ON_CPU = ["test/PlaidML/CppEdsl.BigDot.mlir"]
 
@@ -80,7 +100,7 @@ needs_oracle_runner = pytest.mark.skipif(not os.path.exists(ORACLE_RUNNER),
 
 # ------------------------------------------------------------------ CPU: the loop-nest checker
 @needs_oracle_runner
-@pytest.mark.parametrize("rel", HOT_PATH)
+@pytest.mark.parametrize("rel", HOT_PATH + OTHER_PROGRAMS)
 def test_cpu_loop_nests_reproduce_the_reference_check_lines(rel):
     path = reference_files.need(rel)
     r = _run([ORACLE_RUNNER, path, "--all-loopnests", "-e", "main"])
@@ -133,7 +153,7 @@ def test_the_hot_path_programs_use_the_hot_path_kernels():
 
 # ------------------------------------------------------------------ GPU
 @pytest.mark.gpu
-@pytest.mark.parametrize("rel", HOT_PATH + SLOW_ON_CPU)
+@pytest.mark.parametrize("rel", HOT_PATH + OTHER_PROGRAMS + SLOW_ON_CPU)
 def test_gpu_runner_reproduces_the_reference_check_lines(rel):
     path = reference_files.need(rel)
     r = _run([RUNNER, path, "-e", "main"])
