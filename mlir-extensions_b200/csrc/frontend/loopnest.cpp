@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <map>
 #include <set>
 #include <sstream>
@@ -89,6 +90,9 @@ public:
   BodyWriter(const ConstantTable &c, std::ostringstream &o, const std::string &ind) : constants(c), os(o), indent(ind) {}
   std::map<std::string, Val> env;
   std::string why;
+  // tensors of the enclosing function that the region reads with tensor.extract: extra
+  // pointer arguments of the kernel (cap0, cap1, ...), in this order
+  std::vector<std::pair<std::string, Type>> captured;
 
   Val use(const std::string &name, const std::string &eltHint) {
     auto it = env.find(name);
@@ -326,8 +330,85 @@ public:
       define(o.results[0], resElt, "(" + a + " < 0 ? (" + computeType(resElt) + ")(-" + a + ") : " + a + ")");
       return true;
     }
+    // ---- values of the enclosing function, and branches (what a concatenation lowers to:
+    //      test/Jax/janet/jit_prim_fun.50_linalg.mlir:21-40) ----------------------------
+    if (n == "tensor.dim" && o.operands.size() == 2 && !o.operandTypes.empty()) {
+      const Type &t = o.operandTypes[0];
+      if (!t.isShaped() || t.unranked) { why = "tensor.dim of an unranked value"; return false; }
+      const std::string idx = in(1, "index");
+      std::string e = "0LL";
+      for (int r = static_cast<int>(t.shape.size()) - 1; r >= 0; --r) {
+        if (t.shape[r] < 0) { why = "tensor.dim of a dynamic extent"; return false; }
+        e = "(" + idx + " == " + std::to_string(r) + " ? " + std::to_string(t.shape[r]) + "LL : " + e + ")";
+      }
+      define(o.results[0], "index", "(i64)" + e);
+      return true;
+    }
+    if (n == "tensor.extract" && !o.operands.empty() && !o.operandTypes.empty()) {
+      const Type &t = o.operandTypes[0];
+      if (!t.isShaped() || t.unranked || !storageType(t.elt) || o.operands.size() != 1 + t.shape.size()) {
+        why = "tensor.extract from " + o.operands[0];
+        return false;
+      }
+      size_t k = 0;
+      while (k < captured.size() && captured[k].first != o.operands[0]) ++k;
+      if (k == captured.size()) captured.emplace_back(o.operands[0], t);
+      std::string lin;
+      int64_t stride = 1;
+      for (int r = static_cast<int>(t.shape.size()) - 1; r >= 0; --r) {
+        if (t.shape[r] < 0) { why = "tensor.extract from a dynamic shape"; return false; }
+        std::string term = in(1 + r, "index");
+        if (stride != 1) term += " * " + std::to_string(stride) + "LL";
+        lin = lin.empty() ? term : term + " + " + lin;
+        stride *= t.shape[r];
+      }
+      if (lin.empty()) lin = "0";
+      define(o.results[0], t.elt, loadExpr(t.elt, "cap" + std::to_string(k) + "[" + lin + "]"));
+      return true;
+    }
+    if (n == "scf.if" && o.operands.size() == 1 && o.body) {
+      if (!o.results.empty() && !o.elseBody) { why = "scf.if with results and no else region"; return false; }
+      std::vector<std::string> vars;
+      for (size_t r = 0; r < o.results.size(); ++r) {
+        const std::string &e = o.resultTypes[r].elt;
+        if (!computeType(e)) { why = "scf.if result of type " + e; return false; }
+        vars.push_back("v" + std::to_string(counter++));
+        os << indent << computeType(e) << " " << vars.back() << ";\n";
+      }
+      os << indent << "if (" << in(0, "i1") << ") {\n";
+      if (!region(*o.body, vars, o.resultTypes)) return false;
+      if (o.elseBody) {
+        os << indent << "} else {\n";
+        if (!region(*o.elseBody, vars, o.resultTypes)) return false;
+      }
+      os << indent << "}\n";
+      for (size_t r = 0; r < o.results.size(); ++r) env[o.results[r]] = Val{vars[r], o.resultTypes[r].elt};
+      return true;
+    }
     why = "operation " + n + " has no loop-nest translation";
     return false;
+  }
+
+  // a region of scf.if: its operations one level deeper, scf.yield assigning the results
+  bool region(const Block &b, const std::vector<std::string> &vars, const std::vector<Type> &types) {
+    const std::map<std::string, Val> outer = env;
+    const std::string outerIndent = indent;
+    indent += "  ";
+    bool ok = true, yielded = vars.empty();
+    for (auto &o : b.ops) {
+      if (o->name == "scf.yield") {
+        if (o->operands.size() != vars.size()) { why = "scf.yield count differs from the results"; ok = false; break; }
+        for (size_t r = 0; r < vars.size(); ++r)
+          os << indent << vars[r] << " = " << use(o->operands[r], types[r].elt).expr << ";\n";
+        yielded = true;
+        continue;
+      }
+      if (!emit(*o)) { ok = false; break; }
+    }
+    if (ok && !yielded) { why = "region without scf.yield"; ok = false; }
+    env = outer;
+    indent = outerIndent;
+    return ok;
   }
 
 private:
@@ -404,8 +485,28 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
       why = "extent of d" + std::to_string(d) + " cannot be inferred";
       return false;
     }
+  // A dimension labelled "reduction" that every output is indexed by carries nothing from one
+  // of its iterations to the next: each point updates an element of its own
+  // (test/PlaidML/OpTest.ExplicitPaddingNegInf.mlir:29).  It is run as a parallel dimension, the
+  // outputs keeping their initial contents where the iteration space does not reach.
+  auto inEveryOutput = [&](int d) {
+    for (size_t k = nIn; k < nIn + nOut; ++k) {
+      bool found = false;
+      for (auto &mr : op.maps[k].results)
+        found = found || (mr.simple ? (!mr.isConst && mr.value == d) : mr.shiftDim == d);
+      if (!found) return false;
+    }
+    return true;
+  };
   std::vector<int> par, red;
-  for (int d = 0; d < nd; ++d) (op.iterators[d] == "reduction" ? red : par).push_back(d);
+  bool relabelled = false;
+  for (int d = 0; d < nd; ++d) {
+    if (op.iterators[d] == "reduction" && !inEveryOutput(d)) red.push_back(d);
+    else {
+      par.push_back(d);
+      relabelled = relabelled || op.iterators[d] == "reduction";
+    }
+  }
   // outputs: indexed by parallel dimensions only, and by all of them
   // (a dimension moved by a constant, d0 + 2, still addresses every element at most once: the
   // part of the output the iteration space does not reach keeps its initial value,
@@ -449,28 +550,34 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
 
   // does the region read an output's block argument?
   std::set<std::string> usedNames;
-  for (auto &o : op.body->ops)
-    for (auto &v : o->operands) usedNames.insert(v);
+  std::function<void(const Block &)> collect = [&](const Block &b) {
+    for (auto &o : b.ops) {
+      for (auto &v : o->operands) usedNames.insert(v);
+      if (o->body) collect(*o->body);
+      if (o->elseBody) collect(*o->elseBody);
+    }
+  };
+  collect(*op.body);
   out.readsInit.assign(nOut, false);
   for (size_t k = 0; k < nOut; ++k)
-    out.readsInit[k] = !red.empty() || partial[k] || usedNames.count(op.body->args[nIn + k]) != 0;
+    out.readsInit[k] = !red.empty() || relabelled || partial[k] || usedNames.count(op.body->args[nIn + k]) != 0;
 
-  std::ostringstream os;
-  os << "extern \"C\" __global__ void imex_loopnest(";
+  // the argument list is written last: the region tells which outer tensors it reads
+  std::ostringstream sig, os;
+  sig << "extern \"C\" __global__ void imex_loopnest(";
   out.pointerInputs.clear();
   bool first = true;
   for (size_t k = 0; k < nIn; ++k) {
     if (!typeOf(k).isShaped()) continue;
     out.pointerInputs.push_back(static_cast<int>(k));
-    os << (first ? "" : ", ") << "const " << storageType(typeOf(k).elt) << " *__restrict__ in" << k;
+    sig << (first ? "" : ", ") << "const " << storageType(typeOf(k).elt) << " *__restrict__ in" << k;
     first = false;
   }
   for (size_t k = 0; k < nOut; ++k) {
-    os << (first ? "" : ", ") << storageType(typeOf(nIn + k).elt) << " *__restrict__ out" << k;
+    sig << (first ? "" : ", ") << storageType(typeOf(nIn + k).elt) << " *__restrict__ out" << k;
     first = false;
   }
-  os << ") {\n"
-     << "  const i64 p = IMX_THREAD_INDEX;\n"
+  os << "  const i64 p = IMX_THREAD_INDEX;\n"
      << "  if (p >= " << out.threads << "LL) return;\n"
      << "  i64 q = p;\n";
   for (int i = static_cast<int>(par.size()) - 1; i >= 0; --i) {
@@ -543,7 +650,13 @@ bool buildLoopNest(const Op &op, const ConstantTable &constants, LoopNestKernel 
   for (size_t k = 0; k < nOut; ++k)
     os << "  out" << k << "[o" << k << "] = " << storeExpr(typeOf(nIn + k).elt, "acc" + std::to_string(k)) << ";\n";
   os << "}\n";
-  out.source = os.str();
+  out.captured.clear();
+  for (size_t k = 0; k < body.captured.size(); ++k) {
+    sig << ", const " << storageType(body.captured[k].second.elt) << " *__restrict__ cap" << k;
+    out.captured.push_back(body.captured[k].first);
+  }
+  sig << ") {\n";
+  out.source = sig.str() + os.str();
   std::ostringstream sum;
   sum << "loopnest[" << par.size() << " parallel, " << red.size() << " reduction dims, " << out.threads << " threads]";
   out.summary = sum.str();

@@ -28,6 +28,8 @@ struct LoopNestKernel {
   std::vector<int> pointerInputs;   // indices into op.ins passed as pointers, in argument order
                                     // (scalar ins are written into the text as literals)
   std::vector<bool> readsInit;      // per output: the kernel reads the output's initial contents
+  std::vector<std::string> captured;  // tensors of the enclosing function the region reads with
+                                      // tensor.extract: pointer arguments after the outputs
   int64_t threads = 1;              // points of the parallel iteration space
   std::string summary;              // for plans and diagnostics
 };

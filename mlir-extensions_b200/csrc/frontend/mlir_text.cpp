@@ -903,6 +903,31 @@ private:
       operandList(op->operands);
       expect(':');
       op->resultTypes.push_back(type());
+    } else if (n == "tensor.dim") {
+      // %5 = tensor.dim %arg0, %c0_0 : tensor<1x6xf32>
+      operandList(op->operands);
+      expect(':');
+      op->operandTypes.push_back(type());
+      Type e;
+      e.kind = Type::Scalar;
+      e.elt = "index";
+      op->resultTypes.push_back(e);
+    } else if (n == "scf.if") {
+      // %8 = scf.if %7 -> (f32) { ... scf.yield %10 : f32 } else { ... }
+      operandList(op->operands);
+      skip();
+      if (peek() == '-') {
+        expectArrow();
+        op->resultTypes = typeList();
+      }
+      expect('{');
+      op->body = std::make_unique<Block>();
+      block(*op->body, /*allowLabel=*/false);
+      if (acceptWord("else")) {
+        expect('{');
+        op->elseBody = std::make_unique<Block>();
+        block(*op->elseBody, /*allowLabel=*/false);
+      }
     } else if (n == "tensor.extract_slice") {
       // %r = tensor.extract_slice %x[49999] [1] [1] : tensor<50000xf32> to tensor<1xf32>
       //      (offsets, sizes, strides; static only; the result may drop unit dimensions)

@@ -73,7 +73,8 @@ struct Op {
   std::vector<Type> insTypes, outsTypes;
   std::vector<AffineMap> maps;
   std::vector<std::string> iterators;  // "parallel" / "reduction"
-  std::unique_ptr<Block> body;         // region of linalg.generic / scf.for
+  std::unique_ptr<Block> body;         // region of linalg.generic / scf.for; "then" region of scf.if
+  std::unique_ptr<Block> elseBody;     // "else" region of scf.if
   // arith.constant
   bool hasDense = false;
   bool denseSplat = false;

@@ -728,6 +728,11 @@ private:
       ptrs.push_back(out.buf->ptr);
       outs.push_back(out);
     }
+    for (auto &name : k.captured) {  // tensors the region reads with tensor.extract
+      Value &v = get(fr, name, op);
+      if (v.kind != Value::Tensor) die(where + "tensor.extract from " + name + ", which is no tensor here");
+      ptrs.push_back(v.buf->ptr);
+    }
     ImexKernelDesc d = desc(IMEX_OP_LOOPNEST, 0, 0);
     d.dims[0] = k.threads;
     d.dims[3] = static_cast<int64_t>(ptrs.size());
