@@ -803,6 +803,7 @@ private:
       op->resultTypes.push_back(type());
     } else if (n == "tensor.empty") {
       expect('(');
+      operandList(op->operands);  // the extents of the dynamic dimensions, in order
       expect(')');
       expect(':');
       op->resultTypes.push_back(type());

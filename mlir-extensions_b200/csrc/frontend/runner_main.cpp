@@ -698,18 +698,33 @@ private:
 
   // Any linalg.generic that is none of the recognised ops: the reference pipeline's own
   // lowering, a loop nest with its parallel loops on threads (loopnest.h).
+  static bool hasDynamicExtent(const Op &op) {
+    for (auto *types : {&op.insTypes, &op.outsTypes})
+      for (auto &t : *types)
+        for (auto d : t.shape)
+          if (d < 0) return true;
+    return false;
+  }
+
   void loopNestOp(const Op &op, Frame &fr, void *stream, const std::string &where, const std::string &because) {
     LoopNestKernel k;
     std::string why;
     if (op.results.empty())
       die(where + "linalg ops on buffers (no results) are not supported: the runner works on tensors");
-    std::vector<Type> actual;  // operand types as they are here: this rank's rows of a row-sharded array
-    if (curShard.active) {
+    // operand types as they are here: this rank's rows of a row-sharded array; the extents that
+    // the IR leaves dynamic (tensor<?x?xf32>), taken from the values
+    std::vector<Type> actual;
+    const bool dynamic = hasDynamicExtent(op);
+    if (curShard.active || dynamic) {
       for (size_t i = 0; i < op.ins.size(); ++i) {
         auto it = fr.vals.find(op.ins[i]);
         actual.push_back(it != fr.vals.end() && it->second.kind == Value::Tensor ? it->second.type : op.insTypes[i]);
       }
-      for (auto &t : op.outsTypes) actual.push_back(localType(t));
+      for (size_t r = 0; r < op.outs.size(); ++r) {
+        auto it = fr.vals.find(op.outs[r]);
+        if (dynamic && it != fr.vals.end() && it->second.kind == Value::Tensor) actual.push_back(it->second.type);
+        else actual.push_back(localType(op.outsTypes[r]));
+      }
     }
     if (!buildLoopNest(op, fr.constants, k, why, actual.empty() ? nullptr : &actual))
       die(where + op.name + " is not a recognised hot-path op (" + because + ") and cannot be written as a loop nest (" +
@@ -718,7 +733,7 @@ private:
     for (int i : k.pointerInputs) ptrs.push_back(get(fr, op.ins[i], op).buf->ptr);
     std::vector<Value> outs;
     for (size_t r = 0; r < op.outs.size(); ++r) {
-      const Type t = r < op.resultTypes.size() ? op.resultTypes[r] : op.outsTypes[r];
+      const Type t = dynamic ? actual[op.ins.size() + r] : r < op.resultTypes.size() ? op.resultTypes[r] : op.outsTypes[r];
       Value out = makeTensor(stream, t);
       if (k.readsInit[r]) {
         Value &init = get(fr, op.outs[r], op);
@@ -862,11 +877,39 @@ private:
         }
         fr.vals[op.results[0]] = v;
       } else if (n == "tensor.empty") {
-        fr.vals[op.results[0]] = makeTensor(stream, op.resultTypes[0]);
+        // tensor.empty(%d0, %d1) : tensor<?x?xf32> -- the operands are the dynamic extents, in order
+        // (test/PlaidML/OpTest.EltwiseAdd.dynamic.mlir:17)
+        Type t = op.resultTypes[0];
+        size_t next = 0;
+        for (auto &d : t.shape)
+          if (d < 0) {
+            if (next >= op.operands.size()) die("line " + std::to_string(op.line) + ": tensor.empty with too few extents");
+            d = static_cast<int64_t>(get(fr, op.operands[next++], op).scalar);
+          }
+        fr.vals[op.results[0]] = makeTensor(stream, t);
+      } else if (n == "tensor.dim") {
+        // the extent the value has here: every value of the runner carries its actual shape
+        const Value &t = get(fr, op.operands[0], op);
+        const int64_t d = static_cast<int64_t>(get(fr, op.operands[1], op).scalar);
+        if (t.kind != Value::Tensor || d < 0 || d >= static_cast<int64_t>(t.type.shape.size()))
+          die("line " + std::to_string(op.line) + ": tensor.dim outside the rank of its operand");
+        Value v;
+        v.kind = Value::Scalar;
+        v.type = op.resultTypes[0];
+        v.scalar = static_cast<double>(t.type.shape[d]);
+        fr.constants[op.results[0]] = v.scalar;
+        fr.vals[op.results[0]] = v;
       } else if (n == "tensor.cast" || n == "memref.cast" || n == "bufferization.to_memref" ||
                  n == "bufferization.to_buffer" || n == "bufferization.to_tensor") {
         Value v = get(fr, op.operands[0], op);
-        if (!op.resultTypes[0].unranked) v.type = op.resultTypes[0];
+        if (!op.resultTypes[0].unranked) {
+          // a cast to a type with dynamic extents forgets them in the IR only: the value keeps its shape
+          Type to = op.resultTypes[0];
+          if (to.shape.size() == v.type.shape.size())
+            for (size_t d = 0; d < to.shape.size(); ++d)
+              if (to.shape[d] < 0) to.shape[d] = v.type.shape[d];
+          v.type = to;
+        }
         fr.vals[op.results[0]] = v;
       } else if (n == "tensor.expand_shape" || n == "tensor.collapse_shape") {
         Value v = get(fr, op.operands[0], op);  // contiguous: only the shape changes
@@ -1471,10 +1514,21 @@ private:
 
   void linalgOpBody(const Op &op, const Block &b, Frame &fr, void *stream, std::set<const Op *> &absorbed,
                     std::map<std::string, const Op *> &defs, std::map<std::string, int> &uses) {
-    Classified c = classify(op, fr.constants);
     auto where = "line " + std::to_string(op.line) + ": ";
     if (op.results.empty())
       die(where + "linalg ops on buffers (no results) are not supported: the runner works on tensors");
+    if (hasDynamicExtent(op) && !g_allLoopNests) {
+      // the hot-path kernels are chosen from the static types of the IR; an op whose extents are
+      // only known when it is reached runs as the loop nest written for the shapes at hand
+      if (op.name == "linalg.generic") {
+        loopNestOp(op, fr, stream, where, "dynamic extents in its types");
+      } else {
+        std::unique_ptr<Op> g = namedOpAsGeneric(op, where);
+        loopNestOp(*g, fr, stream, where, "dynamic extents in its types");
+      }
+      return;
+    }
+    Classified c = classify(op, fr.constants);
     if (g_allLoopNests) {
       if (op.name == "linalg.generic") {
         loopNestOp(op, fr, stream, where, "every op is lowered to its loop nest in this mode");

@@ -97,7 +97,41 @@ def test_parse_errors_name_the_line(tmp_path):
     assert rc == 1 and "line 3" in err and "foo.bar" in err
     p.write_text("func.func @main() {\n  %t = tensor.empty() : tensor<?x4xf32>\n  return\n}\n")
     rc, out, err = plan(str(p))
-    assert rc == 1 and "dynamic shapes" in err
+    assert rc == 1 and "line 2" in err and "too few extents" in err
+
+
+def test_dynamic_extents_are_taken_from_the_values(tmp_path):
+    """tensor<?x?xf32> in a callee: tensor.dim reads the extent the value has, tensor.empty(%d0, %d1)
+    allocates it, and the op runs as the loop nest for those extents
+    (the reference's test/PlaidML/OpTest.EltwiseAdd.dynamic.mlir has this form)."""
+    p = tmp_path / "dyn.mlir"
+    p.write_text("""#map = affine_map<(d0, d1) -> (d0, d1)>
+module {
+  func.func @twice(%a: tensor<?x?xf32>) -> tensor<?x?xf32> {
+    %c0 = arith.constant 0 : index
+    %c1 = arith.constant 1 : index
+    %d0 = tensor.dim %a, %c0 : tensor<?x?xf32>
+    %d1 = tensor.dim %a, %c1 : tensor<?x?xf32>
+    %0 = tensor.empty(%d0, %d1) : tensor<?x?xf32>
+    %1 = linalg.generic {indexing_maps = [#map, #map], iterator_types = ["parallel", "parallel"]}
+         ins(%a : tensor<?x?xf32>) outs(%0 : tensor<?x?xf32>) {
+      ^bb0(%x: f32, %y: f32):
+        %2 = arith.addf %x, %x : f32
+        linalg.yield %2 : f32
+    } -> tensor<?x?xf32>
+    return %1 : tensor<?x?xf32>
+  }
+  func.func @main() {
+    %0 = arith.constant dense<1.5> : tensor<3x5xf32>
+    %1 = tensor.cast %0 : tensor<3x5xf32> to tensor<?x?xf32>
+    %2 = call @twice(%1) : (tensor<?x?xf32>) -> tensor<?x?xf32>
+    return
+  }
+}
+""")
+    rc, out, err = plan(str(p))
+    assert rc == 0, err
+    assert "loopnest[2 parallel, 0 reduction dims, 15 threads]" in out
 
 
 def test_filecheck_semantics():
