@@ -229,7 +229,8 @@ public:
     }
     if (n == "arith.bitcast") {
       const std::string a = in(0, opElt);
-      if (opElt == "f32" && resElt == "i32") define(o.results[0], resElt, "imx_f32_bits(" + a + ")");
+      if (opElt == resElt) define(o.results[0], resElt, a);
+      else if (opElt == "f32" && resElt == "i32") define(o.results[0], resElt, "imx_f32_bits(" + a + ")");
       else if (opElt == "i32" && resElt == "f32") define(o.results[0], resElt, "imx_bits_f32(" + a + ")");
       else { why = "bitcast " + opElt + " to " + resElt; return false; }
       return true;

@@ -1145,6 +1145,43 @@ private:
       operandList(op->operands);
       expect(':');
       op->operandTypes.push_back(type());
+    } else if (n == "scf.while") {
+      // %0:6 = scf.while (%a = %init, ...) : (types) -> (types) { ... scf.condition(%c) %a, ... : types }
+      //        do { ^bb0(%a: type, ...): ... scf.yield ... : types }
+      // (test/Jax/janet/jit__get_age_weights_from_tables.8_linalg.mlir:389-591)
+      expect('(');
+      skip();
+      if (peek() != ')') {
+        do {
+          op->iterArgs.push_back(ident());
+          expect('=');
+          op->iterInits.push_back(ident());
+        } while (accept(','));
+      }
+      expect(')');
+      expect(':');
+      op->operandTypes = typeList();
+      expectArrow();
+      op->resultTypes = typeList();
+      expect('{');
+      op->body = std::make_unique<Block>();  // the "before" region: its arguments are the names above
+      op->body->args = op->iterArgs;
+      op->body->argTypes = op->operandTypes;
+      block(*op->body, /*allowLabel=*/false);
+      expectWord("do");
+      expect('{');
+      op->elseBody = std::make_unique<Block>();  // the "after" region
+      block(*op->elseBody, /*allowLabel=*/true);
+    } else if (n == "scf.condition") {
+      expect('(');
+      operandList(op->operands);  // the condition, then the forwarded values
+      expect(')');
+      operandList(op->operands);
+      if (accept(':')) {
+        do {
+          op->operandTypes.push_back(type());
+        } while (accept(','));
+      }
     } else if (n == "scf.for") {
       op->body = std::make_unique<Block>();
       op->body->args.push_back(ident());  // induction variable

@@ -74,7 +74,7 @@ struct Op {
   std::vector<AffineMap> maps;
   std::vector<std::string> iterators;  // "parallel" / "reduction"
   std::unique_ptr<Block> body;         // region of linalg.generic / scf.for; "then" region of scf.if
-  std::unique_ptr<Block> elseBody;     // "else" region of scf.if
+  std::unique_ptr<Block> elseBody;     // "else" region of scf.if; "do" region of scf.while (body: "before")
   // arith.constant
   bool hasDense = false;
   bool denseSplat = false;

@@ -369,6 +369,42 @@ private:
     return results;
   }
 
+  // scf.while on the host: the "before" region decides (scf.condition) and forwards values, the
+  // "do" region computes the next ones.  Each region is run as a block of its own; the values
+  // that cross a region boundary are in device memory (no elementwise chain stays open across it).
+  void whileOp(const Op &op, Frame &fr, void *stream) {
+    const std::string where = "line " + std::to_string(op.line) + ": ";
+    if (!op.body || !op.elseBody || op.elseBody->args.size() != op.resultTypes.size())
+      die(where + "scf.while without its two regions");
+    std::vector<Value> carried;
+    for (auto &i : op.iterInits) carried.push_back(get(fr, i, op));
+    std::map<std::string, const Op *> defsBefore, defsAfter;
+    std::map<std::string, int> usesBefore, usesAfter;
+    index(*op.body, defsBefore, usesBefore);
+    index(*op.elseBody, defsAfter, usesAfter);
+    const std::map<std::string, int> *outerUses = curUses;
+    std::vector<Value> forwarded;
+    for (int64_t it = 0;; ++it) {
+      if (carried.size() != op.body->args.size()) die(where + "scf.while carries a different number of values than it declares");
+      for (size_t k = 0; k < carried.size(); ++k) fr.vals[op.body->args[k]] = carried[k];
+      std::set<const Op *> none;
+      curUses = &usesBefore;
+      std::vector<Value> c = runBlock(*op.body, fr, stream, none, defsBefore, usesBefore);
+      if (c.empty() || c[0].kind != Value::Scalar) die(where + "the first region of scf.while must end in scf.condition");
+      forwarded.assign(c.begin() + 1, c.end());
+      if (forwarded.size() != op.elseBody->args.size()) die(where + "scf.condition forwards a different number of values");
+      // a plan lists the launches of the loop once
+      const bool again = g_plan ? it == 0 : c[0].scalar != 0;
+      if (!again) break;
+      for (size_t k = 0; k < forwarded.size(); ++k) fr.vals[op.elseBody->args[k]] = forwarded[k];
+      none.clear();
+      curUses = &usesAfter;
+      carried = runBlock(*op.elseBody, fr, stream, none, defsAfter, usesAfter);
+    }
+    curUses = outerUses;
+    for (size_t k = 0; k < op.results.size() && k < forwarded.size(); ++k) fr.vals[op.results[k]] = forwarded[k];
+  }
+
   static void index(const Block &b, std::map<std::string, const Op *> &defs, std::map<std::string, int> &uses) {
     for (auto &o : b.ops) {
       for (auto &r : o->results) defs[r] = o.get();
@@ -833,8 +869,8 @@ private:
       const Op &op = *up;
       if (absorbed.count(&op)) continue;
       const std::string &n = op.name;
-      if (n == "return" || n == "func.return" || n == "scf.yield") {
-        std::vector<Value> out;
+      if (n == "return" || n == "func.return" || n == "scf.yield" || n == "scf.condition") {
+        std::vector<Value> out;  // scf.condition: the condition, then the forwarded values
         for (auto &v : op.operands) out.push_back(get(fr, v, op));
         return out;
       }
@@ -943,10 +979,13 @@ private:
         } else if (!g_plan) {
           std::vector<char> host(t.buf->bytes);
           gpuMemCopy(stream, host.data(), t.buf->ptr, host.size());
-          float f = 0;
-          if (t.type.elt == "f32") std::memcpy(&f, host.data(), 4);
-          else die("tensor.extract supports f32 only");
-          v.scalar = f;
+          const std::string &e = t.type.elt;
+          if (e == "f32") { float f; std::memcpy(&f, host.data(), 4); v.scalar = f; }
+          else if (e == "f64") { std::memcpy(&v.scalar, host.data(), 8); }
+          else if (e == "i1" || e == "i8") { v.scalar = static_cast<double>(static_cast<int8_t>(host[0])); }
+          else if (e == "i32") { int32_t i; std::memcpy(&i, host.data(), 4); v.scalar = i; }
+          else if (e == "i64" || e == "index") { int64_t i; std::memcpy(&i, host.data(), 8); v.scalar = static_cast<double>(i); }
+          else die("line " + std::to_string(op.line) + ": tensor.extract of element type " + e);
         }
         fr.constants[op.results[0]] = v.scalar;
         fr.vals[op.results[0]] = v;
@@ -1002,6 +1041,8 @@ private:
           else std::cout << static_cast<long long>(v.scalar) << "\n";
         }
         std::cout.flush();
+      } else if (n == "scf.while") {
+        whileOp(op, fr, stream);
       } else if (n == "scf.for" && op.iterArgs.empty() && hostLoop(op, fr)) {
         // ran as a compiled host loop nest (host_loops.h)
       } else if (n == "scf.for") {

@@ -81,6 +81,8 @@ OTHER_PROGRAMS = [
     "test/PlaidML/OpTest.ExplicitPaddingNegInf.mlir",
     # extents the IR leaves dynamic (tensor<?x?xf32>, tensor.dim, tensor.empty(%d0, %d1)): known when the op is reached
     "test/PlaidML/OpTest.EltwiseAdd.dynamic.mlir", "test/PlaidML/OpTest.Sum.dynamic.mlir",
+    # a binary search as scf.while on the host over tensors (16 rounds of some forty launches)
+    "test/Jax/janet/jit__get_age_weights_from_tables.8_linalg.mlir",
 ]
 # 2048^3 on one host thread: the CPU run takes a minute; the GPU run is instant
 SLOW_ON_CPU = ["test/PlaidML/CppEdsl.BigDot.mlir"]
