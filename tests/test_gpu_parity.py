@@ -791,6 +791,28 @@ def test_fused_chain_of_exact_operations_is_bit_exact(pkg, sess, kind, expr_path
         assert sess.download(dy32, (rows, cols), np.float32).tobytes() == ref.tobytes()
 
 
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_reciprocal_in_a_16_bit_chain_is_bit_exact_for_every_value(pkg, sess, kind):
+    """1 / x over all 65536 bit patterns of the type (zeros, denormals, infinities and NaNs
+    included) against divf rounded to the type: the packed chain takes the f16 reciprocal from
+    the hardware approximation, which must round to the same value as the exact quotient."""
+    B = pkg.blob
+    bits = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    back = _NP16[kind][2]
+    x = back(bits)
+    d = sess.upload(bits)
+    dy = sess.alloc(bits.nbytes)
+    sess.run(B.expr("rcp", 256, 256, "one in0 div", B.F16 if kind == "f16" else B.BF16), [d, dy])
+    assert sess.last_kernel() == "expr_jit"
+    got = sess.download(dy, (256, 256), np.uint16)
+    with np.errstate(all="ignore"):
+        ref = oracle.binary("divf", np.ones_like(x), x, _NP16[kind][0])
+    ref_bits = _NP16[kind][1](ref)
+    nan = np.isnan(ref)
+    assert np.array_equal(np.isnan(back(got)), nan)
+    assert np.array_equal(got[~nan], ref_bits[~nan])
+
+
 @pytest.mark.parametrize("shape", [(512, 1024), (200, 70), (40, 300), (6, 606208)])
 @pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
 def test_fused_chain_into_column_reduce(pkg, sess, kind, expr_path, shape):
