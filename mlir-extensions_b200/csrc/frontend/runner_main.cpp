@@ -782,6 +782,7 @@ private:
     for (auto &name : k.captured) {  // tensors the region reads with tensor.extract
       Value &v = get(fr, name, op);
       if (v.kind != Value::Tensor) die(where + "tensor.extract from " + name + ", which is no tensor here");
+      if (v.globalRows >= 0) die(where + "tensor.extract inside a region from " + name + ", which is split by rows over ranks");
       ptrs.push_back(v.buf->ptr);
     }
     ImexKernelDesc d = desc(IMEX_OP_LOOPNEST, 0, 0);
