@@ -54,6 +54,10 @@ __device__ __forceinline__ float exp_c(float t) {
 // tests compare all 65536 bit patterns on the device).  An f16 value extended to f32 is never
 // an f32 denormal, nor is its reciprocal, so the flushing form loses nothing.
 __device__ __forceinline__ float rcp_h(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+// The same for bf16, whose range is that of f32: the form that keeps denormal arguments and
+// results.  A bf16 quotient is at least 2^-17 (relative; 2^-9 of a denormal step) from a rounding
+// boundary, far more than the approximation's one f32 ulp.
+__device__ __forceinline__ float rcp_b(float x) { float r; asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 // two 16-bit values in one register (element 0 in the low half)
 __device__ __forceinline__ unsigned pack_h(float lo, float hi) { unsigned d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
 __device__ __forceinline__ unsigned pack_b(float lo, float hi) { unsigned d; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
@@ -180,7 +184,7 @@ std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, st
       if (op == 66) { st.push_back(def("mul" + sfx + "(" + a + ", " + b + ")")); continue; }
       const char *fn = op == 67 ? "__fdiv_rn" : op == 68 ? "maximumf" : "minimumf";
       if (op == 67 && (a == "0x3f803f80u" || a == "0x3c003c00u")) {   // 1 / b, as above
-        const std::string rcp = bf16 ? "__frcp_rn" : "rcp_h";   // bf16 reaches the f32 denormals: exact form
+        const std::string rcp = bf16 ? "rcp_b" : "rcp_h";
         st.push_back(def(via_f32(rcp + "(lo" + sfx + "(" + b + "))", rcp + "(hi" + sfx + "(" + b + "))")));
         continue;
       }
