@@ -17,7 +17,9 @@ __device__ __forceinline__ float relu_ugt(float x) { return !(x <= 0.0f) ? x : 0
 // (convert-math-to-libm).  libm's expf costs ~25 instructions per element and,
 // with every warp of the single wave in the same phase, was a third of the
 // 4096x1024 softmax kernel's time.  NaN, -inf (ex2(-inf) = 0) and +inf pass through; results
-// below the normal range come out as the hardware's subnormals, overflow as +inf.
+// below the normal range come out as the hardware's subnormals, overflow as +inf: where the
+// correction is not a number (an infinite argument, or 2^y = inf times a negative residual)
+// the uncorrected 2^y is the result.
 __device__ __forceinline__ float exp_neg(float t) {
   const float L2E_HI = 1.44269502162933349609375f;   // float(log2(e))
   const float L2E_LO = 1.92596299112661746e-8f;      // log2(e) - L2E_HI
@@ -28,7 +30,8 @@ __device__ __forceinline__ float exp_neg(float t) {
   float e;
   asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(y));
   // 2^(y + r) = 2^y * (1 + r ln2 + ...);  |r| < 2^-18, the next term is below 2^-38
-  return isfinite(r) ? __fmaf_rn(e, __fmul_rn(r, LN2), e) : e;
+  const float c = __fmaf_rn(e, __fmul_rn(r, LN2), e);
+  return c == c ? c : e;
 }
 
 // negf, exp, addf 1, divf 1/., then mulf s*x

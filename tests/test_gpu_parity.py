@@ -624,6 +624,10 @@ def test_transpose3d_of_16bit_elements(pkg, sess, dims, perm):
 def test_eltwise_relu_silu(pkg, sess):
     X = np.random.default_rng(8).normal(0, 4, 100003).astype(np.float32)
     X[:4] = [np.nan, -0.0, 0.0, -np.inf]
+    # exp(-x) overflows from x = -88.73 down: silu is x / inf = -0 there, whatever the sign of the
+    # rounding residual the exponential's correction is built from
+    X[4:104] = -np.linspace(88.0, 200.0, 100, dtype=np.float32)
+    X[104:108] = [-1e4, -3e38, np.inf, 3e38]
     dX, dY = sess.upload(X), sess.alloc(X.nbytes)
     sess.run(pkg.blob.eltwise("relu", X.size, pkg.blob.EPI_RELU), [dX, dY])
     got = sess.download(dY, X.shape, np.float32)
@@ -632,9 +636,12 @@ def test_eltwise_relu_silu(pkg, sess):
     sess.run(pkg.blob.eltwise("silu", X.size, pkg.blob.EPI_SILU), [dX, dY])
     got = sess.download(dY, X.shape, np.float32)
     ref = oracle.silu(X)
-    ok = ~np.isnan(ref)
     assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert np.array_equal(np.isinf(got), np.isinf(ref))
+    ok = np.isfinite(ref)
     assert oracle.max_rel_err(got[ok], ref[ok], 1e-37) <= 1e-5
+    zero = ref == 0                      # signed zeros: -0 below the overflow of exp(-x)
+    assert np.array_equal(got[zero].view(np.uint32), ref[zero].view(np.uint32))
 
 
 def test_fill_uniform_matches_oracle_bits(pkg, sess):
@@ -811,6 +818,35 @@ def test_reciprocal_in_a_16_bit_chain_is_bit_exact_for_every_value(pkg, sess, ki
     nan = np.isnan(ref)
     assert np.array_equal(np.isnan(back(got)), nan)
     assert np.array_equal(got[~nan], ref_bits[~nan])
+
+
+@pytest.mark.parametrize("op", ["exp", "log", "sqrt", "rsqrt", "tanh"])
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_unary_functions_of_a_16_bit_chain_over_every_value(pkg, sess, kind, op):
+    """Every one of the 65536 arguments of the type through the compiled chain, against the
+    function of the host's libm in f32 rounded to the type (what the reference's CPU pipeline
+    computes).  sqrt and rsqrt are exactly rounded on both sides; exp, log and tanh are
+    different implementations whose f32 results may fall on either side of a 16-bit rounding
+    boundary: at most two arguments in 65536 may differ, by one code (measured: none for exp,
+    tanh and the bf16 log, one for the f16 log)."""
+    B = pkg.blob
+    bits = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    back = _NP16[kind][2]
+    x = back(bits)
+    d = sess.upload(bits)
+    dy = sess.alloc(bits.nbytes)
+    sess.run(B.expr("every_" + op, 256, 256, "in0 " + op, B.F16 if kind == "f16" else B.BF16), [d, dy])
+    assert sess.last_kernel() == "expr_jit"
+    got = sess.download(dy, (256, 256), np.uint16)
+    with np.errstate(all="ignore"):
+        ref = oracle.unary(op, x, _NP16[kind][0])
+    ref_bits = _NP16[kind][1](ref)
+    nan = np.isnan(ref)
+    assert np.array_equal(np.isnan(back(got)), nan)   # e.g. exp of a large argument is +inf, not NaN
+    differ = (got != ref_bits) & ~nan
+    allowed = 0 if op in ("sqrt", "rsqrt") else 2
+    assert np.count_nonzero(differ) <= allowed
+    assert np.all(np.abs(got[differ].astype(np.int32) - ref_bits[differ].astype(np.int32)) <= 1)
 
 
 @pytest.mark.parametrize("shape", [(512, 1024), (200, 70), (40, 300), (6, 606208)])
