@@ -329,8 +329,11 @@ softmax_rows_x16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ y
     __syncthreads();
     mx = red[0];
     for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
-    for (int i = threadIdx.x; i < cols; i += blockDim.x)
-      row[i] = round16<BF16>(expf(round16<BF16>(__fsub_rn(row[i], mx))));
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float t = round16<BF16>(__fsub_rn(row[i], mx));
+      // the two forms that give libm's expf rounded to the type for every argument of the type
+      row[i] = round16<BF16>(BF16 ? exp_neg(t) : exp_f16_arg(t));
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       // The chain s <- round16(x_i + s) is the critical path of the kernel.  One native 16-bit
