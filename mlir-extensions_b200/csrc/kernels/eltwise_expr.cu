@@ -83,12 +83,13 @@ __device__ __forceinline__ float minimumf(float a, float b) {
   return fminf(a, b);
 }
 
-__device__ __forceinline__ float unary(int op, float x) {
+__device__ __forceinline__ float unary(int op, float x, int dt) {
   switch (op) {
   case 32: return -x;
   case 33: return fabsf(x);
   case 34: return logf(x);
-  case 35: return expf(x);
+  // 16-bit types: the forms that round to libm's 16-bit value for every argument, as in the compiled chains
+  case 35: return dt == kF16 ? exp_f16_arg(x) : dt == kBF16 ? exp_neg(x) : expf(x);
   case 36: return __fsqrt_rn(x);
   case 37: return __fdiv_rn(1.0f, __fsqrt_rn(x));
   case 38: return tanhf(x);
@@ -140,7 +141,7 @@ __device__ __forceinline__ void evaluate(const ExprParams &p, long long row, lon
       }
     } else if (op < 64) {
 #pragma unroll
-      for (int v = 0; v < V; ++v) top[v] = round_to(unary(op, top[v]), p.dtype);
+      for (int v = 0; v < V; ++v) top[v] = round_to(unary(op, top[v], p.dtype), p.dtype);
     } else {
       --sp;
 #pragma unroll
