@@ -271,6 +271,11 @@ public:
         static const std::map<std::string, const char *> binary = {
             {"powf", "pow"}, {"atan2", "atan2"}, {"copysign", "copysign"}};
         auto u = unary.find(fn);
+        if (fn == "exp" && (resElt == "f16" || resElt == "bf16") && o.operands.size() == 1) {
+          // forms that round to libm's 16-bit value for every argument of the type (the kernel prelude)
+          define(o.results[0], resElt, rounded(resElt, "imx_exp_" + resElt + "(" + in(0, resElt) + ")"));
+          return true;
+        }
         if (u != unary.end() && o.operands.size() == 1) {
           define(o.results[0], resElt, rounded(resElt, mathName(u->second) + "(" + in(0, resElt) + ")"));
           return true;

@@ -42,6 +42,21 @@ __device__ __forceinline__ float imx_maximum(float a, float b) { return a != a ?
 __device__ __forceinline__ float imx_minimum(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 __device__ __forceinline__ double imx_maximum(double a, double b) { return a != a ? a : (b != b ? b : fmax(a, b)); }
 __device__ __forceinline__ double imx_minimum(double a, double b) { return a != a ? a : (b != b ? b : fmin(a, b)); }
+// math.exp on an f16 / bf16 value (the result is rounded to the type by the caller): 2^(x log2 e)
+// on the hardware unit with the rounding error of the product fed back.  Rounded to the type
+// these equal libm's expf rounded to the type for every one of the 65536 arguments of the type
+// (the f16 form leaves out the low part of log2 e; both tested over all arguments on the device).
+__device__ __forceinline__ float imx_exp_16(float x, float l2e_lo) {
+  const float y = __fmul_rn(x, 1.44269502162933349609375f);
+  float r = __fmaf_rn(x, 1.44269502162933349609375f, -y);
+  r = __fmaf_rn(x, l2e_lo, r);
+  float e;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(y));
+  const float c = __fmaf_rn(e, __fmul_rn(r, 0.693147182464599609375f), e);
+  return c == c ? c : e;   // infinite x, or 2^y = inf with a negative residual: no correction
+}
+__device__ __forceinline__ float imx_exp_f16(float x) { return imx_exp_16(x, 0.0f); }
+__device__ __forceinline__ float imx_exp_bf16(float x) { return imx_exp_16(x, 1.92596299112661746e-8f); }
 __device__ __forceinline__ float imx_maxnum(float a, float b) { return fmaxf(a, b); }
 __device__ __forceinline__ float imx_minnum(float a, float b) { return fminf(a, b); }
 __device__ __forceinline__ double imx_maxnum(double a, double b) { return fmax(a, b); }

@@ -84,6 +84,8 @@ static inline float imx_maximum(float a, float b) { return a != a ? a : (b != b 
 static inline float imx_minimum(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 static inline double imx_maximum(double a, double b) { return a != a ? a : (b != b ? b : fmax(a, b)); }
 static inline double imx_minimum(double a, double b) { return a != a ? a : (b != b ? b : fmin(a, b)); }
+static inline float imx_exp_f16(float x) { return expf(x); }   // the device side has forms of its own for 16-bit arguments
+static inline float imx_exp_bf16(float x) { return expf(x); }
 static inline float imx_maxnum(float a, float b) { return fmaxf(a, b); }
 static inline float imx_minnum(float a, float b) { return fminf(a, b); }
 static inline double imx_maxnum(double a, double b) { return fmax(a, b); }
