@@ -36,13 +36,14 @@ __device__ __forceinline__ float exp_neg(float t) {
 
 // exp of an f16 value, for a result that is rounded to f16: without the low part of log2 e.
 // Rounded to f16 it equals libm's expf rounded to f16 for every one of the 65536 f16 arguments,
-// as exp_neg does for every bf16 argument (both tested over all arguments on the device).
+// as exp_neg does for every bf16 argument (both tested over all arguments on the device).  A result
+// below f32's normal range rounds to zero in f16 flushed or not: the flushing form of ex2.
 __device__ __forceinline__ float exp_f16_arg(float t) {
   const float L2E_HI = 1.44269502162933349609375f;
   const float y = __fmul_rn(t, L2E_HI);
   const float r = __fmaf_rn(t, L2E_HI, -y);
   float e;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(y));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y));
   const float c = __fmaf_rn(e, __fmul_rn(r, 0.693147182464599609375f), e);
   return c == c ? c : e;
 }

@@ -50,12 +50,13 @@ __device__ __forceinline__ float exp_c(float t) {
 }
 // The form for f16 chains: without the low part of log2 e.  Rounded to f16 it equals libm's expf
 // rounded to f16 for every one of the 65536 f16 arguments (tested on the device), as exp_c does
-// for every bf16 argument.
+// for every bf16 argument.  Results below f32's normal range round to zero in f16 whether they are
+// flushed or not, so the flushing form of ex2 is used.
 __device__ __forceinline__ float exp_s(float t) {
   const float y = __fmul_rn(t, 1.44269502162933349609375f);
   const float r = __fmaf_rn(t, 1.44269502162933349609375f, -y);
   float e;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(y));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y));
   const float c = __fmaf_rn(e, __fmul_rn(r, 0.693147182464599609375f), e);
   return c == c ? c : e;
 }
