@@ -81,6 +81,15 @@ __device__ __forceinline__ float hi_b(unsigned x) { return __uint_as_float(x & 0
 __device__ __forceinline__ unsigned add_h(unsigned a, unsigned b) { unsigned d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ unsigned sub_h(unsigned a, unsigned b) { unsigned d; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ unsigned mul_h(unsigned a, unsigned b) { unsigned d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+// relu as the reference writes it (x > 0 or unordered ? x : 0) on both halves: the halves that
+// compare <= 0 (never a NaN) are cleared, which also turns -0 into +0
+__device__ __forceinline__ unsigned relu_h(unsigned x) { unsigned m; asm("set.le.u32.f16x2 %0, %1, %2;" : "=r"(m) : "r"(x), "r"(0u)); return x & ~m; }
+__device__ __forceinline__ unsigned relu_b(unsigned x) { unsigned m; asm("set.le.u32.bf16x2 %0, %1, %2;" : "=r"(m) : "r"(x), "r"(0u)); return x & ~m; }
+// arith.maximumf / minimumf: NaN if either operand is one
+__device__ __forceinline__ unsigned max_h(unsigned a, unsigned b) { unsigned d; asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned min_h(unsigned a, unsigned b) { unsigned d; asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned max_b(unsigned a, unsigned b) { unsigned d; asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ unsigned min_b(unsigned a, unsigned b) { unsigned d; asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ unsigned add_b(unsigned a, unsigned b) { unsigned d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ unsigned sub_b(unsigned a, unsigned b) { unsigned d; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
 __device__ __forceinline__ unsigned mul_b(unsigned a, unsigned b) { unsigned d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
@@ -146,7 +155,8 @@ std::string emit_body(const unsigned char *code, int ncode, const std::string &r
 // rounding the exact result once to an 11-bit (8-bit) significand equals rounding it to
 // f32's 24 bits first and then to 16 bits (24 >= 2 * 11 + 2, so the double rounding is
 // innocuous), i.e. the result is bit for bit that of extend - operate in f32 - round.  neg
-// and abs are sign-bit operations.  Everything else unpacks to f32, applies the f32
+// and abs are sign-bit operations, relu clears the halves that compare <= 0, maximumf / minimumf
+// are the packed NaN-propagating instructions.  Everything else unpacks to f32, applies the f32
 // function and packs with one rounding conversion for both values.
 std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, std::ostringstream &os) {
   const std::string sfx = bf16 ? "_b" : "_h";
@@ -175,6 +185,7 @@ std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, st
       st.pop_back();
       if (op == 32) { st.push_back(def("(" + a + " ^ 0x80008000u)")); continue; }
       if (op == 33) { st.push_back(def("(" + a + " & 0x7fff7fffu)")); continue; }
+      if (op == 39) { st.push_back(def("relu" + sfx + "(" + a + ")")); continue; }
       const std::string lo = "lo" + sfx + "(" + a + ")", hi = "hi" + sfx + "(" + a + ")";
       auto f = [&](const std::string &x) -> std::string {
         switch (op) {
@@ -195,6 +206,8 @@ std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, st
       if (op == 64) { st.push_back(def("add" + sfx + "(" + a + ", " + b + ")")); continue; }
       if (op == 65) { st.push_back(def("sub" + sfx + "(" + a + ", " + b + ")")); continue; }
       if (op == 66) { st.push_back(def("mul" + sfx + "(" + a + ", " + b + ")")); continue; }
+      if (op == 68) { st.push_back(def("max" + sfx + "(" + a + ", " + b + ")")); continue; }
+      if (op == 69) { st.push_back(def("min" + sfx + "(" + a + ", " + b + ")")); continue; }
       const char *fn = op == 67 ? "__fdiv_rn" : op == 68 ? "maximumf" : "minimumf";
       if (op == 67 && (a == "0x3f803f80u" || a == "0x3c003c00u")) {   // 1 / b, as above
         const std::string rcp = bf16 ? "rcp_b" : "rcp_h";
