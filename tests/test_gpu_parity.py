@@ -850,6 +850,32 @@ def test_unary_functions_of_a_16_bit_chain_over_every_value(pkg, sess, kind, op,
     assert np.all(np.abs(got[differ].astype(np.int32) - ref_bits[differ].astype(np.int32)) <= 1)
 
 
+@pytest.mark.parametrize("op", ["max", "min", "add", "sub", "mul"])
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_packed_binary_operations_of_a_16_bit_chain(pkg, sess, kind, op):
+    """A million random pairs of bit patterns plus every pair of special values (signed zeros,
+    infinities, a NaN, the smallest denormals): the packed instructions of the 16-bit chains give
+    the bits of extend - operate in f32 - round (maximumf / minimumf: NaN if either is one)."""
+    B = pkg.blob
+    rng = np.random.default_rng(5)
+    a = rng.integers(0, 65536, (1024, 1024), dtype=np.uint16)
+    b = rng.integers(0, 65536, (1024, 1024), dtype=np.uint16)
+    inf, nan_bits = (0x7C00, 0x7E00) if kind == "f16" else (0x7F80, 0x7FC0)
+    sp = np.array([0x0000, 0x8000, inf, inf | 0x8000, nan_bits, 0x0001, 0x8001], np.uint16)
+    a[0, :49], b[0, :49] = np.repeat(sp, 7), np.tile(sp, 7)
+    back = _NP16[kind][2]
+    da, db, dy = sess.upload(a), sess.upload(b), sess.alloc(a.nbytes)
+    sess.run(B.expr("pairs_" + op, 1024, 1024, "in0 in1 " + op, B.F16 if kind == "f16" else B.BF16), [da, db, dy])
+    assert sess.last_kernel() == "expr_jit"
+    got = sess.download(dy, a.shape, np.uint16)
+    name = {"max": "maximumf", "min": "minimumf", "add": "addf", "sub": "subf", "mul": "mulf"}[op]
+    with np.errstate(all="ignore"):
+        ref = oracle.binary(name, back(a), back(b), _NP16[kind][0])
+    nan = np.isnan(ref)
+    assert np.array_equal(np.isnan(back(got)), nan)
+    assert np.array_equal(got[~nan], _NP16[kind][1](ref)[~nan])
+
+
 @pytest.mark.parametrize("shape", [(512, 1024), (200, 70), (40, 300), (6, 606208)])
 @pytest.mark.parametrize("kind", ["f32", "f16", "bf16"])
 def test_fused_chain_into_column_reduce(pkg, sess, kind, expr_path, shape):
