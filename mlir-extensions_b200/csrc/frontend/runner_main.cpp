@@ -413,6 +413,14 @@ private:
       for (auto &v : o->outs) uses[v]++;
       for (auto &v : o->iterInits) uses[v]++;
       if (o->body && o->name == "scf.for") index(*o->body, defs, uses);
+      if (o->name == "scf.while" && o->body && o->elseBody) {
+        // uses only: a value of this block that a region of the loop reads has a use that is not
+        // visible at this level (no fusion across it); the regions' own definitions are indexed
+        // when they run
+        std::map<std::string, const Op *> regionDefs;
+        index(*o->body, regionDefs, uses);
+        index(*o->elseBody, regionDefs, uses);
+      }
     }
   }
 
