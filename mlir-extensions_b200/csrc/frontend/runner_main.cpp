@@ -405,6 +405,16 @@ private:
     for (size_t k = 0; k < op.results.size() && k < forwarded.size(); ++k) fr.vals[op.results[k]] = forwarded[k];
   }
 
+  // tensors of the enclosing function that the region of a linalg.generic reads with
+  // tensor.extract: uses that no operand list shows
+  static void countCaptured(const Block &b, std::map<std::string, int> &uses) {
+    for (auto &o : b.ops) {
+      if (o->name == "tensor.extract" && !o->operands.empty()) uses[o->operands[0]]++;
+      if (o->body) countCaptured(*o->body, uses);
+      if (o->elseBody) countCaptured(*o->elseBody, uses);
+    }
+  }
+
   static void index(const Block &b, std::map<std::string, const Op *> &defs, std::map<std::string, int> &uses) {
     for (auto &o : b.ops) {
       for (auto &r : o->results) defs[r] = o.get();
@@ -413,6 +423,7 @@ private:
       for (auto &v : o->outs) uses[v]++;
       for (auto &v : o->iterInits) uses[v]++;
       if (o->body && o->name == "scf.for") index(*o->body, defs, uses);
+      if (o->body && o->name == "linalg.generic") countCaptured(*o->body, uses);
       if (o->name == "scf.while" && o->body && o->elseBody) {
         // uses only: a value of this block that a region of the loop reads has a use that is not
         // visible at this level (no fusion across it); the regions' own definitions are indexed
