@@ -850,6 +850,62 @@ def test_unary_functions_of_a_16_bit_chain_over_every_value(pkg, sess, kind, op,
     assert np.all(np.abs(got[differ].astype(np.int32) - ref_bits[differ].astype(np.int32)) <= 1)
 
 
+def _f32_sweep():
+    """Every sign, exponent and leading seven mantissa bits of f32 (all 65536 upper halves) with
+    four lower halves each: zeros, denormals, the overflow and underflow thresholds of exp, the
+    infinities and NaNs are all in it."""
+    hi = np.arange(65536, dtype=np.uint32).reshape(256, 256, 1) << 16
+    lo = np.array([0x0000, 0x0001, 0x8000, 0xFFFF], np.uint32).reshape(1, 1, 4)
+    return (hi | lo).reshape(256, 1024).view(np.float32)
+
+
+def _same_class(got, ref):
+    """NaNs, infinities (with sign) and zeros (with sign) fall in the same places."""
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    for special in (np.inf, -np.inf):
+        assert np.array_equal(got == special, ref == special)
+    zero = ref == 0
+    assert np.array_equal(got[zero].view(np.uint32), ref[zero].view(np.uint32))
+
+
+@pytest.mark.parametrize("op", ["exp", "log", "sqrt", "rsqrt", "tanh", "relu", "neg", "abs", "rcp"])
+def test_unary_functions_of_an_f32_chain_over_every_exponent(pkg, sess, op, expr_path):
+    B = pkg.blob
+    x = _f32_sweep()
+    d, dy = sess.upload(x), sess.alloc(x.nbytes)
+    prog = "one in0 div" if op == "rcp" else "in0 " + op
+    sess.run(B.expr("sweep_" + op, 256, 1024, prog, B.F32), [d, dy])
+    assert sess.last_kernel() == "expr" + expr_path
+    got = sess.download(dy, x.shape, np.float32)
+    with np.errstate(all="ignore"):
+        if op == "rcp":
+            ref = oracle.binary("divf", np.ones_like(x), x)
+        else:
+            ref = oracle.unary({"neg": "negf", "abs": "absf"}.get(op, op), x)
+    _same_class(got, ref)
+    ok = np.isfinite(ref) & (ref != 0)
+    if op in ("exp", "log", "tanh"):   # libm on the host and on the device: a few units in the last place
+        assert oracle.max_rel_err(got[ok], ref[ok], 1e-37) <= 2.0 ** -21
+    else:
+        assert np.array_equal(got[ok].view(np.uint32), ref[ok].view(np.uint32))
+
+
+def test_standalone_silu_and_relu_over_every_exponent(pkg, sess):
+    x = _f32_sweep().reshape(-1)
+    dX, dY = sess.upload(x), sess.alloc(x.nbytes)
+    for name, epi, fn in (("relu", pkg.blob.EPI_RELU, oracle.relu), ("silu", pkg.blob.EPI_SILU, oracle.silu)):
+        sess.run(pkg.blob.eltwise(name + "_sweep", x.size, epi), [dX, dY])
+        got = sess.download(dY, x.shape, np.float32)
+        with np.errstate(all="ignore"):
+            ref = fn(x)
+        _same_class(got, ref)
+        ok = np.isfinite(ref) & (ref != 0)
+        if name == "relu":
+            assert np.array_equal(got[ok].view(np.uint32), ref[ok].view(np.uint32))
+        else:
+            assert oracle.max_rel_err(got[ok], ref[ok], 1e-37) <= 1e-5
+
+
 @pytest.mark.parametrize("op", ["max", "min", "add", "sub", "mul"])
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
 def test_packed_binary_operations_of_a_16_bit_chain(pkg, sess, kind, op):
