@@ -339,6 +339,38 @@ def test_gemm_transposed_and_16bit_on_the_exact_simt_path(pkg, sess, kind):
 
 
 @pytest.mark.parametrize("silu", ["hardware exp2 / reciprocal (default)", "reference chain"])
+def test_gemm_silu_where_the_exponential_overflows(silu):
+    """Pre-activations of a few hundred either way: exp(-x) overflows below x = -88.7, where silu is
+    x / inf = -0, and vanishes above +88.7, where silu is x.  No NaN may come out of either form."""
+    import subprocess
+    import sys
+    prog = (
+        "import sys, numpy as np; sys.path.insert(0, %r)\n"
+        "from __graft_entry__ import load_package; from oracle import oracle\n"
+        "pkg = load_package(); B = pkg.blob\n"
+        "M, N, K = 512, 1024, 128\n"
+        "A = oracle.to_bf16_bits(oracle.fill_uniform((M, K), 3, -16.0, 16.0))\n"
+        "Bm = oracle.to_bf16_bits(oracle.fill_uniform((K, N), 4, -4.0, 4.0))\n"
+        "with pkg.Session(device=0) as s:\n"
+        "    dA, dB, dC = s.upload(A), s.upload(Bm), s.upload(np.full((M, N), np.nan, np.float32))\n"
+        "    s.run(B.gemm('g', M, N, K, B.BF16, B.EPI_SILU), [dA, dB, dC])\n"
+        "    assert s.last_kernel() == 'gemm_tcgen05_2cta', s.last_kernel()\n"
+        "    got = s.download(dC, (M, N), np.float32)\n"
+        "pre = oracle.matmul_x16_f32(A, Bm, True)\n"
+        "assert (pre < -100).mean() > 0.2 and (pre > 100).mean() > 0.2\n"
+        "ref = oracle.silu(pre)\n"
+        "assert not np.isnan(got).any() and not np.isinf(got).any()\n"
+        "assert np.all(np.abs(got[pre < -100]) == 0) and np.all(np.signbit(got[pre < -100]))\n"
+        "err = oracle.rel_frobenius(got, ref)\n"
+        "assert err <= 1e-3, err\n" % (os.path.dirname(HERE),))
+    env = dict(os.environ)
+    if silu == "reference chain":
+        env["IMEX_GEMM_PRECISE_EPILOGUE"] = "1"
+    r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("silu", ["hardware exp2 / reciprocal (default)", "reference chain"])
 @pytest.mark.parametrize("shape", [(512, 1024, 128), (300, 520, 200), (1000, 1544, 72), (2304, 4608, 256),
                                    (20000, 512, 64)])
 def test_gemm_pair_kernel_silu_flavours(shape, silu):
