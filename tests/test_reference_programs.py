@@ -160,6 +160,28 @@ def test_the_hot_path_programs_use_the_hot_path_kernels():
     assert r.returncode == 0 and r.stdout.count("+bias") == 6, r.stdout[-800:] + r.stderr[-400:]
 
 
+# a program of this repository with the tensor-level forms beside the hot path (concatenation through
+# scf.if / tensor.dim / tensor.extract, dynamic extents, slice, pad, scf.while) and CHECK lines of its own:
+# it needs no reference checkout
+OWN_PROGRAM = os.path.join(MLIR, "tensor_forms.mlir")
+
+
+@needs_oracle_runner
+@pytest.mark.parametrize("mode", [["--all-loopnests"], []])
+def test_cpu_checker_on_the_tensor_forms(mode):
+    r = _run([ORACLE_RUNNER, OWN_PROGRAM, "-e", "main"] + mode)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    _check(OWN_PROGRAM, r.stdout)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [["--all-loopnests"], []])
+def test_gpu_runner_on_the_tensor_forms(mode):
+    r = _run([RUNNER, OWN_PROGRAM, "-e", "main"] + mode)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    _check(OWN_PROGRAM, r.stdout)
+
+
 # ------------------------------------------------------------------ GPU
 @pytest.mark.gpu
 @pytest.mark.parametrize("rel", HOT_PATH + OTHER_PROGRAMS + SLOW_ON_CPU)
