@@ -34,7 +34,8 @@ struct LoopNestKernel {
   std::string summary;              // for plans and diagnostics
 };
 
-// False (with `why`) when the op cannot be written as a loop nest: dynamic shapes, an
+// False (with `why`) when the op cannot be written as a loop nest: extents still dynamic in
+// the types it is given (`types` carries the actual ones when the IR's are dynamic), an
 // operation or element type without a C counterpart, an output indexed by a reduction
 // dimension, or a parallel dimension missing from an output's map.
 // `types`, when given, replaces the operand types written in the op (ins, then outs): the

@@ -237,7 +237,7 @@ private:
   Value makeTensorExact(void *stream, const Type &t, bool hostVisible = false) {
     if (t.unranked) die("cannot allocate an unranked tensor");
     for (auto d : t.shape)
-      if (d < 0) die("dynamic shapes are not supported: kernel arguments carry no shape");
+      if (d < 0) die("an array with an extent that is still unknown cannot be allocated (" + t.str() + ")");
     Value v;
     v.kind = Value::Tensor;
     v.type = t;
