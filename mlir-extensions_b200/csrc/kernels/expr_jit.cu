@@ -208,8 +208,10 @@ std::string emit_body_packed(const unsigned char *code, int ncode, bool bf16, st
       if (op == 66) { st.push_back(def("mul" + sfx + "(" + a + ", " + b + ")")); continue; }
       if (op == 68) { st.push_back(def("max" + sfx + "(" + a + ", " + b + ")")); continue; }
       if (op == 69) { st.push_back(def("min" + sfx + "(" + a + ", " + b + ")")); continue; }
-      const char *fn = op == 67 ? "__fdiv_rn" : op == 68 ? "maximumf" : "minimumf";
-      if (op == 67 && (a == "0x3f803f80u" || a == "0x3c003c00u")) {   // 1 / b, as above
+      // what is left is the division: 1 / b through the hardware reciprocal (rcp_h, rcp_b: the
+      // same 16-bit value as the quotient for every b), a / b as the IEEE quotient in f32
+      const char *fn = "__fdiv_rn";
+      if (a == "0x3f803f80u" || a == "0x3c003c00u") {
         const std::string rcp = bf16 ? "rcp_b" : "rcp_h";
         st.push_back(def(via_f32(rcp + "(lo" + sfx + "(" + b + "))", rcp + "(hi" + sfx + "(" + b + "))")));
         continue;
